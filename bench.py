@@ -1,0 +1,359 @@
+"""Benchmark of the fdmmv hot path:  out = K(X,C)^T (K(X,C) v + w).
+
+    python bench.py --gpus N --steps K --warmup W            # this implementation
+    python bench.py --impl reference --steps K --warmup W    # the reference algorithm on the host cores
+
+Workload (one step = one fdmmv over one batch of synthetic input): benchmark configuration 2 --
+Gaussian kernel sigma = 5, fp32, X: 1,000,000 x 28 from a two-component isotropic Gaussian mixture
+(means +-0.5, unit variance), C: 20,000 rows of X, v ~ N(0,1) (M x 1), w ~ N(0,1) (N x 1).  With N
+GPUs every rank holds its own 1,000,000-row shard (weak scaling), C and v are replicated, and the
+M x 1 partial results are summed with one NCCL all-reduce per step.
+
+Prints ONE JSON line.  `value` is kernel pair-evaluations per second (N*M*T / time) with the inputs
+resident in HBM; `e2e` is the same metric through the host-buffer entry point (pinned host inputs
+copied in, result copied out, inside the timed region); `roofline` describes the dominant kernel
+(the tcgen05 sweep), timed live with CUDA events on its stream; `cpu_baseline` is the CPU oracle
+timed on a bounded sample on this machine's host cores.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np
+import torch
+
+N_PER_GPU = 1_000_000
+M = 20_000
+D = 28
+T = 1
+SIGMA = 5.0
+METRIC = "fdmmv pair-evals/s (N*M*T)"
+UNIT = "pair-evals/s"
+WORKLOAD = "config2: fdmmv Gaussian sigma=5 fp32, N=1e6 per GPU x d=28 mixture, M=20000 sampled rows, T=1, w~N(0,1)"
+
+
+def gen_shard(n, seed, device):
+    g = torch.Generator(device=device).manual_seed(seed)
+    z = (torch.rand(n, 1, generator=g, device=device) < 0.5).to(torch.float32)
+    X = torch.randn(n, D, generator=g, device=device) + (2.0 * z - 1.0) * 0.5
+    w = torch.randn(n, T, generator=g, device=device)
+    return X, w
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(bf16_tflops=float(p["bf16_tflops"]), bf16_sustained=float(p.get("bf16_tflops_sustained", 0.0)),
+                    hbm_gbs=float(p["hbm_gbs"]), source="measured")
+    return dict(bf16_tflops=1590.0, bf16_sustained=1400.0, hbm_gbs=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=self.out, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.out.close()
+        sm, smax, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        with open(self.path) as f:
+            for line in f:
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 9:
+                    continue
+                try:
+                    sm.append(float(parts[1]))
+                    smax.append(float(parts[2]))
+                    power.append(float(parts[3]))
+                except ValueError:
+                    continue
+                for nm, val in zip(names, parts[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(nm)
+        os.unlink(self.path)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        busy = [s for s, p in zip(sm, power) if p > 300.0] or sm
+        return {"sm_mhz": float(np.median(busy)), "sm_max_mhz": float(max(smax)), "power_w_max": float(max(power)),
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def time_cpu_oracle(n_sample, reps):
+    """Times the CPU oracle's fdmmv (the reference algorithm: blocked GEMM + element-wise passes)
+    on n_sample rows of the workload with all host threads.  Returns (pair-evals/s, seconds, cores)."""
+    from oracle import falkon_oracle as fo
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    X, w = gen_shard(n_sample, 1002, "cpu")
+    g = torch.Generator().manual_seed(2002)
+    C = X[torch.randperm(n_sample, generator=g)[:M]].contiguous()
+    v = torch.randn(M, T, generator=g)
+    best = None
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        fo.fdmmv(X, C, v, w, "gaussian", SIGMA, max_block_elems=256 * 2**20)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return n_sample * M * T / best, best, cores
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    n_sample = 50_000
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    from oracle import falkon_oracle as fo
+
+    X, w = gen_shard(n_sample, 1002, "cpu")
+    g = torch.Generator().manual_seed(2002)
+    C = X[torch.randperm(n_sample, generator=g)[:M]].contiguous()
+    v = torch.randn(M, T, generator=g)
+    for _ in range(args.warmup):
+        fo.fdmmv(X, C, v, w, "gaussian", SIGMA, max_block_elems=256 * 2**20)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        fo.fdmmv(X, C, v, w, "gaussian", SIGMA, max_block_elems=256 * 2**20)
+    dt = time.perf_counter() - t0
+    value = args.steps * n_sample * M * T / dt
+    sample = f"each step = one fdmmv on the first {n_sample} rows of the workload (M={M}, d={D}), CPU oracle port of the reference algorithm, {cores} threads"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": sample},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--rows", type=int, default=N_PER_GPU, help="rows of X per GPU (default: the benchmark size)")
+    ap.add_argument("--simt", action="store_true", help="force the SIMT kernel (comparison runs)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 0)
+    if args.impl == "reference":
+        return run_reference(args)
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a GPU (there is no CPU fallback)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    import torch.distributed as dist
+
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    from falkon_b200 import FalkonOptions, _lib
+    from falkon_b200.kernels import GaussianKernel
+    from falkon_b200.sharded import ShardedKernelOps
+
+    _lib.build()
+    lib = _lib.load()
+    if lib.flk_check_device() != 0:
+        raise RuntimeError(_lib.last_error())
+    n = args.rows
+    X, w = gen_shard(n, 1002 + rank, dev)
+    g = torch.Generator(device=dev).manual_seed(2002)
+    # centres: M rows of rank 0's shard, replicated on every rank
+    idx = torch.randperm(n, generator=g, device=dev)[:M]
+    C = X[idx].contiguous()
+    v = torch.randn(M, T, generator=g, device=dev)
+    if world > 1:
+        dist.broadcast(C, 0)
+        dist.broadcast(v, 0)
+    opt = FalkonOptions()
+    kernel = GaussianKernel(SIGMA, opt=opt)
+    flags = _lib.FLAG_FORCE_SIMT if args.simt else 0
+    kernel.params.flk_flags = flags
+    ops = ShardedKernelOps(kernel)
+    out = torch.empty(M, T, dtype=torch.float32, device=dev)
+    flush = torch.empty(256 * 2**20, dtype=torch.uint8, device=dev)  # > L2 (126 MB)
+
+    def step():
+        ops.dmmv(X, C, v, w, out=out)
+
+    for _ in range(max(args.warmup, 0)):
+        step()
+    torch.cuda.synchronize()
+
+    # ---------------- timed region: K steps, device events per step, L2 flushed between steps ----------
+    _lib.set_timing(True)
+    sampler = ClockSampler(local_rank if "CUDA_VISIBLE_DEVICES" not in os.environ else
+                           int(os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank]))
+    if rank == 0:
+        sampler.start()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    stops = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    sweep_ms = []
+    launches0 = _lib.launch_count()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    wall0 = time.perf_counter()
+    for i in range(args.steps):
+        flush.fill_(i & 0xFF)
+        starts[i].record()
+        step()
+        stops[i].record()
+        sweep_ms.append(_lib.sweep_ms())  # waits for this step's sweeps (also paces the host)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    wall = time.perf_counter() - wall0
+    launches = _lib.launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    _lib.set_timing(False)
+    dev_ms = sum(s.elapsed_time(e) for s, e in zip(starts, stops))
+    tmax = torch.tensor([dev_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+    total_ms = float(tmax.item())
+    ms_per_step = total_ms / args.steps
+    pairs_per_step = float(n) * world * M * T
+    value = pairs_per_step / (ms_per_step * 1e-3)
+    tc_status = _lib.tc_status(dev)
+
+    # ---------------- end-to-end through the host-buffer entry point (rank-local, N=1 semantics per rank) ----
+    Xh = X.cpu().pin_memory()
+    Ch = C.cpu().pin_memory()
+    vh = v.cpu().pin_memory()
+    wh = w.cpu().pin_memory()
+    outh = torch.empty(M, T, dtype=torch.float32).pin_memory()
+    e2e_steps = max(3, min(args.steps, 5))
+    ops.dmmv(Xh, Ch, vh, wh, out=outh)  # warm-up (sizes the workspace)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        ops.dmmv(Xh, Ch, vh, wh, out=outh)  # returns after the result is on the host
+    torch.cuda.synchronize()
+    e2e_s = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
+    e2e_value = pairs_per_step * e2e_steps / float(e2e_s.item())
+    parity = float((outh.to(dev) - out).norm() / out.norm()) if world == 1 else None
+    h2d = (Xh.numel() + Ch.numel() + vh.numel() + wh.numel()) * 4
+    d2h = outh.numel() * 4
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    # ---------------- roofline of the dominant kernel ----------------
+    peaks = load_peaks()
+    s1 = float(np.mean([a for a, _ in sweep_ms if a >= 0])) if sweep_ms else float("nan")
+    s2 = float(np.mean([b for _, b in sweep_ms if b >= 0])) if sweep_ms else float("nan")
+    sweep_avg_ms = 0.5 * (s1 + s2)
+    pairs_per_launch = float(n) * M  # one sweep evaluates every (row, centre) pair once
+    uses_tc = bool(lib.flk_uses_tensor_cores(0, 0, D, T, flags))
+    sm_mhz = (clocks or {}).get("sm_mhz") or 1965.0
+    # tensor flops the 3xTF32 formulation needs per pair: 2 * (3 d + 2 * norm pieces)
+    k_used = 3 * D + 2 * 2
+    tensor_tflops = pairs_per_launch * 2 * k_used / (sweep_avg_ms * 1e-3) / 1e12
+    tf32_peak = peaks["bf16_tflops"] / 2.0
+    mufu_peak = 148 * 16 * sm_mhz * 1e6  # ex2 per second at the sampled clock
+    fp32_peak_tflops = 148 * 128 * 2 * sm_mhz * 1e6 / 1e12
+    alg_flops_pair = 2 * D + 2 * T + 4 + 1
+    roofline = {
+        "bound": "tensor",
+        "kernel": "flk::tc::kmv_tc_kernel" if uses_tc else "flk::kmv_simt_kernel",
+        "achieved": tensor_tflops if uses_tc else pairs_per_launch * alg_flops_pair / (sweep_avg_ms * 1e-3) / 1e12,
+        "peak": tf32_peak if uses_tc else fp32_peak_tflops,
+        "unit": "TFLOP/s",
+        "frac": (tensor_tflops / tf32_peak) if uses_tc else
+                (pairs_per_launch * alg_flops_pair / (sweep_avg_ms * 1e-3) / 1e12 / fp32_peak_tflops),
+        "traffic": None,
+        "peak_source": (f"tf32 dense peak = bf16 {peaks['source']} peak / 2" if uses_tc else
+                        "fp32 FMA lanes x sampled SM clock (nominal lanes)"),
+        "launch_ms": {"sweep1_Kv": s1, "sweep2_KTu": s2},
+        "pairs_per_launch": pairs_per_launch,
+        "mufu": {"achieved_gops": pairs_per_launch / (sweep_avg_ms * 1e-3) / 1e9, "peak_gops": mufu_peak / 1e9,
+                 "frac": pairs_per_launch / (sweep_avg_ms * 1e-3) / mufu_peak,
+                 "note": "one ex2 per kernel evaluation; peak = 148 SMs x 16 MUFU lanes x sampled SM clock"},
+        "fp32_algorithmic": {"flops_per_pair": alg_flops_pair,
+                             "achieved_tflops": pairs_per_launch * alg_flops_pair / (sweep_avg_ms * 1e-3) / 1e12,
+                             "peak_tflops": fp32_peak_tflops,
+                             "frac": pairs_per_launch * alg_flops_pair / (sweep_avg_ms * 1e-3) / 1e12 / fp32_peak_tflops,
+                             "note": "north-star view: work counted as if done on the FP32 FMA pipe"},
+    }
+    cpu_baseline = None
+    if not args.no_cpu_baseline and world == 1:
+        n_cpu = 100_000
+        val, secs, cores = time_cpu_oracle(n_cpu, reps=1)
+        cpu_baseline = {"value": val, "unit": UNIT, "cores": cores, "kind": "port",
+                        "sample": f"one fdmmv on {n_cpu} rows of the workload (M={M}, d={D}), {secs:.1f} s, CPU oracle with {cores} threads"}
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": WORKLOAD, "rows_per_gpu": n, "global_rows": n * world, "centres": M, "d": D, "T": T,
+                   "kernel": "simt" if args.simt else "tcgen05-3xTF32", "l2": "256 MB buffer written between timed steps",
+                   "collective": "NCCL all-reduce of the M x T partial" if world > 1 else "none"},
+        "roofline": roofline,
+        "cpu_baseline": cpu_baseline,
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "steps": e2e_steps, "rel_l2_vs_device_path": parity},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+        "wall_s_timed_region": wall,
+        "tc_status": tc_status,
+    }
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

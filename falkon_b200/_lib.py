@@ -1,0 +1,260 @@
+"""Loader (and builder) of ``libfalkon_b200.so`` and thin ctypes wrappers around its C ABI.
+
+The library is built in-tree with nvcc for sm_100a (``build()``), and loaded with ctypes.  There
+is no fallback: if the shared library is missing or fails to load, every product raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+import threading
+from typing import Optional
+
+import numpy as np
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_CSRC = os.path.join(_HERE, "csrc")
+LIB_PATH = os.path.join(_HERE, "libfalkon_b200.so")
+
+FLK_F32, FLK_F64 = 0, 1
+FLK_GAUSSIAN, FLK_LAPLACIAN, FLK_MATERN15, FLK_MATERN25 = 0, 1, 2, 3
+FLAG_FORCE_SIMT, FLAG_FORCE_TC = 1, 2
+
+FLK_ERR_BAD_ARG, FLK_ERR_LAYOUT, FLK_ERR_WORKSPACE = -1, -2, -3
+FLK_ERR_CUDA, FLK_ERR_UNSUPPORTED, FLK_ERR_DEVICE, FLK_ERR_TIMEOUT = -4, -5, -6, -7
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC", "-shared",
+]
+
+_lock = threading.Lock()
+_lib: Optional[ctypes.CDLL] = None
+
+
+def sources():
+    return [os.path.join(_CSRC, f) for f in sorted(os.listdir(_CSRC)) if f.endswith((".cu", ".cuh"))] + [
+        os.path.join(os.path.dirname(_HERE), "include", "falkon_b200.h")
+    ]
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    """Compiles csrc/flk_api.cu into libfalkon_b200.so (nvcc cross-compiles without a GPU)."""
+    if not force and os.path.exists(LIB_PATH):
+        newest = max(os.path.getmtime(s) for s in sources())
+        if os.path.getmtime(LIB_PATH) >= newest:
+            return LIB_PATH
+    nvcc = os.environ.get("NVCC", "nvcc")
+    cmd = [nvcc] + NVCC_FLAGS + ["-o", LIB_PATH, os.path.join(_CSRC, "flk_api.cu")]
+    if verbose:
+        print(" ".join(cmd))
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"nvcc failed:\n{res.stdout}\n{res.stderr}")
+    return LIB_PATH
+
+
+_i64, _int, _vp = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p
+_dp = ctypes.POINTER(ctypes.c_double)
+
+_MAT = [_vp, _i64, _i64, _i64]  # pointer, rows, row stride, col stride
+
+_SIGNATURES = {
+    "flk_version": (_int, []),
+    "flk_last_error": (ctypes.c_char_p, []),
+    "flk_status_name": (ctypes.c_char_p, [_int]),
+    "flk_check_device": (_int, []),
+    "flk_uses_tensor_cores": (_int, [_int, _int, _i64, _i64, _int]),
+    "flk_launch_count": (_i64, []),
+    "flk_square_norm": (_int, [_int, _vp, _i64, _i64, _i64, _i64, _dp, _i64, _vp, _vp]),
+    "flk_fmmv_workspace_bytes": (_i64, [_int, _int, _i64, _i64, _i64, _i64, _int]),
+    "flk_fdmmv_workspace_bytes": (_i64, [_int, _int, _i64, _i64, _i64, _i64, _int]),
+    "flk_fmmv_host_workspace_bytes": (_i64, [_int, _int, _i64, _i64, _i64, _i64, _int]),
+    "flk_fdmmv_host_workspace_bytes": (_i64, [_int, _int, _i64, _i64, _i64, _i64, _int]),
+    # dtype, kernel, X1(4), X2(4), d, v ptr, t, v strides(2), out ptr + strides(3), sigma, len, ws, bytes, flags, stream
+    "flk_fmmv": (_int, [_int, _int] + _MAT + _MAT + [_i64, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _dp, _i64, _vp, _i64, _int, _vp]),
+    "flk_fmmv_host": (_int, [_int, _int] + _MAT + _MAT + [_i64, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _dp, _i64, _vp, _i64, _int, _vp]),
+    # dtype, kernel, X1(4), X2(4), d, v(3), w(3), t, out(3), sigma, len, ws, bytes, flags, stream
+    "flk_fdmmv": (_int, [_int, _int] + _MAT + _MAT + [_i64, _vp, _i64, _i64, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _dp, _i64, _vp, _i64, _int, _vp]),
+    "flk_fdmmv_host": (_int, [_int, _int] + _MAT + _MAT + [_i64, _vp, _i64, _i64, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _dp, _i64, _vp, _i64, _int, _vp]),
+    "flk_tc_status": (_int, [_vp, _vp, ctypes.POINTER(_int)]),
+    "flk_set_timing": (_int, [_int]),
+    "flk_get_sweep_ms": (_int, [ctypes.POINTER(ctypes.c_float), ctypes.POINTER(ctypes.c_float)]),
+}
+
+EXPORTED_SYMBOLS = tuple(_SIGNATURES)
+
+
+def load() -> ctypes.CDLL:
+    """Loads the shared library (once per process); raises if it does not exist."""
+    global _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} not found: the CUDA library has not been built "
+                "(run `python -c 'import __graft_entry__ as g; g.build()'` or falkon_b200._lib.build()). "
+                "falkon_b200 has no CPU fallback."
+            )
+        lib = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in _SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+        return lib
+
+
+class FlkError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(message)
+        self.status = status
+
+
+def last_error() -> str:
+    return load().flk_last_error().decode()
+
+
+def raise_for_status(status: int):
+    """Maps a C status code to the exception type the reference raises for the same mistake
+    (ValueError for shapes / layout, RuntimeError for device problems, MemoryError for workspace)."""
+    if status == 0:
+        return
+    msg = last_error()
+    name = load().flk_status_name(status).decode()
+    text = f"{name}: {msg}"
+    if status in (FLK_ERR_BAD_ARG, FLK_ERR_LAYOUT):
+        raise ValueError(text)
+    if status == FLK_ERR_WORKSPACE:
+        raise MemoryError(text)
+    if status == FLK_ERR_UNSUPPORTED:
+        raise NotImplementedError(text)
+    raise FlkError(status, text)
+
+
+# ---------------------------------------------------------------------------------------------
+# workspace cache: one growing byte buffer per device, handed to the C ABI (which never allocates)
+# ---------------------------------------------------------------------------------------------
+_workspaces = {}
+
+
+def workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    key = (device.type, device.index)
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        if buf is not None:
+            del _workspaces[key]
+            del buf
+        buf = torch.empty(int(nbytes * 1.05) + 4096, dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
+def release_workspaces():
+    _workspaces.clear()
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return FLK_F32
+    if dtype == torch.float64:
+        return FLK_F64
+    raise TypeError(f"falkon_b200 supports float32 and float64 data, not {dtype}")
+
+
+def _mat_args(t: Optional[torch.Tensor], with_rows: bool = True):
+    if t is None:
+        return [None, 0, 0, 0] if with_rows else [None, 0, 0]
+    args = [ctypes.c_void_p(t.data_ptr())]
+    if with_rows:
+        args.append(t.shape[0])
+    args += [t.stride(0), t.stride(1)]
+    return args
+
+
+def _sigma_args(sigma: np.ndarray):
+    sigma = np.ascontiguousarray(sigma, dtype=np.float64).reshape(-1)
+    return sigma, sigma.ctypes.data_as(_dp), sigma.shape[0]
+
+
+def call_fmmv(kernel_id, sigma, X1, X2, v, out, flags=0, host=False, device=None):
+    """out[n, t] = k(X1, X2) v through the C ABI (device pointers, or host pointers with host=True)."""
+    lib = load()
+    dt = dtype_code(X1.dtype)
+    n, d = X1.shape
+    m = X2.shape[0]
+    t = v.shape[1]
+    dev = device if host else X1.device
+    query = lib.flk_fmmv_host_workspace_bytes if host else lib.flk_fmmv_workspace_bytes
+    need = query(dt, kernel_id, n, m, d, t, flags)
+    if need < 0:
+        raise_for_status(int(need))
+    keep, sig_ptr, sig_len = _sigma_args(sigma)
+    with torch.cuda.device(dev):
+        ws = workspace(dev, need)
+        stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        fn = lib.flk_fmmv_host if host else lib.flk_fmmv
+        status = fn(dt, kernel_id, *_mat_args(X1), *_mat_args(X2), d,
+                    ctypes.c_void_p(v.data_ptr()), t, v.stride(0), v.stride(1),
+                    *_mat_args(out, with_rows=False), sig_ptr, sig_len,
+                    ctypes.c_void_p(ws.data_ptr()), ws.numel(), flags, stream)
+    del keep
+    raise_for_status(status)
+    return out
+
+
+def call_fdmmv(kernel_id, sigma, X1, X2, v, w, out, flags=0, host=False, device=None):
+    """out[m, t] = k(X1, X2)^T (k(X1, X2) v + w) through the C ABI."""
+    lib = load()
+    dt = dtype_code(X1.dtype)
+    n, d = X1.shape
+    m = X2.shape[0]
+    t = v.shape[1] if v is not None else w.shape[1]
+    dev = device if host else X1.device
+    query = lib.flk_fdmmv_host_workspace_bytes if host else lib.flk_fdmmv_workspace_bytes
+    need = query(dt, kernel_id, n, m, d, t, flags)
+    if need < 0:
+        raise_for_status(int(need))
+    keep, sig_ptr, sig_len = _sigma_args(sigma)
+    with torch.cuda.device(dev):
+        ws = workspace(dev, need)
+        stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        fn = lib.flk_fdmmv_host if host else lib.flk_fdmmv
+        status = fn(dt, kernel_id, *_mat_args(X1), *_mat_args(X2), d,
+                    *_mat_args(v, with_rows=False), *_mat_args(w, with_rows=False), t,
+                    *_mat_args(out, with_rows=False), sig_ptr, sig_len,
+                    ctypes.c_void_p(ws.data_ptr()), ws.numel(), flags, stream)
+    del keep
+    raise_for_status(status)
+    return out
+
+
+def tc_status(device: torch.device) -> int:
+    """Status word of the last tensor-core launch that used this device's cached workspace."""
+    lib = load()
+    key = (device.type, device.index)
+    if key not in _workspaces:
+        return 0
+    out = ctypes.c_int(0)
+    with torch.cuda.device(device):
+        stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+        raise_for_status(lib.flk_tc_status(ctypes.c_void_p(_workspaces[key].data_ptr()), stream, ctypes.byref(out)))
+    return out.value
+
+
+def set_timing(enable: bool):
+    raise_for_status(load().flk_set_timing(1 if enable else 0))
+
+
+def sweep_ms():
+    """(sweep 1 ms, sweep 2 ms) of the most recent timed call; -1 where the sweep did not run."""
+    a, b = ctypes.c_float(-1), ctypes.c_float(-1)
+    raise_for_status(load().flk_get_sweep_ms(ctypes.byref(a), ctypes.byref(b)))
+    return a.value, b.value
+
+
+def launch_count() -> int:
+    return int(load().flk_launch_count())

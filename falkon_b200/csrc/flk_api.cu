@@ -1,0 +1,753 @@
+// extern "C" entry points of libfalkon_b200: argument checks, workspace planning, dispatch.
+#include <algorithm>
+#include <atomic>
+#include <vector>
+
+#include "flk_common.cuh"
+#include "flk_prep.cuh"
+#include "flk_simt.cuh"
+#include "flk_tc.cuh"
+
+namespace flk {
+
+static std::atomic<int64_t> g_launches{0};
+static inline void count_launch(int n = 1) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+constexpr int kNumSMs = 148;  // B200
+
+// Optional per-sweep timing (CUDA events recorded on the caller's stream around the dominant
+// kernel of each sweep).  Off by default; bench.py turns it on to measure the kernel live.
+struct SweepTimer {
+  bool enabled = false;
+  int device = -1;
+  cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};  // sweep 1 start/stop, sweep 2 start/stop
+  bool valid[2] = {false, false};
+};
+static SweepTimer g_timer;
+
+static int timer_mark(int slot, cudaStream_t stream) {
+  if (!g_timer.enabled) return FLK_OK;
+  int dev = 0;
+  FLK_CUDA_TRY(cudaGetDevice(&dev));
+  if (g_timer.device != dev || g_timer.ev[0] == nullptr) {
+    for (int i = 0; i < 4; ++i) {
+      if (g_timer.ev[i] != nullptr) cudaEventDestroy(g_timer.ev[i]);
+      FLK_CUDA_TRY(cudaEventCreate(&g_timer.ev[i]));
+    }
+    g_timer.device = dev;
+    g_timer.valid[0] = g_timer.valid[1] = false;
+  }
+  FLK_CUDA_TRY(cudaEventRecord(g_timer.ev[slot], stream));
+  if (slot & 1) g_timer.valid[slot >> 1] = true;
+  return FLK_OK;
+}
+
+struct Mat {
+  const void* ptr;
+  int64_t rows, cols, rs, cs;
+};
+
+static int check_mat(const char* name, const Mat& m, bool nullable) {
+  if (m.ptr == nullptr) {
+    if (nullable) return FLK_OK;
+    return fail(FLK_ERR_BAD_ARG, "%s: null pointer", name);
+  }
+  if (m.rows < 0 || m.cols < 0) return fail(FLK_ERR_BAD_ARG, "%s: negative size", name);
+  if (m.rs != 1 && m.cs != 1 && m.rows > 1 && m.cols > 1)
+    return fail(FLK_ERR_LAYOUT, "%s: must be memory contiguous along one dimension (strides %lld, %lld)",
+                name, (long long)m.rs, (long long)m.cs);
+  if (m.rs < 0 || m.cs < 0) return fail(FLK_ERR_LAYOUT, "%s: negative stride", name);
+  if (m.rows > 1 && m.cols > 1) {
+    if (m.cs == 1 && m.rs < m.cols) return fail(FLK_ERR_LAYOUT, "%s: row stride smaller than width", name);
+    if (m.rs == 1 && m.cs != 1 && m.cs < m.rows)
+      return fail(FLK_ERR_LAYOUT, "%s: column stride smaller than height", name);
+  }
+  return FLK_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// One "sweep" = raw[chunks][r_pad][tp] = sum_j k(A_i, B_j) vec[j][:]  over the whole reduction side.
+// ---------------------------------------------------------------------------------------------
+struct SweepPlan {
+  bool tc;            // tensor-core kernel?
+  int64_t r, s;       // live rows on the output / reduction side
+  int64_t r_pad, s_pad;
+  int tt, tp, t_chunks;
+  int br, bc;         // CTA tile (rows x columns)
+  int row_tiles, n_col_tiles, tiles_per_chunk, n_chunks;
+  int64_t raw_elems() const { return (int64_t)n_chunks * r_pad * tp; }
+};
+
+static void choose_tt(int64_t t, int* tt, int* tp) {
+  if (t <= 1) *tt = 1;
+  else if (t == 2) *tt = 2;
+  else *tt = 4;
+  *tp = (int)round_up(std::max<int64_t>(t, 1), *tt);
+}
+
+static SweepPlan plan_sweep(bool tc, int dtype, int64_t r, int64_t s, int64_t t) {
+  SweepPlan p;
+  p.tc = tc;
+  p.r = r;
+  p.s = s;
+  p.r_pad = round_up(std::max<int64_t>(r, 1), kRowPad);
+  p.s_pad = round_up(std::max<int64_t>(s, 1), kRowPad);
+  choose_tt(t, &p.tt, &p.tp);
+  p.t_chunks = p.tp / p.tt;
+  if (tc) {
+    p.br = tc::kRowsPerCta;
+    p.bc = tc::kColsPerTile;
+  } else {
+    p.br = 128;
+    p.bc = (dtype == FLK_F32) ? 128 : 64;
+  }
+  p.row_tiles = (int)ceil_div(std::max<int64_t>(r, 1), p.br);
+  p.n_col_tiles = (int)ceil_div(std::max<int64_t>(s, 1), p.bc);
+  // Split the reduction side into chunks so that the grid fills whole waves of the 148 SMs:
+  // among the chunk counts that give at least two waves (when the problem allows), take the one
+  // with the best wave efficiency, preferring fewer chunks (less partial-result traffic).
+  const int64_t resident = tc ? 1 : ((dtype == FLK_F32 && p.tt == 1) ? 2 : 1);
+  const int64_t slots = kNumSMs * resident;
+  const int64_t ctas_rows = (int64_t)p.row_tiles * p.t_chunks;
+  const int64_t min_tiles = tc ? 8 : 4;  // keep the row tile's staging cost amortised
+  const int64_t max_chunks = std::max<int64_t>(1, std::min<int64_t>(p.n_col_tiles / min_tiles, 4096));
+  int64_t best_chunks = 1;
+  double best_score = -1.0;
+  for (int64_t want = 1; want <= max_chunks; ++want) {
+    const int64_t tpc = ceil_div(p.n_col_tiles, want);
+    const int64_t chunks = ceil_div(p.n_col_tiles, tpc);
+    const int64_t ctas = ctas_rows * chunks;
+    const int64_t waves = ceil_div(ctas, slots);
+    double eff = (double)ctas / (double)(waves * slots);
+    if (ctas < 2 * slots) eff *= 0.5 * (double)ctas / (double)(2 * slots);  // too few CTAs to balance
+    if (eff > best_score + 0.01) {
+      best_score = eff;
+      best_chunks = chunks;
+    }
+    if (ctas >= 8 * slots) break;
+  }
+  p.tiles_per_chunk = (int)ceil_div(p.n_col_tiles, best_chunks);
+  p.n_chunks = (int)ceil_div(p.n_col_tiles, p.tiles_per_chunk);
+  return p;
+}
+
+static bool tc_eligible(int dtype, int kernel, int64_t d, int64_t t, int flags) {
+  (void)kernel;
+  (void)t;
+  if (flags & FLK_FLAG_FORCE_SIMT) return false;
+  if (dtype != FLK_F32) return false;
+  return tc::supports_d(d);
+}
+
+// Bump allocator over the caller's workspace (256-byte granules).
+struct Carver {
+  char* base;
+  int64_t off = 0;
+  explicit Carver(void* b) : base(reinterpret_cast<char*>(b)) {}
+  void* take(int64_t bytes) {
+    void* p = base ? base + off : nullptr;
+    off += round_up(std::max<int64_t>(bytes, 1), 256);
+    return p;
+  }
+};
+
+static inline int64_t esize(int dtype) { return dtype == FLK_F32 ? 4 : 8; }
+static inline int ld_for(int dtype, int64_t d) { return (int)round_up(d, dtype == FLK_F32 ? 4 : 2); }
+
+// Operand images in the workspace.
+struct Operand {
+  // SIMT form
+  void* xs = nullptr;     // [rows_pad x ld]
+  void* norms = nullptr;  // [rows_pad]
+  // tensor-core form
+  void* img_a = nullptr;  // tile images for the output side
+  void* img_b = nullptr;  // tile images for the reduction side
+};
+
+struct Layout {
+  bool tc;
+  int64_t total = 0;
+  void* status = nullptr;  // 256 bytes: device status word of the tensor-core kernel
+  void* sigma = nullptr;   // d entries of T (per-dimension length-scales)
+  Operand x1, x2;
+  void* vbuf = nullptr;  // padded copy of the vector operand of the first sweep
+  void* ubuf = nullptr;  // fdmmv only: u = K v + w, padded
+  void* raw1 = nullptr;
+  void* raw2 = nullptr;
+  SweepPlan s1, s2;
+};
+
+// need_x1_as_b / need_x2_as_a: which tensor-core images each operand needs.
+static Layout make_layout(void* ws, bool dmmv, bool has_v, int dtype, int kernel, int64_t n, int64_t m,
+                          int64_t d, int64_t t, int flags) {
+  Layout L;
+  L.tc = tc_eligible(dtype, kernel, d, t, flags);
+  const int64_t es = esize(dtype);
+  Carver c(ws);
+  L.status = c.take(256);
+  L.sigma = c.take(std::max<int64_t>(d, 1) * es);
+  L.s1 = plan_sweep(L.tc, dtype, n, m, t);  // rows = X1, reduction over X2
+  L.s2 = plan_sweep(L.tc, dtype, m, n, t);  // rows = X2, reduction over X1 (fdmmv only)
+  const int64_t n_pad = L.s1.r_pad, m_pad = L.s1.s_pad;
+  if (L.tc) {
+    const int64_t kp = tc::padded_k(d);
+    const bool first = !dmmv || has_v;  // is the first sweep executed?
+    if (first) L.x1.img_a = c.take(n_pad * kp * 4);
+    if (first) L.x2.img_b = c.take(m_pad * kp * 4);
+    if (dmmv) {
+      L.x2.img_a = c.take(m_pad * kp * 4);
+      L.x1.img_b = c.take(n_pad * kp * 4);
+    }
+  } else {
+    const int ld = ld_for(dtype, d);
+    L.x1.xs = c.take(n_pad * ld * es);
+    L.x1.norms = c.take(n_pad * es);
+    L.x2.xs = c.take(m_pad * ld * es);
+    L.x2.norms = c.take(m_pad * es);
+  }
+  const int tp = L.s1.tp;
+  if (!dmmv) {
+    L.vbuf = c.take(m_pad * tp * es);
+    L.raw1 = c.take(L.s1.raw_elems() * es);
+  } else {
+    if (has_v) {
+      L.vbuf = c.take(m_pad * tp * es);
+      L.raw1 = c.take(L.s1.raw_elems() * es);
+    }
+    L.ubuf = c.take(n_pad * tp * es);
+    L.raw2 = c.take(L.s2.raw_elems() * es);
+  }
+  L.total = c.off;
+  return L;
+}
+
+static int check_common(int dtype, int kernel, int64_t n, int64_t m, int64_t d, int64_t t) {
+  if (dtype != FLK_F32 && dtype != FLK_F64) return fail(FLK_ERR_BAD_ARG, "unknown dtype %d", dtype);
+  if (kernel < FLK_GAUSSIAN || kernel > FLK_MATERN25) return fail(FLK_ERR_BAD_ARG, "unknown kernel id %d", kernel);
+  if (n < 0 || m < 0 || d < 0 || t < 0) return fail(FLK_ERR_BAD_ARG, "negative dimension");
+  if (d > (1 << 20) || t > (1 << 20)) return fail(FLK_ERR_UNSUPPORTED, "d or t too large");
+  if (n > (int64_t)1 << 40 || m > (int64_t)1 << 40) return fail(FLK_ERR_UNSUPPORTED, "n or m too large");
+  return FLK_OK;
+}
+
+static int check_sigma(const double* sigma, int64_t sigma_len, int64_t d) {
+  if (sigma == nullptr) return fail(FLK_ERR_BAD_ARG, "sigma: null pointer");
+  if (sigma_len != 1 && sigma_len != d)
+    return fail(FLK_ERR_BAD_ARG, "sigma must have 1 or d=%lld entries, got %lld", (long long)d, (long long)sigma_len);
+  return FLK_OK;
+}
+
+static int check_workspace(const void* ws, int64_t have, int64_t need) {
+  if (ws == nullptr) return fail(FLK_ERR_WORKSPACE, "workspace: null pointer (%lld bytes needed)", (long long)need);
+  if ((reinterpret_cast<uintptr_t>(ws) & 255) != 0) return fail(FLK_ERR_WORKSPACE, "workspace must be 256-byte aligned");
+  if (have < need)
+    return fail(FLK_ERR_WORKSPACE, "workspace too small: %lld bytes given, %lld needed", (long long)have, (long long)need);
+  return FLK_OK;
+}
+
+// Uploads per-dimension length-scales (cast to T, as the reference casts sigma to the data dtype).
+template <typename T>
+static int upload_sigma(const double* sigma, int64_t sigma_len, void* dst, T* scalar_out, const T** dev_out,
+                        cudaStream_t stream) {
+  if (sigma_len == 1) {
+    *scalar_out = (T)sigma[0];
+    *dev_out = nullptr;
+    return FLK_OK;
+  }
+  std::vector<T> tmp((size_t)sigma_len);
+  for (int64_t k = 0; k < sigma_len; ++k) tmp[(size_t)k] = (T)sigma[k];
+  // pageable source: the runtime stages the bytes before returning, so `tmp` may go out of scope
+  FLK_CUDA_TRY(cudaMemcpyAsync(dst, tmp.data(), sizeof(T) * (size_t)sigma_len, cudaMemcpyHostToDevice, stream));
+  *scalar_out = (T)1;
+  *dev_out = reinterpret_cast<const T*>(dst);
+  return FLK_OK;
+}
+
+template <typename T>
+static int run_prep_rows(const Mat& X, const T* sigma_dev, T sigma_scalar, int sigma_len, void* xs, int ld,
+                         int64_t rows_pad, void* norms, cudaStream_t stream) {
+  int blocks = (int)ceil_div(rows_pad, kPrepRows);
+  prep_rows_kernel<T><<<blocks, 256, 0, stream>>>(reinterpret_cast<const T*>(X.ptr), X.rows, (int)X.cols, X.rs,
+                                                  X.cs, sigma_dev, sigma_scalar, sigma_len,
+                                                  reinterpret_cast<T*>(xs), ld, rows_pad,
+                                                  reinterpret_cast<T*>(norms));
+  count_launch();
+  FLK_CUDA_TRY(cudaGetLastError());
+  return FLK_OK;
+}
+
+template <typename T>
+static int run_prep_vec(const Mat& v, void* vbuf, int64_t s_pad, int tp, int tt, cudaStream_t stream) {
+  prep_vec_kernel<T><<<grid_for(s_pad * tp), 256, 0, stream>>>(reinterpret_cast<const T*>(v.ptr), v.rows,
+                                                                (int)v.cols, v.rs, v.cs,
+                                                                reinterpret_cast<T*>(vbuf), s_pad, tp, tt);
+  count_launch();
+  FLK_CUDA_TRY(cudaGetLastError());
+  return FLK_OK;
+}
+
+template <typename T>
+static int run_finalize(const SweepPlan& sp, const void* raw, const Mat* add, void* out, int64_t out_rs,
+                        int64_t out_cs, int64_t t, bool padded, cudaStream_t stream) {
+  finalize_kernel<T><<<grid_for(sp.r_pad * sp.tp), 256, 0, stream>>>(
+      reinterpret_cast<const T*>(raw), sp.n_chunks, sp.r_pad, sp.tp, sp.r, (int)t,
+      add ? reinterpret_cast<const T*>(add->ptr) : nullptr, add ? add->rs : 0, add ? add->cs : 0,
+      reinterpret_cast<T*>(out), out_rs, out_cs, padded ? 1 : 0, sp.tt);
+  count_launch();
+  FLK_CUDA_TRY(cudaGetLastError());
+  return FLK_OK;
+}
+
+template <typename T>
+static int run_sweep_simt(int kernel, const SweepPlan& sp, const Operand& a, const Operand& b, int ld,
+                          const void* vec, void* raw, cudaStream_t stream, int sweep_idx) {
+  SimtArgs<T> args;
+  args.A = reinterpret_cast<const T*>(a.xs);
+  args.an = reinterpret_cast<const T*>(a.norms);
+  args.B = reinterpret_cast<const T*>(b.xs);
+  args.bn = reinterpret_cast<const T*>(b.norms);
+  args.vec = reinterpret_cast<const T*>(vec);
+  args.raw = reinterpret_cast<T*>(raw);
+  args.ld = ld;
+  args.tp = sp.tp;
+  args.r_pad = sp.r_pad;
+  args.s_pad = sp.s_pad;
+  args.row_tiles = sp.row_tiles;
+  args.n_col_tiles = sp.n_col_tiles;
+  args.tiles_per_chunk = sp.tiles_per_chunk;
+  FLK_TRY(timer_mark(2 * sweep_idx, stream));
+  FLK_TRY((launch_simt_any<T>(kernel, args, sp.tt, sp.n_chunks, sp.t_chunks, stream)));
+  FLK_TRY(timer_mark(2 * sweep_idx + 1, stream));
+  count_launch();
+  return FLK_OK;
+}
+
+static int run_sweep_tc(int kernel, const SweepPlan& sp, const void* img_a, const void* img_b, int64_t d,
+                        const void* vec, void* raw, void* status, cudaStream_t stream, int sweep_idx) {
+  tc::SweepArgs args;
+  args.img_a = reinterpret_cast<const float*>(img_a);
+  args.img_b = reinterpret_cast<const float*>(img_b);
+  args.vec = reinterpret_cast<const float*>(vec);
+  args.raw = reinterpret_cast<float*>(raw);
+  args.status = reinterpret_cast<int*>(status);
+  args.tp = sp.tp;
+  args.r_pad = sp.r_pad;
+  args.s_pad = sp.s_pad;
+  args.row_tiles = sp.row_tiles;
+  args.n_col_tiles = sp.n_col_tiles;
+  args.tiles_per_chunk = sp.tiles_per_chunk;
+  FLK_TRY(timer_mark(2 * sweep_idx, stream));
+  FLK_TRY(tc::launch_sweep(kernel, (int)d, args, sp.tt, sp.n_chunks, sp.t_chunks, stream));
+  FLK_TRY(timer_mark(2 * sweep_idx + 1, stream));
+  count_launch();
+  return FLK_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// fmmv / fdmmv on device pointers
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+static int fmmv_impl(int dtype, int kernel, const Mat& X1, const Mat& X2, const Mat& v, void* out,
+                     int64_t out_rs, int64_t out_cs, const double* sigma, int64_t sigma_len, void* ws,
+                     int64_t ws_bytes, int flags, cudaStream_t stream) {
+  const int64_t n = X1.rows, m = X2.rows, d = X1.cols, t = v.cols;
+  Layout L = make_layout(ws, false, true, dtype, kernel, n, m, d, t, flags);
+  if ((flags & FLK_FLAG_FORCE_TC) && !L.tc)
+    return fail(FLK_ERR_UNSUPPORTED, "tensor-core kernel does not cover dtype=%d d=%lld", dtype, (long long)d);
+  FLK_TRY(check_workspace(ws, ws_bytes, L.total));
+  if (n == 0 || t == 0) return FLK_OK;
+  T sig_scalar;
+  const T* sig_dev;
+  FLK_TRY(upload_sigma<T>(sigma, sigma_len, L.sigma, &sig_scalar, &sig_dev, stream));
+  FLK_TRY(run_prep_vec<T>(v, L.vbuf, L.s1.s_pad, L.s1.tp, L.s1.tt, stream));
+  if (L.tc) {
+    FLK_CUDA_TRY(cudaMemsetAsync(L.status, 0, 256, stream));
+    FLK_TRY(tc::prep_images(kernel, X1.ptr, X1.rows, X1.rs, X1.cs, (int)d, (const float*)sig_dev,
+                            (float)sig_scalar, (int)sigma_len, L.s1.r_pad, (float*)L.x1.img_a, nullptr, stream));
+    FLK_TRY(tc::prep_images(kernel, X2.ptr, X2.rows, X2.rs, X2.cs, (int)d, (const float*)sig_dev,
+                            (float)sig_scalar, (int)sigma_len, L.s1.s_pad, nullptr, (float*)L.x2.img_b, stream));
+    count_launch(2);
+    FLK_TRY(run_sweep_tc(kernel, L.s1, L.x1.img_a, L.x2.img_b, d, L.vbuf, L.raw1, L.status, stream, 0));
+  } else {
+    const int ld = ld_for(dtype, d);
+    FLK_TRY(run_prep_rows<T>(X1, sig_dev, sig_scalar, (int)sigma_len, L.x1.xs, ld, L.s1.r_pad, L.x1.norms, stream));
+    FLK_TRY(run_prep_rows<T>(X2, sig_dev, sig_scalar, (int)sigma_len, L.x2.xs, ld, L.s1.s_pad, L.x2.norms, stream));
+    FLK_TRY(run_sweep_simt<T>(kernel, L.s1, L.x1, L.x2, ld, L.vbuf, L.raw1, stream, 0));
+  }
+  FLK_TRY(run_finalize<T>(L.s1, L.raw1, nullptr, out, out_rs, out_cs, t, false, stream));
+  return FLK_OK;
+}
+
+template <typename T>
+static int fdmmv_impl(int dtype, int kernel, const Mat& X1, const Mat& X2, const Mat& v, const Mat& w, int64_t t,
+                      void* out, int64_t out_rs, int64_t out_cs, const double* sigma, int64_t sigma_len,
+                      void* ws, int64_t ws_bytes, int flags, cudaStream_t stream) {
+  const int64_t n = X1.rows, m = X2.rows, d = X1.cols;
+  const bool has_v = v.ptr != nullptr, has_w = w.ptr != nullptr;
+  Layout L = make_layout(ws, true, has_v, dtype, kernel, n, m, d, t, flags);
+  if ((flags & FLK_FLAG_FORCE_TC) && !L.tc)
+    return fail(FLK_ERR_UNSUPPORTED, "tensor-core kernel does not cover dtype=%d d=%lld", dtype, (long long)d);
+  FLK_TRY(check_workspace(ws, ws_bytes, L.total));
+  if (m == 0 || t == 0) return FLK_OK;
+  T sig_scalar;
+  const T* sig_dev;
+  FLK_TRY(upload_sigma<T>(sigma, sigma_len, L.sigma, &sig_scalar, &sig_dev, stream));
+  const int ld = ld_for(dtype, d);
+  if (L.tc) {
+    FLK_CUDA_TRY(cudaMemsetAsync(L.status, 0, 256, stream));
+    FLK_TRY(tc::prep_images(kernel, X1.ptr, X1.rows, X1.rs, X1.cs, (int)d, (const float*)sig_dev,
+                            (float)sig_scalar, (int)sigma_len, L.s1.r_pad, (float*)L.x1.img_a,
+                            (float*)L.x1.img_b, stream));
+    FLK_TRY(tc::prep_images(kernel, X2.ptr, X2.rows, X2.rs, X2.cs, (int)d, (const float*)sig_dev,
+                            (float)sig_scalar, (int)sigma_len, L.s1.s_pad, (float*)L.x2.img_a,
+                            (float*)L.x2.img_b, stream));
+    count_launch(2);
+  } else {
+    FLK_TRY(run_prep_rows<T>(X1, sig_dev, sig_scalar, (int)sigma_len, L.x1.xs, ld, L.s1.r_pad, L.x1.norms, stream));
+    FLK_TRY(run_prep_rows<T>(X2, sig_dev, sig_scalar, (int)sigma_len, L.x2.xs, ld, L.s1.s_pad, L.x2.norms, stream));
+  }
+  if (has_v) {
+    // sweep 1: u = K v (+ w), kept as a padded vector operand
+    FLK_TRY(run_prep_vec<T>(v, L.vbuf, L.s1.s_pad, L.s1.tp, L.s1.tt, stream));
+    if (L.tc) {
+      FLK_TRY(run_sweep_tc(kernel, L.s1, L.x1.img_a, L.x2.img_b, d, L.vbuf, L.raw1, L.status, stream, 0));
+    } else {
+      FLK_TRY(run_sweep_simt<T>(kernel, L.s1, L.x1, L.x2, ld, L.vbuf, L.raw1, stream, 0));
+    }
+    FLK_TRY(run_finalize<T>(L.s1, L.raw1, has_w ? &w : nullptr, L.ubuf, 0, 0, t, true, stream));
+  } else {
+    FLK_TRY(run_prep_vec<T>(w, L.ubuf, L.s1.r_pad, L.s1.tp, L.s1.tt, stream));
+  }
+  // sweep 2: out = K^T u  (rows = X2, reduction over X1)
+  if (L.tc) {
+    FLK_TRY(run_sweep_tc(kernel, L.s2, L.x2.img_a, L.x1.img_b, d, L.ubuf, L.raw2, L.status, stream, 1));
+  } else {
+    FLK_TRY(run_sweep_simt<T>(kernel, L.s2, L.x2, L.x1, ld, L.ubuf, L.raw2, stream, 1));
+  }
+  FLK_TRY(run_finalize<T>(L.s2, L.raw2, nullptr, out, out_rs, out_cs, t, false, stream));
+  return FLK_OK;
+}
+
+
+// ---------------------------------------------------------------------------------------------
+// Host-buffer variants: stage dense copies of the operands in the workspace, run, copy back.
+// ---------------------------------------------------------------------------------------------
+struct Staged {
+  Mat dev;          // the device copy, same orientation as the host matrix
+  int64_t bytes;    // bytes reserved in the workspace
+};
+
+// A strided host matrix is copied as the dense block spanned by its unit-stride dimension.
+static Staged plan_stage(const Mat& h, int64_t es, Carver& c) {
+  Staged s;
+  s.dev = h;
+  s.bytes = 0;
+  if (h.ptr == nullptr || h.rows == 0 || h.cols == 0) {
+    s.dev.ptr = nullptr;
+    return s;
+  }
+  s.bytes = h.rows * h.cols * es;
+  s.dev.ptr = c.take(s.bytes);
+  const bool row_major = (h.cs == 1) || (h.rs != 1);
+  if (row_major) {
+    s.dev.rs = h.cols;
+    s.dev.cs = 1;
+  } else {
+    s.dev.rs = 1;
+    s.dev.cs = h.rows;
+  }
+  return s;
+}
+
+static int copy_matrix(const Mat& dst, const Mat& src, int64_t es, cudaMemcpyKind kind, cudaStream_t stream) {
+  if (src.ptr == nullptr || dst.ptr == nullptr || src.rows == 0 || src.cols == 0) return FLK_OK;
+  const bool row_major = (dst.cs == 1 && src.cs == 1);
+  // width = contiguous run, height = number of runs
+  int64_t width, height, spitch, dpitch;
+  if (row_major) {
+    width = src.cols * es;
+    height = src.rows;
+    spitch = (src.rows > 1 ? src.rs : src.cols) * es;
+    dpitch = (dst.rows > 1 ? dst.rs : dst.cols) * es;
+  } else {
+    if (src.rs != 1 || dst.rs != 1) return fail(FLK_ERR_LAYOUT, "internal: orientation mismatch in staged copy");
+    width = src.rows * es;
+    height = src.cols;
+    spitch = (src.cols > 1 ? src.cs : src.rows) * es;
+    dpitch = (dst.cols > 1 ? dst.cs : dst.rows) * es;
+  }
+  if (spitch < width) spitch = width;
+  if (dpitch < width) dpitch = width;
+  if (spitch == width && dpitch == width) {  // fully contiguous on both sides: one linear copy
+    FLK_CUDA_TRY(cudaMemcpyAsync(const_cast<void*>(dst.ptr), src.ptr, (size_t)(width * height), kind, stream));
+    return FLK_OK;
+  }
+  FLK_CUDA_TRY(cudaMemcpy2DAsync(const_cast<void*>(dst.ptr), (size_t)dpitch, src.ptr, (size_t)spitch, (size_t)width,
+                                 (size_t)height, kind, stream));
+  return FLK_OK;
+}
+
+// Reads the tensor-core status word after the stream has drained; non-zero means a bounded wait gave up.
+static int check_tc_status(const void* inner_ws) {
+  int host = 0;
+  FLK_CUDA_TRY(cudaMemcpy(&host, inner_ws, sizeof(int), cudaMemcpyDeviceToHost));
+  if (host != 0) return fail(FLK_ERR_TIMEOUT, "tensor-core kernel gave up waiting on a barrier (status 0x%x)", host);
+  return FLK_OK;
+}
+
+struct HostLayout {
+  Staged x1, x2, v, w, out;
+  void* inner = nullptr;
+  int64_t inner_bytes = 0;
+  int64_t total = 0;
+};
+
+static HostLayout make_host_layout(void* ws, bool dmmv, int dtype, int kernel, const Mat& X1, const Mat& X2,
+                                   const Mat& v, const Mat& w, const Mat& out, int64_t t, int flags) {
+  HostLayout H;
+  const int64_t es = esize(dtype);
+  Carver c(ws);
+  H.x1 = plan_stage(X1, es, c);
+  H.x2 = plan_stage(X2, es, c);
+  H.v = plan_stage(v, es, c);
+  H.w = plan_stage(w, es, c);
+  H.out = plan_stage(out, es, c);
+  H.inner_bytes = make_layout(nullptr, dmmv, v.ptr != nullptr, dtype, kernel, X1.rows, X2.rows, X1.cols, t, flags).total;
+  H.inner = c.take(H.inner_bytes);
+  H.total = c.off;
+  return H;
+}
+
+}  // namespace flk
+
+using namespace flk;
+
+extern "C" {
+
+int flk_version(void) { return 100; }
+
+const char* flk_last_error(void) { return last_error_buf(); }
+
+const char* flk_status_name(int status) {
+  switch (status) {
+    case FLK_OK: return "FLK_OK";
+    case FLK_ERR_BAD_ARG: return "FLK_ERR_BAD_ARG";
+    case FLK_ERR_LAYOUT: return "FLK_ERR_LAYOUT";
+    case FLK_ERR_WORKSPACE: return "FLK_ERR_WORKSPACE";
+    case FLK_ERR_CUDA: return "FLK_ERR_CUDA";
+    case FLK_ERR_UNSUPPORTED: return "FLK_ERR_UNSUPPORTED";
+    case FLK_ERR_DEVICE: return "FLK_ERR_DEVICE";
+    case FLK_ERR_TIMEOUT: return "FLK_ERR_TIMEOUT";
+  }
+  return "FLK_UNKNOWN";
+}
+
+int flk_check_device(void) {
+  int dev = 0;
+  FLK_CUDA_TRY(cudaGetDevice(&dev));
+  int major = 0, minor = 0;
+  FLK_CUDA_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+  FLK_CUDA_TRY(cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev));
+  if (major != 10) return fail(FLK_ERR_DEVICE, "device %d has compute capability %d.%d; sm_100 required", dev, major, minor);
+  return FLK_OK;
+}
+
+int flk_uses_tensor_cores(int dtype, int kernel, int64_t d, int64_t t, int flags) {
+  return tc_eligible(dtype, kernel, d, t, flags) ? 1 : 0;
+}
+
+int64_t flk_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int flk_square_norm(int dtype, const void* X, int64_t n, int64_t d, int64_t x_rs, int64_t x_cs,
+                    const double* sigma_host, int64_t sigma_len, void* out, void* stream) {
+  FLK_TRY(check_common(dtype, FLK_GAUSSIAN, n, 0, d, 0));
+  Mat mx{X, n, d, x_rs, x_cs};
+  FLK_TRY(check_mat("X", mx, false));
+  if (out == nullptr) return fail(FLK_ERR_BAD_ARG, "out: null pointer");
+  if (sigma_host != nullptr && sigma_len != 1 && sigma_len != d)
+    return fail(FLK_ERR_BAD_ARG, "sigma must have 1 or d entries");
+  if (sigma_host != nullptr && sigma_len != 1)
+    return fail(FLK_ERR_UNSUPPORTED, "flk_square_norm takes a scalar sigma only (no workspace to stage a vector)");
+  if (n == 0) return FLK_OK;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  int blocks = (int)ceil_div(n, kPrepRows);
+  if (dtype == FLK_F32) {
+    float s = sigma_host ? (float)sigma_host[0] : 1.0f;
+    norm_rows_kernel<float><<<blocks, 256, 0, st>>>((const float*)X, n, (int)d, x_rs, x_cs, s, (float*)out);
+  } else {
+    double s = sigma_host ? sigma_host[0] : 1.0;
+    norm_rows_kernel<double><<<blocks, 256, 0, st>>>((const double*)X, n, (int)d, x_rs, x_cs, s, (double*)out);
+  }
+  count_launch();
+  FLK_CUDA_TRY(cudaGetLastError());
+  return FLK_OK;
+}
+
+int64_t flk_fmmv_workspace_bytes(int dtype, int kernel, int64_t n, int64_t m, int64_t d, int64_t t, int flags) {
+  int s = check_common(dtype, kernel, n, m, d, t);
+  if (s != FLK_OK) return s;
+  return make_layout(nullptr, false, true, dtype, kernel, n, m, d, t, flags).total;
+}
+
+int64_t flk_fdmmv_workspace_bytes(int dtype, int kernel, int64_t n, int64_t m, int64_t d, int64_t t, int flags) {
+  int s = check_common(dtype, kernel, n, m, d, t);
+  if (s != FLK_OK) return s;
+  return make_layout(nullptr, true, true, dtype, kernel, n, m, d, t, flags).total;
+}
+
+int flk_fmmv(int dtype, int kernel, const void* X1, int64_t n, int64_t x1_rs, int64_t x1_cs, const void* X2,
+             int64_t m, int64_t x2_rs, int64_t x2_cs, int64_t d, const void* v, int64_t t, int64_t v_rs,
+             int64_t v_cs, void* out, int64_t out_rs, int64_t out_cs, const double* sigma_host,
+             int64_t sigma_len, void* workspace, int64_t workspace_bytes, int flags, void* stream) {
+  FLK_TRY(check_common(dtype, kernel, n, m, d, t));
+  Mat a{X1, n, d, x1_rs, x1_cs}, b{X2, m, d, x2_rs, x2_cs}, vv{v, m, t, v_rs, v_cs}, oo{out, n, t, out_rs, out_cs};
+  FLK_TRY(check_mat("X1", a, n == 0));
+  FLK_TRY(check_mat("X2", b, m == 0));
+  FLK_TRY(check_mat("v", vv, m == 0 || t == 0));
+  FLK_TRY(check_mat("out", oo, n == 0 || t == 0));
+  FLK_TRY(check_sigma(sigma_host, sigma_len, d));
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == FLK_F32)
+    return fmmv_impl<float>(dtype, kernel, a, b, vv, out, out_rs, out_cs, sigma_host, sigma_len, workspace,
+                            workspace_bytes, flags, st);
+  return fmmv_impl<double>(dtype, kernel, a, b, vv, out, out_rs, out_cs, sigma_host, sigma_len, workspace,
+                           workspace_bytes, flags, st);
+}
+
+int flk_fdmmv(int dtype, int kernel, const void* X1, int64_t n, int64_t x1_rs, int64_t x1_cs, const void* X2,
+              int64_t m, int64_t x2_rs, int64_t x2_cs, int64_t d, const void* v, int64_t v_rs, int64_t v_cs,
+              const void* w, int64_t w_rs, int64_t w_cs, int64_t t, void* out, int64_t out_rs, int64_t out_cs,
+              const double* sigma_host, int64_t sigma_len, void* workspace, int64_t workspace_bytes, int flags,
+              void* stream) {
+  FLK_TRY(check_common(dtype, kernel, n, m, d, t));
+  if (v == nullptr && w == nullptr) return fail(FLK_ERR_BAD_ARG, "One of v and w must be specified to run fdMMV.");
+  Mat a{X1, n, d, x1_rs, x1_cs}, b{X2, m, d, x2_rs, x2_cs}, vv{v, m, t, v_rs, v_cs}, ww{w, n, t, w_rs, w_cs},
+      oo{out, m, t, out_rs, out_cs};
+  FLK_TRY(check_mat("X1", a, n == 0));
+  FLK_TRY(check_mat("X2", b, m == 0));
+  FLK_TRY(check_mat("v", vv, true));
+  FLK_TRY(check_mat("w", ww, true));
+  FLK_TRY(check_mat("out", oo, m == 0 || t == 0));
+  FLK_TRY(check_sigma(sigma_host, sigma_len, d));
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == FLK_F32)
+    return fdmmv_impl<float>(dtype, kernel, a, b, vv, ww, t, out, out_rs, out_cs, sigma_host, sigma_len, workspace,
+                             workspace_bytes, flags, st);
+  return fdmmv_impl<double>(dtype, kernel, a, b, vv, ww, t, out, out_rs, out_cs, sigma_host, sigma_len, workspace,
+                            workspace_bytes, flags, st);
+}
+
+
+int64_t flk_fmmv_host_workspace_bytes(int dtype, int kernel, int64_t n, int64_t m, int64_t d, int64_t t, int flags) {
+  int s = check_common(dtype, kernel, n, m, d, t);
+  if (s != FLK_OK) return s;
+  int dummy = 0;
+  Mat a{&dummy, n, d, d, 1}, b{&dummy, m, d, d, 1}, vv{&dummy, m, t, t, 1}, ww{nullptr, 0, 0, 0, 0},
+      oo{&dummy, n, t, t, 1};
+  return make_host_layout(nullptr, false, dtype, kernel, a, b, vv, ww, oo, t, flags).total;
+}
+
+int64_t flk_fdmmv_host_workspace_bytes(int dtype, int kernel, int64_t n, int64_t m, int64_t d, int64_t t, int flags) {
+  int s = check_common(dtype, kernel, n, m, d, t);
+  if (s != FLK_OK) return s;
+  int dummy = 0;
+  Mat a{&dummy, n, d, d, 1}, b{&dummy, m, d, d, 1}, vv{&dummy, m, t, t, 1}, ww{&dummy, n, t, t, 1},
+      oo{&dummy, m, t, t, 1};
+  return make_host_layout(nullptr, true, dtype, kernel, a, b, vv, ww, oo, t, flags).total;
+}
+
+int flk_fmmv_host(int dtype, int kernel, const void* X1, int64_t n, int64_t x1_rs, int64_t x1_cs, const void* X2,
+                  int64_t m, int64_t x2_rs, int64_t x2_cs, int64_t d, const void* v, int64_t t, int64_t v_rs,
+                  int64_t v_cs, void* out, int64_t out_rs, int64_t out_cs, const double* sigma_host,
+                  int64_t sigma_len, void* workspace, int64_t workspace_bytes, int flags, void* stream) {
+  FLK_TRY(check_common(dtype, kernel, n, m, d, t));
+  Mat a{X1, n, d, x1_rs, x1_cs}, b{X2, m, d, x2_rs, x2_cs}, vv{v, m, t, v_rs, v_cs}, ww{nullptr, 0, 0, 0, 0},
+      oo{out, n, t, out_rs, out_cs};
+  FLK_TRY(check_mat("X1", a, n == 0));
+  FLK_TRY(check_mat("X2", b, m == 0));
+  FLK_TRY(check_mat("v", vv, m == 0 || t == 0));
+  FLK_TRY(check_mat("out", oo, n == 0 || t == 0));
+  FLK_TRY(check_sigma(sigma_host, sigma_len, d));
+  HostLayout H = make_host_layout(workspace, false, dtype, kernel, a, b, vv, ww, oo, t, flags);
+  FLK_TRY(check_workspace(workspace, workspace_bytes, H.total));
+  if (n == 0 || t == 0) return FLK_OK;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int64_t es = esize(dtype);
+  FLK_TRY(copy_matrix(H.x1.dev, a, es, cudaMemcpyHostToDevice, st));
+  FLK_TRY(copy_matrix(H.x2.dev, b, es, cudaMemcpyHostToDevice, st));
+  FLK_TRY(copy_matrix(H.v.dev, vv, es, cudaMemcpyHostToDevice, st));
+  FLK_TRY(flk_fmmv(dtype, kernel, H.x1.dev.ptr, n, H.x1.dev.rs, H.x1.dev.cs, H.x2.dev.ptr, m, H.x2.dev.rs,
+                   H.x2.dev.cs, d, H.v.dev.ptr, t, H.v.dev.rs, H.v.dev.cs, const_cast<void*>(H.out.dev.ptr),
+                   H.out.dev.rs, H.out.dev.cs, sigma_host, sigma_len, H.inner, H.inner_bytes, flags, stream));
+  FLK_TRY(copy_matrix(oo, H.out.dev, es, cudaMemcpyDeviceToHost, st));
+  FLK_CUDA_TRY(cudaStreamSynchronize(st));
+  if (tc_eligible(dtype, kernel, d, t, flags)) FLK_TRY(check_tc_status(H.inner));
+  return FLK_OK;
+}
+
+int flk_fdmmv_host(int dtype, int kernel, const void* X1, int64_t n, int64_t x1_rs, int64_t x1_cs, const void* X2,
+                   int64_t m, int64_t x2_rs, int64_t x2_cs, int64_t d, const void* v, int64_t v_rs, int64_t v_cs,
+                   const void* w, int64_t w_rs, int64_t w_cs, int64_t t, void* out, int64_t out_rs, int64_t out_cs,
+                   const double* sigma_host, int64_t sigma_len, void* workspace, int64_t workspace_bytes, int flags,
+                   void* stream) {
+  FLK_TRY(check_common(dtype, kernel, n, m, d, t));
+  if (v == nullptr && w == nullptr) return fail(FLK_ERR_BAD_ARG, "One of v and w must be specified to run fdMMV.");
+  Mat a{X1, n, d, x1_rs, x1_cs}, b{X2, m, d, x2_rs, x2_cs}, vv{v, m, t, v_rs, v_cs}, ww{w, n, t, w_rs, w_cs},
+      oo{out, m, t, out_rs, out_cs};
+  FLK_TRY(check_mat("X1", a, n == 0));
+  FLK_TRY(check_mat("X2", b, m == 0));
+  FLK_TRY(check_mat("v", vv, true));
+  FLK_TRY(check_mat("w", ww, true));
+  FLK_TRY(check_mat("out", oo, m == 0 || t == 0));
+  FLK_TRY(check_sigma(sigma_host, sigma_len, d));
+  HostLayout H = make_host_layout(workspace, true, dtype, kernel, a, b, vv, ww, oo, t, flags);
+  FLK_TRY(check_workspace(workspace, workspace_bytes, H.total));
+  if (m == 0 || t == 0) return FLK_OK;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int64_t es = esize(dtype);
+  FLK_TRY(copy_matrix(H.x1.dev, a, es, cudaMemcpyHostToDevice, st));
+  FLK_TRY(copy_matrix(H.x2.dev, b, es, cudaMemcpyHostToDevice, st));
+  FLK_TRY(copy_matrix(H.v.dev, vv, es, cudaMemcpyHostToDevice, st));
+  FLK_TRY(copy_matrix(H.w.dev, ww, es, cudaMemcpyHostToDevice, st));
+  FLK_TRY(flk_fdmmv(dtype, kernel, H.x1.dev.ptr, n, H.x1.dev.rs, H.x1.dev.cs, H.x2.dev.ptr, m, H.x2.dev.rs,
+                    H.x2.dev.cs, d, H.v.dev.ptr, H.v.dev.rs, H.v.dev.cs, H.w.dev.ptr, H.w.dev.rs, H.w.dev.cs, t,
+                    const_cast<void*>(H.out.dev.ptr), H.out.dev.rs, H.out.dev.cs, sigma_host, sigma_len, H.inner,
+                    H.inner_bytes, flags, stream));
+  FLK_TRY(copy_matrix(oo, H.out.dev, es, cudaMemcpyDeviceToHost, st));
+  FLK_CUDA_TRY(cudaStreamSynchronize(st));
+  if (tc_eligible(dtype, kernel, d, t, flags)) FLK_TRY(check_tc_status(H.inner));
+  return FLK_OK;
+}
+
+int flk_set_timing(int enable) {
+  g_timer.enabled = enable != 0;
+  g_timer.valid[0] = g_timer.valid[1] = false;
+  return FLK_OK;
+}
+
+int flk_get_sweep_ms(float* sweep1_ms, float* sweep2_ms) {
+  if (sweep1_ms == nullptr || sweep2_ms == nullptr) return fail(FLK_ERR_BAD_ARG, "null pointer");
+  *sweep1_ms = -1.0f;
+  *sweep2_ms = -1.0f;
+  if (g_timer.valid[0]) {
+    FLK_CUDA_TRY(cudaEventSynchronize(g_timer.ev[1]));
+    FLK_CUDA_TRY(cudaEventElapsedTime(sweep1_ms, g_timer.ev[0], g_timer.ev[1]));
+  }
+  if (g_timer.valid[1]) {
+    FLK_CUDA_TRY(cudaEventSynchronize(g_timer.ev[3]));
+    FLK_CUDA_TRY(cudaEventElapsedTime(sweep2_ms, g_timer.ev[2], g_timer.ev[3]));
+  }
+  return FLK_OK;
+}
+
+int flk_tc_status(const void* workspace, void* stream, int* status_out) {
+  if (workspace == nullptr || status_out == nullptr) return fail(FLK_ERR_BAD_ARG, "null pointer");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  int host[4] = {0, 0, 0, 0};
+  FLK_CUDA_TRY(cudaMemcpyAsync(host, workspace, sizeof(host), cudaMemcpyDeviceToHost, st));
+  FLK_CUDA_TRY(cudaStreamSynchronize(st));
+  *status_out = host[0];
+  return FLK_OK;
+}
+
+}  // extern "C"

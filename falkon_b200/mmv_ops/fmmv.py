@@ -1,0 +1,158 @@
+"""``fmmv`` and ``fdmmv``: implicit kernel-matrix / vector products on the B200.
+
+Drop-in for the functions of the same name in the reference (falkon/mmv_ops/fmmv.py:960-973 and
+:976-1131): same positional / keyword signatures, same output-allocation rules, same exception
+types.  Where the reference loops over row blocks, materialises each n_blk x m kernel block in
+device memory and calls cuBLAS twice, these functions make one call into the C ABI of
+``libfalkon_b200`` (include/falkon_b200.h), whose CUDA kernels keep the block in registers /
+tensor memory.  There is no CPU path: ``use_cpu=True`` or a missing GPU raises.
+"""
+from typing import Dict, Optional
+
+import torch
+
+from .. import _lib
+from ..options import BaseOptions
+from .utils import check_contiguity, create_output_mat
+
+__all__ = ("fmmv", "fdmmv")
+
+
+def _kernel_spec(kernel):
+    """(kernel id for the C ABI, sigma as fp64 numpy vector) of a distance-kernel object."""
+    spec = getattr(kernel, "_flk_spec", None)
+    if spec is None:
+        raise NotImplementedError(
+            f"falkon_b200 computes kernel-vector products for Gaussian, Laplacian and Matern kernels; "
+            f"{type(kernel).__name__} does not describe itself to the CUDA library (no _flk_spec)."
+        )
+    return spec()
+
+
+def _require_cuda(opt: Optional[BaseOptions], *tensors):
+    if opt is not None and getattr(opt, "use_cpu", False):
+        raise RuntimeError(
+            "falkon_b200 has no CPU implementation of the kernel-vector products (use_cpu=True was requested). "
+            "Use the reference package for CPU execution."
+        )
+    if not torch.cuda.is_available():
+        raise RuntimeError("falkon_b200 needs a CUDA device (B200, sm_100); none is available.")
+
+
+def _is_sparse(*xs):
+    return any(type(x).__name__ == "SparseTensor" or (isinstance(x, torch.Tensor) and x.is_sparse) for x in xs)
+
+
+def _flags(opt) -> int:
+    return int(getattr(opt, "flk_flags", 0) or 0)
+
+
+def _pick_device(devs):
+    cuda = [d for d in devs if d.type == "cuda"]
+    if cuda:
+        if any(d != cuda[0] for d in cuda):
+            raise RuntimeError("All CUDA input arguments must be on the same device")
+        return cuda[0]
+    return torch.device("cuda", torch.cuda.current_device())
+
+
+def _to_dev(t, dev):
+    return None if t is None else (t if t.device == dev else t.to(dev, non_blocking=True))
+
+
+def fmmv(
+    X1: torch.Tensor,
+    X2: torch.Tensor,
+    v: torch.Tensor,
+    kernel,
+    out: Optional[torch.Tensor] = None,
+    opt: Optional[BaseOptions] = None,
+    kwargs_m1: Optional[Dict[str, torch.Tensor]] = None,
+    kwargs_m2: Optional[Dict[str, torch.Tensor]] = None,
+) -> torch.Tensor:
+    """``k(X1, X2) @ v`` -> (n x t).  Signature of falkon/mmv_ops/fmmv.py:960-969."""
+    if _is_sparse(X1, X2):
+        raise NotImplementedError("Sparse kernel-vector products are not implemented by falkon_b200.")
+    if kwargs_m1 or kwargs_m2:
+        raise NotImplementedError("Distance kernels take no per-row keyword tensors (kwargs_m1 / kwargs_m2).")
+    kernel_id, sigma = _kernel_spec(kernel)
+    params = list(getattr(kernel, "diff_params", {}).values())
+    if torch.is_grad_enabled() and any(t.requires_grad for t in [X1, X2, v] + params):
+        raise NotImplementedError(
+            "falkon_b200 does not implement the backward pass of the kernel-vector product; "
+            "call it under torch.no_grad() / inference_mode() or detach the inputs."
+        )
+    check_contiguity((X1, "X1"), (X2, "X2"), (v, "v"), (out, "out"))
+    _require_cuda(opt, X1, X2, v)
+    if v.dim() == 1:
+        v = v.reshape(-1, 1)
+    data_devs = (X1.device, X2.device, v.device)
+    n, t = X1.shape[0], v.shape[1]
+    with torch.inference_mode():
+        out = create_output_mat(out, data_devs, (n, t), v.dtype, "cuda", X1)
+        dev = _pick_device(data_devs + (out.device,))
+        all_host = all(d.type == "cpu" for d in data_devs) and out.device.type == "cpu"
+        if all_host:
+            _lib.call_fmmv(kernel_id, sigma, X1, X2, v, out, flags=_flags(opt), host=True, device=dev)
+        else:
+            o_dev = out if out.device == dev else torch.empty(out.shape, dtype=out.dtype, device=dev)
+            _lib.call_fmmv(kernel_id, sigma, _to_dev(X1, dev), _to_dev(X2, dev), _to_dev(v, dev), o_dev,
+                           flags=_flags(opt))
+            if o_dev is not out:
+                out.copy_(o_dev)
+    return out
+
+
+def fdmmv(
+    X1: torch.Tensor,
+    X2: torch.Tensor,
+    v: Optional[torch.Tensor],
+    w: Optional[torch.Tensor],
+    kernel,
+    out: Optional[torch.Tensor] = None,
+    differentiable: bool = False,
+    opt: Optional[BaseOptions] = None,
+    kwargs_m1: Optional[Dict[str, torch.Tensor]] = None,
+    kwargs_m2: Optional[Dict[str, torch.Tensor]] = None,
+) -> torch.Tensor:
+    """``k(X1, X2)^T (k(X1, X2) v + w)`` -> (m x t).  Signature of falkon/mmv_ops/fmmv.py:976-987
+    (also called positionally as ``(X1, X2, v, w, kernel, out, differentiable, opt)``,
+    falkon/kernels/diff_kernel.py:145)."""
+    if differentiable:
+        raise NotImplementedError(
+            "Manual D-MMV is not implemented for differentiable inputs. Try using the KeOps version instead."
+        )
+    if _is_sparse(X1, X2):
+        raise NotImplementedError("Sparse kernel-vector products are not implemented by falkon_b200.")
+    if kwargs_m1 or kwargs_m2:
+        raise NotImplementedError("Distance kernels take no per-row keyword tensors (kwargs_m1 / kwargs_m2).")
+    if v is None and w is None:
+        raise ValueError("One of v and w must be specified to run fdMMV.")
+    kernel_id, sigma = _kernel_spec(kernel)
+    check_contiguity((X1, "X1"), (X2, "X2"), (v, "v"), (w, "w"), (out, "out"))
+    _require_cuda(opt, X1, X2)
+    if v is not None and v.dim() == 1:
+        v = v.reshape(-1, 1)
+    if w is not None and w.dim() == 1:
+        w = w.reshape(-1, 1)
+    data_devs = [X1.device, X2.device]
+    if v is not None:
+        data_devs.append(v.device)
+    if w is not None:
+        data_devs.append(w.device)
+    m = X2.shape[0]
+    t = v.shape[1] if v is not None else w.shape[1]
+    dtype = v.dtype if v is not None else w.dtype
+    with torch.inference_mode():
+        out = create_output_mat(out, data_devs, (m, t), dtype, "cuda", X1)
+        dev = _pick_device(tuple(data_devs) + (out.device,))
+        all_host = all(d.type == "cpu" for d in data_devs) and out.device.type == "cpu"
+        if all_host:
+            _lib.call_fdmmv(kernel_id, sigma, X1, X2, v, w, out, flags=_flags(opt), host=True, device=dev)
+        else:
+            o_dev = out if out.device == dev else torch.empty(out.shape, dtype=out.dtype, device=dev)
+            _lib.call_fdmmv(kernel_id, sigma, _to_dev(X1, dev), _to_dev(X2, dev), _to_dev(v, dev),
+                            _to_dev(w, dev), o_dev, flags=_flags(opt))
+            if o_dev is not out:
+                out.copy_(o_dev)
+    return out

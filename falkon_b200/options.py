@@ -1,0 +1,111 @@
+"""Option dataclasses of the operator API.
+
+Field names and defaults are those of the reference's option classes
+(falkon/options.py:164-303: BaseOptions :168-181, KeopsOptions :205-208,
+ConjugateGradientOptions :223-227, PreconditionerOptions :257-259, CholeskyOptions :281-283),
+so option objects written for the reference configure this package unchanged and
+``dataclasses.replace(kernel.params, **dataclasses.asdict(opt))`` (falkon/kernels/kernel.py:283-285)
+keeps working.  On the kernel-vector-product path most of them have nothing left to control:
+no n x m block is ever allocated, so the memory budgets are accepted and ignored, and KeOps is
+never consulted.  ``use_cpu=True`` is rejected by the products (there is no CPU path here).
+"""
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+__all__ = (
+    "BaseOptions",
+    "KeopsOptions",
+    "ConjugateGradientOptions",
+    "PreconditionerOptions",
+    "CholeskyOptions",
+    "FalkonOptions",
+)
+
+
+@dataclass
+class BaseOptions:
+    debug: bool = False
+    use_cpu: bool = False
+    max_gpu_mem: float = np.inf
+    max_cpu_mem: float = np.inf
+    compute_arch_speed: bool = False
+    no_single_kernel: bool = True
+    min_cuda_pc_size_32: int = 10000
+    min_cuda_pc_size_64: int = 30000
+    min_cuda_iter_size_32: int = 10_000 * 10 * 3_000
+    min_cuda_iter_size_64: int = 30_000 * 10 * 3_000
+    never_store_kernel: bool = False
+    store_kernel_d_threshold: int = 1200
+    num_fmm_streams: int = 2
+    memory_slack: float = 0.9
+
+    def get_base_options(self):
+        return BaseOptions(**{f: getattr(self, f) for f in BaseOptions.__dataclass_fields__})
+
+
+@dataclass
+class KeopsOptions:
+    keops_acc_dtype: str = "auto"
+    keops_sum_scheme: str = "auto"
+    keops_active: str = "auto"
+    keops_memory_slack: float = 0.7
+
+    def get_keops_options(self):
+        return KeopsOptions(**{f: getattr(self, f) for f in KeopsOptions.__dataclass_fields__})
+
+
+@dataclass
+class ConjugateGradientOptions:
+    cg_epsilon_32: float = 1e-7
+    cg_epsilon_64: float = 1e-15
+    cg_tolerance: float = 1e-7
+    cg_full_gradient_every: int = 10
+    cg_differential_convergence: bool = False
+
+    def cg_epsilon(self, dtype):
+        if dtype == torch.float32:
+            return self.cg_epsilon_32
+        if dtype == torch.float64:
+            return self.cg_epsilon_64
+        raise TypeError(f"Data-type {str(dtype)} invalid")
+
+    def get_conjgrad_options(self):
+        return ConjugateGradientOptions(
+            **{f: getattr(self, f) for f in ConjugateGradientOptions.__dataclass_fields__}
+        )
+
+
+@dataclass
+class PreconditionerOptions:
+    pc_epsilon_32: float = 1e-5
+    pc_epsilon_64: float = 1e-13
+    cpu_preconditioner: bool = False
+
+    def pc_epsilon(self, dtype):
+        if dtype == torch.float32:
+            return self.pc_epsilon_32
+        if dtype == torch.float64:
+            return self.pc_epsilon_64
+        raise TypeError(f"Data-type {str(dtype)} invalid")
+
+    def get_pc_options(self):
+        return PreconditionerOptions(**{f: getattr(self, f) for f in PreconditionerOptions.__dataclass_fields__})
+
+
+@dataclass(frozen=False)
+class CholeskyOptions:
+    chol_force_in_core: bool = False
+    chol_force_ooc: bool = False
+    chol_par_blk_multiplier: int = 2
+
+    def get_chol_options(self):
+        return CholeskyOptions(**{f: getattr(self, f) for f in CholeskyOptions.__dataclass_fields__})
+
+
+@dataclass()
+class FalkonOptions(BaseOptions, ConjugateGradientOptions, PreconditionerOptions, CholeskyOptions, KeopsOptions):
+    """Global options; the union of all option groups (falkon/options.py:293-303)."""
+
+    pass

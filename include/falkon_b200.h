@@ -1,0 +1,182 @@
+/*
+ * falkon_b200 -- C ABI of the B200 (sm_100a) kernel-vector-product library.
+ *
+ * This is the drop-in boundary for Falkon's implicit kernel-matrix products.  In the reference
+ * these products are Python loops over torch ops plus one native operator (falkon::square_norm);
+ * the entry points below are what a binding for this path replaces them with.  Every function
+ *   - takes plain pointers, sizes and element strides (no torch types),
+ *   - returns FLK_OK (0) or a negative flk_status and never throws, aborts or traps,
+ *   - allocates nothing: scratch memory is a caller-provided device workspace whose size comes
+ *     from the matching *_workspace_bytes query,
+ *   - enqueues its work on the given CUDA stream and returns without synchronising, unless its
+ *     description says otherwise (the *_host variants synchronise before returning).
+ *
+ * Matrices are 2-D, described by (pointer, rows, row_stride, col_stride) with strides in
+ * elements; one of the two strides must be 1 (C order or Fortran order), as the reference
+ * requires (falkon/mmv_ops/utils.py:36-39, falkon/utils/tensor_helpers.py:210-213).
+ * X1 is n x d, X2 is m x d, v is m x t, w is n x t.
+ *
+ * The length-scale `sigma` is a HOST array of doubles of length 1 or d, the form in which the
+ * reference keeps it (an fp64 parameter, falkon/kernels/distance_kernel.py:20-38); it is cast to
+ * the data type per call exactly as the reference does (distance_kernel.py:148).
+ */
+#ifndef FALKON_B200_H
+#define FALKON_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum flk_status {
+  FLK_OK = 0,
+  FLK_ERR_BAD_ARG = -1,      /* null pointer, negative size, unknown enum value            */
+  FLK_ERR_LAYOUT = -2,       /* neither stride is 1, or a stride is too small / misaligned  */
+  FLK_ERR_WORKSPACE = -3,    /* workspace missing, misaligned or smaller than required      */
+  FLK_ERR_CUDA = -4,         /* a CUDA runtime call failed; see flk_last_error()            */
+  FLK_ERR_UNSUPPORTED = -5,  /* valid request outside what this build implements            */
+  FLK_ERR_DEVICE = -6,       /* the current device is not an sm_100 (B200-class) GPU        */
+  FLK_ERR_TIMEOUT = -7       /* a bounded device-side wait gave up (tensor-core kernel)     */
+} flk_status;
+
+typedef enum flk_dtype { FLK_F32 = 0, FLK_F64 = 1 } flk_dtype;
+
+/* Matern with nu = 0.5 is FLK_LAPLACIAN and nu = inf is FLK_GAUSSIAN, as in
+ * falkon/kernels/distance_kernel.py:235-238. */
+typedef enum flk_kernel {
+  FLK_GAUSSIAN = 0,
+  FLK_LAPLACIAN = 1,
+  FLK_MATERN15 = 2,
+  FLK_MATERN25 = 3
+} flk_kernel;
+
+/* Bits of the `flags` argument. */
+#define FLK_FLAG_FORCE_SIMT 1 /* never use the tensor-core kernel (diagnostics / comparison) */
+#define FLK_FLAG_FORCE_TC 2   /* fail with FLK_ERR_UNSUPPORTED instead of using the SIMT kernel */
+
+/* Library version (major * 10000 + minor * 100 + patch). */
+int flk_version(void);
+
+/* Message describing the last failure on the calling thread (empty string if none). */
+const char* flk_last_error(void);
+
+/* Name of a status code. */
+const char* flk_status_name(int status);
+
+/* FLK_OK when the current CUDA device can run this library (compute capability 10.x). */
+int flk_check_device(void);
+
+/* 1 when the tensor-core (tcgen05) kernel serves this problem, 0 when the SIMT kernel does. */
+int flk_uses_tensor_cores(int dtype, int kernel, int64_t d, int64_t t, int flags);
+
+/*
+ * Row-wise squared norms of X / sigma:  out[i] = sum_k (X[i,k] / sigma[k])^2 , out has n entries.
+ * Replaces falkon::square_norm as the distance kernels call it
+ * (falkon/c_ext/ops/square_norm.cpp:23-26; call sites falkon/kernels/distance_kernel.py:153-154).
+ * sigma may be NULL (no scaling).  Needs no workspace.
+ */
+int flk_square_norm(int dtype, const void* X, int64_t n, int64_t d, int64_t x_rs, int64_t x_cs,
+                    const double* sigma_host, int64_t sigma_len, void* out, void* stream);
+
+/* Device workspace needed by flk_fmmv for these sizes, in bytes (negative flk_status on error). */
+int64_t flk_fmmv_workspace_bytes(int dtype, int kernel, int64_t n, int64_t m, int64_t d, int64_t t,
+                                 int flags);
+
+/*
+ * out[n x t] = k(X1, X2) v                                   (all pointers are DEVICE pointers)
+ * Replaces fmmv / KernelMmvFnFull.forward / mmv_run_thread
+ * (falkon/mmv_ops/fmmv.py:960-973, :887-932, :309-402) for dense inputs.  The n x m kernel block
+ * is never written to memory.  Either of n, m may be the large dimension: with n small and m
+ * large this is the reduction over data rows that the CG right-hand side needs
+ * (falkon/optim/conjgrad.py:296).
+ */
+int flk_fmmv(int dtype, int kernel,
+             const void* X1, int64_t n, int64_t x1_rs, int64_t x1_cs,
+             const void* X2, int64_t m, int64_t x2_rs, int64_t x2_cs,
+             int64_t d,
+             const void* v, int64_t t, int64_t v_rs, int64_t v_cs,
+             void* out, int64_t out_rs, int64_t out_cs,
+             const double* sigma_host, int64_t sigma_len,
+             void* workspace, int64_t workspace_bytes, int flags, void* stream);
+
+/* Device workspace needed by flk_fdmmv for these sizes, in bytes (negative flk_status on error). */
+int64_t flk_fdmmv_workspace_bytes(int dtype, int kernel, int64_t n, int64_t m, int64_t d, int64_t t,
+                                  int flags);
+
+/*
+ * out[m x t] = k(X1, X2)^T ( k(X1, X2) v + w )               (all pointers are DEVICE pointers)
+ * Replaces fdmmv / dmmv_run_thread (falkon/mmv_ops/fmmv.py:976-1131, :683-767) for dense inputs.
+ * w may be NULL (treated as zero, fmmv.py:753); v may be NULL (out = k^T w, the contract of
+ * falkon/kernels/kernel.py:350-353); at least one of them must be given.
+ */
+int flk_fdmmv(int dtype, int kernel,
+              const void* X1, int64_t n, int64_t x1_rs, int64_t x1_cs,
+              const void* X2, int64_t m, int64_t x2_rs, int64_t x2_cs,
+              int64_t d,
+              const void* v, int64_t v_rs, int64_t v_cs,
+              const void* w, int64_t w_rs, int64_t w_cs,
+              int64_t t,
+              void* out, int64_t out_rs, int64_t out_cs,
+              const double* sigma_host, int64_t sigma_len,
+              void* workspace, int64_t workspace_bytes, int flags, void* stream);
+
+/*
+ * Host-buffer variants: X1, X2, v, w and out are HOST pointers (pinned memory gives asynchronous
+ * copies; pageable memory works too).  The inputs are staged into the device workspace, the
+ * device entry point above runs, and the result is copied back; the call returns after the
+ * stream has been synchronised, so `out` is valid on return.  This is the reference's
+ * "data on the CPU, compute on the GPU" case (falkon/mmv_ops/fmmv.py:798-854, :1080-1125)
+ * for one GPU.  The workspace must hold flk_*_host_workspace_bytes bytes of DEVICE memory.
+ */
+int64_t flk_fmmv_host_workspace_bytes(int dtype, int kernel, int64_t n, int64_t m, int64_t d,
+                                      int64_t t, int flags);
+int flk_fmmv_host(int dtype, int kernel,
+                  const void* X1, int64_t n, int64_t x1_rs, int64_t x1_cs,
+                  const void* X2, int64_t m, int64_t x2_rs, int64_t x2_cs,
+                  int64_t d,
+                  const void* v, int64_t t, int64_t v_rs, int64_t v_cs,
+                  void* out, int64_t out_rs, int64_t out_cs,
+                  const double* sigma_host, int64_t sigma_len,
+                  void* workspace, int64_t workspace_bytes, int flags, void* stream);
+
+int64_t flk_fdmmv_host_workspace_bytes(int dtype, int kernel, int64_t n, int64_t m, int64_t d,
+                                       int64_t t, int flags);
+int flk_fdmmv_host(int dtype, int kernel,
+                   const void* X1, int64_t n, int64_t x1_rs, int64_t x1_cs,
+                   const void* X2, int64_t m, int64_t x2_rs, int64_t x2_cs,
+                   int64_t d,
+                   const void* v, int64_t v_rs, int64_t v_cs,
+                   const void* w, int64_t w_rs, int64_t w_cs,
+                   int64_t t,
+                   void* out, int64_t out_rs, int64_t out_cs,
+                   const double* sigma_host, int64_t sigma_len,
+                   void* workspace, int64_t workspace_bytes, int flags, void* stream);
+
+/*
+ * Counters for the calling process: number of kernels this library has launched and the status
+ * word of the last tensor-core launch read back by flk_tc_status (0 = clean).
+ */
+int64_t flk_launch_count(void);
+
+/*
+ * Optional timing of the dominant kernels, for benchmarking.  After flk_set_timing(1) every
+ * fmmv / fdmmv call records CUDA events on its stream around its first sweep (K v) and, for
+ * fdmmv, its second sweep (K^T u).  flk_get_sweep_ms waits for those events and returns the two
+ * durations of the most recent call in milliseconds (-1 where no such sweep ran).  One set of
+ * events per process: not for concurrent use from several threads.
+ */
+int flk_set_timing(int enable);
+int flk_get_sweep_ms(float* sweep1_ms, float* sweep2_ms);
+
+/*
+ * Reads the device-side status word that the tensor-core kernel sets when one of its bounded
+ * waits gives up (a barrier that never completed).  Synchronises the stream.  0 = clean; any
+ * other value encodes which wait ran out.  `workspace` is the workspace of the call to check.
+ */
+int flk_tc_status(const void* workspace, void* stream, int* status_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FALKON_B200_H */

@@ -1,0 +1,97 @@
+"""CPU-side checks of the C ABI: the library loads, exports every symbol the header declares,
+and rejects bad arguments with status codes before touching the GPU."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from falkon_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "falkon_b200.h")
+
+
+@pytest.fixture(scope="module")
+def lib():
+    _lib.build()
+    return _lib.load()
+
+
+def declared_symbols():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(flk_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported(lib):
+    names = declared_symbols()
+    assert len(names) >= 14
+    for name in names:
+        assert hasattr(lib, name), f"{name} declared in include/falkon_b200.h but not exported"
+    assert set(names) == set(_lib.EXPORTED_SYMBOLS)
+
+
+def test_version_and_status_names(lib):
+    assert lib.flk_version() >= 100
+    assert lib.flk_status_name(0) == b"FLK_OK"
+    assert lib.flk_status_name(-3) == b"FLK_ERR_WORKSPACE"
+    assert lib.flk_status_name(-7) == b"FLK_ERR_TIMEOUT"
+
+
+def test_workspace_queries_are_pure_host_arithmetic(lib):
+    small = lib.flk_fdmmv_workspace_bytes(0, 0, 20000, 1000, 10, 1, 0)
+    big = lib.flk_fdmmv_workspace_bytes(0, 0, 10_000_000, 50_000, 28, 1, 0)
+    assert 0 < small < big < 16 * 2**30
+    assert lib.flk_fmmv_workspace_bytes(0, 0, 20000, 1000, 10, 1, 0) <= small
+    assert lib.flk_fdmmv_host_workspace_bytes(0, 0, 20000, 1000, 10, 1, 0) > small
+    # fp64 and large d go to the SIMT kernel, fp32 with d <= 30 to the tensor-core kernel
+    assert lib.flk_uses_tensor_cores(0, 0, 28, 1, 0) == 1
+    assert lib.flk_uses_tensor_cores(0, 3, 30, 4, 0) == 1
+    assert lib.flk_uses_tensor_cores(0, 0, 31, 1, 0) == 0
+    assert lib.flk_uses_tensor_cores(1, 0, 9, 1, 0) == 0
+    assert lib.flk_uses_tensor_cores(0, 0, 28, 1, _lib.FLAG_FORCE_SIMT) == 0
+    assert lib.flk_fmmv_workspace_bytes(7, 0, 10, 10, 2, 1, 0) == _lib.FLK_ERR_BAD_ARG
+    assert lib.flk_fmmv_workspace_bytes(0, 9, 10, 10, 2, 1, 0) == _lib.FLK_ERR_BAD_ARG
+    assert lib.flk_fmmv_workspace_bytes(0, 0, -1, 10, 2, 1, 0) == _lib.FLK_ERR_BAD_ARG
+
+
+def test_argument_errors_return_status_codes(lib):
+    sig = (ctypes.c_double * 1)(1.0)
+    dummy = ctypes.c_void_p(4096)
+    # null X1
+    st = lib.flk_fmmv(0, 0, None, 10, 4, 1, dummy, 5, 4, 1, 4, dummy, 1, 1, 1, dummy, 1, 1, sig, 1, dummy, 1 << 30, 0, None)
+    assert st == _lib.FLK_ERR_BAD_ARG and b"X1" in lib.flk_last_error()
+    # neither stride is 1
+    st = lib.flk_fmmv(0, 0, dummy, 10, 8, 2, dummy, 5, 4, 1, 4, dummy, 1, 1, 1, dummy, 1, 1, sig, 1, dummy, 1 << 30, 0, None)
+    assert st == _lib.FLK_ERR_LAYOUT
+    # sigma of the wrong length
+    st = lib.flk_fmmv(0, 0, dummy, 10, 4, 1, dummy, 5, 4, 1, 4, dummy, 1, 1, 1, dummy, 1, 1, sig, 3, dummy, 1 << 30, 0, None)
+    assert st == _lib.FLK_ERR_BAD_ARG
+    # missing / undersized / misaligned workspace
+    st = lib.flk_fmmv(0, 0, dummy, 10, 4, 1, dummy, 5, 4, 1, 4, dummy, 1, 1, 1, dummy, 1, 1, sig, 1, None, 0, 0, None)
+    assert st == _lib.FLK_ERR_WORKSPACE
+    st = lib.flk_fmmv(0, 0, dummy, 10, 4, 1, dummy, 5, 4, 1, 4, dummy, 1, 1, 1, dummy, 1, 1, sig, 1, dummy, 16, 0, None)
+    assert st == _lib.FLK_ERR_WORKSPACE
+    st = lib.flk_fmmv(0, 0, dummy, 10, 4, 1, dummy, 5, 4, 1, 4, dummy, 1, 1, 1, dummy, 1, 1, sig, 1, ctypes.c_void_p(4100), 1 << 30, 0, None)
+    assert st == _lib.FLK_ERR_WORKSPACE
+    # fdmmv without v and w
+    st = lib.flk_fdmmv(0, 0, dummy, 10, 4, 1, dummy, 5, 4, 1, 4, None, 0, 0, None, 0, 0, 1, dummy, 1, 1, sig, 1, dummy, 1 << 30, 0, None)
+    assert st == _lib.FLK_ERR_BAD_ARG
+    # forcing the tensor-core kernel where it does not apply
+    st = lib.flk_fmmv(1, 0, dummy, 10, 4, 1, dummy, 5, 4, 1, 4, dummy, 1, 1, 1, dummy, 1, 1, sig, 1, dummy, 1 << 30, _lib.FLAG_FORCE_TC, None)
+    assert st == _lib.FLK_ERR_UNSUPPORTED
+
+
+def test_status_maps_to_reference_exception_types(lib):
+    lib.flk_fmmv_workspace_bytes(0, 0, -1, 10, 2, 1, 0)
+    with pytest.raises(ValueError):
+        _lib.raise_for_status(_lib.FLK_ERR_BAD_ARG)
+    with pytest.raises(ValueError):
+        _lib.raise_for_status(_lib.FLK_ERR_LAYOUT)
+    with pytest.raises(MemoryError):
+        _lib.raise_for_status(_lib.FLK_ERR_WORKSPACE)
+    with pytest.raises(NotImplementedError):
+        _lib.raise_for_status(_lib.FLK_ERR_UNSUPPORTED)
+    with pytest.raises(RuntimeError):
+        _lib.raise_for_status(_lib.FLK_ERR_CUDA)

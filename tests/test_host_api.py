@@ -1,0 +1,114 @@
+"""CPU tests of the host-side mirror of the reference's operator API (no GPU work)."""
+import dataclasses
+
+import numpy as np
+import pytest
+import torch
+
+from falkon_b200 import FalkonOptions
+from falkon_b200.kernels import GaussianKernel, Kernel, LaplacianKernel, MaternKernel, validate_sigma
+from falkon_b200.mmv_ops import fdmmv, fmmv
+from falkon_b200.mmv_ops.utils import create_output_mat, is_contig, is_f_contig
+from falkon_b200 import _lib
+
+
+def test_options_match_reference_field_list():
+    # names and defaults of falkon/options.py:168-181, :205-208, :223-227, :257-259, :281-283
+    expected = {
+        "debug": False, "use_cpu": False, "max_gpu_mem": np.inf, "max_cpu_mem": np.inf,
+        "compute_arch_speed": False, "no_single_kernel": True, "min_cuda_pc_size_32": 10000,
+        "min_cuda_pc_size_64": 30000, "min_cuda_iter_size_32": 300_000_000, "min_cuda_iter_size_64": 900_000_000,
+        "never_store_kernel": False, "store_kernel_d_threshold": 1200, "num_fmm_streams": 2, "memory_slack": 0.9,
+        "keops_acc_dtype": "auto", "keops_sum_scheme": "auto", "keops_active": "auto", "keops_memory_slack": 0.7,
+        "cg_epsilon_32": 1e-7, "cg_epsilon_64": 1e-15, "cg_tolerance": 1e-7, "cg_full_gradient_every": 10,
+        "cg_differential_convergence": False, "pc_epsilon_32": 1e-5, "pc_epsilon_64": 1e-13,
+        "cpu_preconditioner": False, "chol_force_in_core": False, "chol_force_ooc": False,
+        "chol_par_blk_multiplier": 2,
+    }
+    assert dataclasses.asdict(FalkonOptions()) == expected
+    o = FalkonOptions(max_gpu_mem=1.0, keops_active="no")
+    merged = dataclasses.replace(FalkonOptions(debug=True), **dataclasses.asdict(o))
+    assert merged.max_gpu_mem == 1.0 and merged.keops_active == "no" and merged.debug is False
+    assert o.cg_epsilon(torch.float32) == 1e-7 and o.pc_epsilon(torch.float64) == 1e-13
+    with pytest.raises(TypeError):
+        o.cg_epsilon(torch.float16)
+    assert o.get_base_options().max_gpu_mem == 1.0
+
+
+def test_sigma_and_nu_validation():
+    assert validate_sigma(3).dtype == torch.float64 and validate_sigma(3).shape == (1,)
+    assert validate_sigma(torch.tensor([[1.0], [2.0]])).shape == (2,)
+    with pytest.raises(ValueError):
+        validate_sigma(torch.eye(3))
+    with pytest.raises(TypeError):
+        validate_sigma(None)
+    k = MaternKernel(2.0, 2.5)
+    assert k.nu == 2.5 and k.name == "2.5-matern" and k.nondiff_params == {"nu": 2.5}
+    assert list(k.diff_params) == ["sigma"]
+    assert MaternKernel(2.0, 0.5)._flk_spec()[0] == _lib.FLK_LAPLACIAN
+    assert MaternKernel(2.0, float("inf"))._flk_spec()[0] == _lib.FLK_GAUSSIAN
+    with pytest.raises(ValueError):
+        MaternKernel(2.0, 3.5)
+    with pytest.raises(TypeError):
+        MaternKernel(2.0, 2)
+    g = GaussianKernel(torch.tensor([1.0, 2.0, 3.0]))
+    kid, sig = g._flk_spec()
+    assert kid == _lib.FLK_GAUSSIAN and sig.dtype == np.float64 and sig.tolist() == [1.0, 2.0, 3.0]
+    d = g.detach()
+    assert isinstance(d, GaussianKernel) and d.params is g.params
+    assert "GaussianKernel" in repr(g) and "Laplacian" in str(LaplacianKernel(1.0))
+
+
+def test_dimension_and_dtype_errors_follow_reference():
+    k = GaussianKernel(1.0)
+    X, C, v, w = torch.randn(10, 3), torch.randn(4, 3), torch.randn(4, 2), torch.randn(10, 2)
+    with pytest.raises(ValueError, match="One of v and w"):
+        k.dmmv(X, C, None, None)
+    with pytest.raises(ValueError, match="must be 2D"):
+        k.mmv(X[0], C, v)
+    with pytest.raises(ValueError, match="Dimensions of matrix v"):
+        k.mmv(X, C, torch.randn(5, 2))
+    with pytest.raises(ValueError, match="Dimensions of matrix w"):
+        k.dmmv(X, C, v, torch.randn(9, 2))
+    with pytest.raises(ValueError, match="Output dimension"):
+        k.dmmv(X, C, v, w, out=torch.empty(10, 2))
+    with pytest.raises(TypeError):
+        k.mmv(X.double(), C, v)
+    with pytest.raises(NotImplementedError):
+        k(X, C)
+
+
+def test_products_fail_loudly_without_gpu_or_with_use_cpu():
+    k = GaussianKernel(1.0)
+    X, C, v = torch.randn(10, 3), torch.randn(4, 3), torch.randn(4, 1)
+    with pytest.raises(RuntimeError, match="no CPU implementation"):
+        k.mmv(X, C, v, opt=FalkonOptions(use_cpu=True))
+    if not torch.cuda.is_available():
+        with pytest.raises(RuntimeError, match="needs a CUDA device"):
+            k.mmv(X, C, v)
+        with pytest.raises(RuntimeError, match="needs a CUDA device"):
+            k.dmmv(X, C, v, None)
+    with pytest.raises(NotImplementedError):
+        fdmmv(X, C, v, None, k, None, True, FalkonOptions())  # positional, differentiable=True
+    with pytest.raises(ValueError, match="memory contiguous"):
+        fmmv(torch.randn(10, 6)[:, ::2], C, v, k, opt=FalkonOptions())
+
+    class Custom(Kernel):
+        def compute(self, X1, X2, out, diag, **kw):
+            return out
+
+    with pytest.raises(NotImplementedError, match="_flk_spec"):
+        Custom("custom", None).mmv(X, C, v)
+
+
+def test_output_allocation_rules():
+    Xc = torch.empty(6, 3)
+    Xf = torch.empty(3, 6).t()
+    assert is_contig(Xc) and is_contig(Xf) and is_f_contig(Xf, strict=True) and not is_f_contig(Xc, strict=True)
+    cpu = torch.device("cpu")
+    o = create_output_mat(None, [cpu, cpu], (6, 2), torch.float32, "cuda", Xc)
+    assert o.shape == (6, 2) and o.stride() == (2, 1) and o.device.type == "cpu"
+    o = create_output_mat(None, [cpu, cpu], (6, 2), torch.float64, "cuda", Xf)
+    assert o.stride() == (1, 6) and o.dtype == torch.float64
+    given = torch.empty(6, 2)
+    assert create_output_mat(given, [cpu], (6, 2), torch.float32, "cuda", Xc) is given

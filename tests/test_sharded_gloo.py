@@ -1,0 +1,80 @@
+"""World-size-2 gloo test of the row-sharded products (CPU; local products from the oracle)."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, port, ret):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from falkon_b200.kernels import GaussianKernel
+        from falkon_b200.sharded import ShardedKernelOps, shard_rows
+        from oracle import falkon_oracle as fo
+
+        rng = np.random.default_rng(7)
+        n, m, d, t = 1001, 37, 5, 2
+        X = torch.from_numpy(rng.standard_normal((n, d)))
+        C = X[:m].clone()
+        v = torch.from_numpy(rng.standard_normal((m, t)))
+        w = torch.from_numpy(rng.standard_normal((n, t)))
+        start, length = shard_rows(n, world, rank)
+        Xs, ws = X[start : start + length], w[start : start + length]
+
+        def local_mmv(A, B, vec, out=None, opt=None):
+            return fo.fmmv(A, B, vec, "gaussian", 2.0)
+
+        def local_dmmv(A, B, vec, ww, out=None, opt=None):
+            return fo.fdmmv(A, B, vec, ww, "gaussian", 2.0)
+
+        ops = ShardedKernelOps(GaussianKernel(2.0), local_mmv=local_mmv, local_dmmv=local_dmmv)
+        assert ops.world == world
+        got = ops.dmmv(Xs, C, v, ws)
+        want = fo.dense_fdmmv_fp64(X.numpy(), C.numpy(), v.numpy(), w.numpy(), "gaussian", 2.0)
+        err1 = fo.rel_l2(got.numpy(), want)
+        got_t = ops.mmv_t(C, Xs, ws)
+        want_t = fo.dense_fmmv_fp64(C.numpy(), X.numpy(), w.numpy(), "gaussian", 2.0)
+        err2 = fo.rel_l2(got_t.numpy(), want_t)
+        rows = ops.mmv(Xs, C, v)
+        want_rows = fo.dense_fmmv_fp64(X.numpy(), C.numpy(), v.numpy(), "gaussian", 2.0)[start : start + length]
+        err3 = fo.rel_l2(rows.numpy(), want_rows)
+        ret[rank] = (err1, err2, err3, length)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_products_world2_gloo():
+    world = 2
+    port = 29500 + (os.getpid() % 2000)
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_worker, args=(world, port, ret), nprocs=world, join=True)
+    assert sorted(ret.keys()) == [0, 1]
+    assert ret[0][3] + ret[1][3] == 1001
+    for r in range(world):
+        assert ret[r][0] < 1e-10 and ret[r][1] < 1e-10 and ret[r][2] < 1e-10, ret[r]
+
+
+def test_shard_rows_partition():
+    sys.path.insert(0, ROOT)
+    from falkon_b200.sharded import shard_rows
+
+    for n in (0, 1, 7, 8, 1001, 10_000_000):
+        for world in (1, 2, 3, 8):
+            spans = [shard_rows(n, world, r) for r in range(world)]
+            assert spans[0][0] == 0
+            assert sum(length for _, length in spans) == n
+            for (s0, l0), (s1, _) in zip(spans, spans[1:]):
+                assert s0 + l0 == s1
+            assert max(length for _, length in spans) - min(length for _, length in spans) <= 1
+    with pytest.raises(ValueError):
+        shard_rows(10, 2, 2)
