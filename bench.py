@@ -18,9 +18,7 @@ timed on a bounded sample on this machine's host cores.
 import argparse
 import json
 import os
-import subprocess
 import sys
-import tempfile
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -59,59 +57,74 @@ def load_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clock, power and clock-event (throttle) reasons through NVML from a background
+    thread while the timed region runs (read-only queries; nothing is set)."""
 
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+               0x80: "hw_power_brake_slowdown"}
 
-    def __init__(self, gpu_index):
-        self.gpu_index = gpu_index
-        self.proc = None
-        self.path = None
+    def __init__(self, torch_device):
+        self.samples = []
+        self.thread = None
+        self.stop_flag = False
+        self.handle = None
+        self.err = None
+        try:
+            import pynvml
+
+            self.nv = pynvml
+            pynvml.nvmlInit()
+            try:
+                uuid = str(torch.cuda.get_device_properties(torch_device).uuid)
+                if not uuid.startswith("GPU-"):
+                    uuid = "GPU-" + uuid
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(uuid)
+            except Exception:
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(torch_device.index or 0)
+            self.sm_max = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+        except Exception as e:  # NVML missing: report that instead of inventing numbers
+            self.err = f"nvml unavailable: {e}"
+
+    def _loop(self):
+        nv = self.nv
+        while not self.stop_flag:
+            try:
+                sm = float(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
+                pw = nv.nvmlDeviceGetPowerUsage(self.handle) / 1000.0
+                try:
+                    rs = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle))
+                except Exception:
+                    rs = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle))
+                self.samples.append((sm, pw, rs))
+            except Exception as e:
+                self.err = str(e)
+                return
+            time.sleep(0.005)
 
     def start(self):
-        try:
-            fd, self.path = tempfile.mkstemp(suffix=".csv")
-            os.close(fd)
-            self.out = open(self.path, "w")
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=self.out, stderr=subprocess.DEVNULL)
-        except Exception:
-            self.proc = None
+        if self.handle is None:
+            return
+        import threading
+
+        self.thread = threading.Thread(target=self._loop, daemon=True)
+        self.thread.start()
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except Exception:
-            self.proc.kill()
-        self.out.close()
-        sm, smax, power, reasons = [], [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        with open(self.path) as f:
-            for line in f:
-                parts = [p.strip() for p in line.split(",")]
-                if len(parts) < 9:
-                    continue
-                try:
-                    sm.append(float(parts[1]))
-                    smax.append(float(parts[2]))
-                    power.append(float(parts[3]))
-                except ValueError:
-                    continue
-                for nm, val in zip(names, parts[5:9]):
-                    if val.lower().startswith("active"):
-                        reasons.add(nm)
-        os.unlink(self.path)
-        if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        busy = [s for s, p in zip(sm, power) if p > 300.0] or sm
-        return {"sm_mhz": float(np.median(busy)), "sm_max_mhz": float(max(smax)), "power_w_max": float(max(power)),
-                "samples": len(sm), "reasons": sorted(reasons)}
+        if self.thread is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [self.err or "not sampled"]}
+        self.stop_flag = True
+        self.thread.join(timeout=2)
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.sm_max, "reasons": [self.err or "no samples"]}
+        sm = [a for a, _, _ in self.samples]
+        pw = [b for _, b, _ in self.samples]
+        bits = 0
+        for _, _, r in self.samples:
+            bits |= r
+        reasons = sorted(name for bit, name in self.REASONS.items() if bits & bit)
+        return {"sm_mhz": float(np.median(sm)), "sm_min_mhz": float(min(sm)), "sm_max_mhz": self.sm_max,
+                "power_w_max": float(max(pw)), "power_w_median": float(np.median(pw)), "samples": len(sm),
+                "reasons": reasons}
 
 
 def time_cpu_oracle(n_sample, reps):
@@ -138,11 +151,13 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    n_sample = 50_000
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     from oracle import falkon_oracle as fo
 
+    # size the per-step sample so that one step costs about a second on this host
+    rate, _, _ = time_cpu_oracle(10_000, reps=1)
+    n_sample = int(min(200_000, max(10_000, round(rate * 1.0 / M, -3))))
     X, w = gen_shard(n_sample, 1002, "cpu")
     g = torch.Generator().manual_seed(2002)
     C = X[torch.randperm(n_sample, generator=g)[:M]].contiguous()
@@ -170,7 +185,7 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=40)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rows", type=int, default=N_PER_GPU, help="rows of X per GPU (default: the benchmark size)")
@@ -228,10 +243,7 @@ def main():
 
     # ---------------- timed region: K steps, device events per step, L2 flushed between steps ----------
     _lib.set_timing(True)
-    sampler = ClockSampler(local_rank if "CUDA_VISIBLE_DEVICES" not in os.environ else
-                           int(os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank]))
-    if rank == 0:
-        sampler.start()
+    sampler = ClockSampler(dev) if rank == 0 else None
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     stops = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     sweep_ms = []
@@ -239,6 +251,8 @@ def main():
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
+    if rank == 0:
+        sampler.start()
     wall0 = time.perf_counter()
     for i in range(args.steps):
         flush.fill_(i & 0xFF)
