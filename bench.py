@@ -127,6 +127,12 @@ class ClockSampler:
                 "reasons": reasons}
 
 
+def cpu_centres(X, g):
+    n = X.shape[0]
+    idx = torch.randperm(n, generator=g)[:M] if n >= M else torch.randint(n, (M,), generator=g)
+    return X[idx].contiguous()
+
+
 def time_cpu_oracle(n_sample, reps):
     """Times the CPU oracle's fdmmv (the reference algorithm: blocked GEMM + element-wise passes)
     on n_sample rows of the workload with all host threads.  Returns (pair-evals/s, seconds, cores)."""
@@ -136,7 +142,7 @@ def time_cpu_oracle(n_sample, reps):
     torch.set_num_threads(cores)
     X, w = gen_shard(n_sample, 1002, "cpu")
     g = torch.Generator().manual_seed(2002)
-    C = X[torch.randperm(n_sample, generator=g)[:M]].contiguous()
+    C = cpu_centres(X, g)
     v = torch.randn(M, T, generator=g)
     best = None
     for _ in range(reps):
@@ -160,7 +166,7 @@ def run_reference(args):
     n_sample = int(min(200_000, max(10_000, round(rate * 1.0 / M, -3))))
     X, w = gen_shard(n_sample, 1002, "cpu")
     g = torch.Generator().manual_seed(2002)
-    C = X[torch.randperm(n_sample, generator=g)[:M]].contiguous()
+    C = cpu_centres(X, g)
     v = torch.randn(M, T, generator=g)
     for _ in range(args.warmup):
         fo.fdmmv(X, C, v, w, "gaussian", SIGMA, max_block_elems=256 * 2**20)
