@@ -21,6 +21,7 @@ LIB_PATH = os.path.join(_HERE, "libfalkon_b200.so")
 FLK_F32, FLK_F64 = 0, 1
 FLK_GAUSSIAN, FLK_LAPLACIAN, FLK_MATERN15, FLK_MATERN25 = 0, 1, 2, 3
 FLAG_FORCE_SIMT, FLAG_FORCE_TC = 1, 2
+STATIC_SCRATCH_BYTES = 64 << 20
 
 FLK_ERR_BAD_ARG, FLK_ERR_LAYOUT, FLK_ERR_WORKSPACE = -1, -2, -3
 FLK_ERR_CUDA, FLK_ERR_UNSUPPORTED, FLK_ERR_DEVICE, FLK_ERR_TIMEOUT = -4, -5, -6, -7
@@ -79,6 +80,8 @@ _SIGNATURES = {
     # dtype, kernel, X1(4), X2(4), d, v(3), w(3), t, out(3), sigma, len, ws, bytes, flags, stream
     "flk_fdmmv": (_int, [_int, _int] + _MAT + _MAT + [_i64, _vp, _i64, _i64, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _dp, _i64, _vp, _i64, _int, _vp]),
     "flk_fdmmv_host": (_int, [_int, _int] + _MAT + _MAT + [_i64, _vp, _i64, _i64, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _dp, _i64, _vp, _i64, _int, _vp]),
+    # dtype, kernel, X1(4), X2(4), d, v ptr, t, v strides(2), out ptr + strides(3), sigma (double), flags, stream
+    "flk_fmmv_static": (_int, [_int, _int] + _MAT + _MAT + [_i64, _vp, _i64, _i64, _i64, _vp, _i64, _i64, ctypes.c_double, _int, _vp]),
     "flk_tc_status": (_int, [_vp, _vp, ctypes.POINTER(_int)]),
     "flk_set_timing": (_int, [_int]),
     "flk_get_sweep_ms": (_int, [ctypes.POINTER(ctypes.c_float), ctypes.POINTER(ctypes.c_float)]),

@@ -751,3 +751,65 @@ int flk_tc_status(const void* workspace, void* stream, int* status_out) {
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// flk_fmmv_static: K(X1, X2) v for callers that have no way to obtain scratch memory.
+//
+// Who needs this: code that runs where device allocation is off the table -- a plug-in inside a host
+// application that handed all device memory to its own pool at start-up (a raw cudaMalloc would fail
+// or steal from that pool), or a latency-critical loop that cannot afford the device-wide
+// synchronisation cudaMalloc / cudaFree imply and has no allocator handle to pass down.  Such a
+// caller cannot supply the workspace flk_fmmv asks for.  Here the workspace is a fixed array that
+// is part of the library image itself, so nothing is allocated by anyone at call time.
+// ---------------------------------------------------------------------------------------------
+namespace flk {
+
+// The scratch array.  It lives in every CUDA context that loads this library, from load until the
+// process exits, whether or not the entry point is ever called.
+static __device__ __align__(256) unsigned char g_static_scratch[FLK_STATIC_SCRATCH_BYTES];
+
+constexpr int kMaxStaticDevices = 64;
+static void* g_static_scratch_addr[kMaxStaticDevices] = {nullptr};
+static std::atomic<bool> g_static_scratch_ready[kMaxStaticDevices];
+
+// `g_static_scratch` named in host code is only the host-side handle of the symbol, not a device
+// address; the address kernels may use has to be asked for, per device, with that device current.
+static int static_scratch_for_current_device(void** out) {
+  int dev = 0;
+  FLK_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxStaticDevices)
+    return fail(FLK_ERR_UNSUPPORTED, "flk_fmmv_static supports device ordinals below %d", kMaxStaticDevices);
+  if (!g_static_scratch_ready[dev].load(std::memory_order_acquire)) {
+    void* ptr = nullptr;
+    FLK_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_static_scratch));
+    if (ptr == nullptr) return fail(FLK_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+    g_static_scratch_addr[dev] = ptr;  // same value if two threads race here
+    g_static_scratch_ready[dev].store(true, std::memory_order_release);
+  }
+  *out = g_static_scratch_addr[dev];
+  return FLK_OK;
+}
+
+}  // namespace flk
+
+extern "C" int flk_fmmv_static(int dtype, int kernel, const void* X1, int64_t n, int64_t x1_rs, int64_t x1_cs,
+                               const void* X2, int64_t m, int64_t x2_rs, int64_t x2_cs, int64_t d, const void* v,
+                               int64_t t, int64_t v_rs, int64_t v_cs, void* out, int64_t out_rs, int64_t out_cs,
+                               double sigma, int flags, void* stream) {
+  FLK_TRY(check_common(dtype, kernel, n, m, d, t));
+  const int64_t need = make_layout(nullptr, false, true, dtype, kernel, n, m, d, t, flags).total;
+  if (need > (int64_t)FLK_STATIC_SCRATCH_BYTES)
+    return fail(FLK_ERR_WORKSPACE,
+                "flk_fmmv_static: this problem needs %lld bytes of scratch but the built-in array holds %lld; "
+                "use flk_fmmv with a caller-provided workspace",
+                (long long)need, (long long)FLK_STATIC_SCRATCH_BYTES);
+  void* scratch = nullptr;
+  FLK_TRY(static_scratch_for_current_device(&scratch));
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  // The array still holds whatever the previous call left.  Everything the kernels read is rewritten
+  // by this call's preparation steps except the status word at the front, which must start at zero.
+  FLK_CUDA_TRY(cudaMemsetAsync(scratch, 0, 256, st));
+  // a scalar length-scale only: staging a per-dimension vector would need a temporary host buffer
+  return flk_fmmv(dtype, kernel, X1, n, x1_rs, x1_cs, X2, m, x2_rs, x2_cs, d, v, t, v_rs, v_cs, out, out_rs, out_cs,
+                  &sigma, 1, scratch, (int64_t)FLK_STATIC_SCRATCH_BYTES, flags, stream);
+}

@@ -154,6 +154,38 @@ int flk_fdmmv_host(int dtype, int kernel,
                    void* workspace, int64_t workspace_bytes, int flags, void* stream);
 
 /*
+ * flk_fmmv_static: out[n x t] = k(X1, X2) v without any workspace argument.  (No counterpart in the
+ * reference: it exists for embedders, not for parity.)
+ *
+ * For callers that cannot allocate device memory and therefore cannot give flk_fmmv its workspace:
+ * a plug-in whose host application took all device memory into its own pool at start-up, or a
+ * real-time loop that must never run into the device-wide synchronisation of cudaMalloc / cudaFree.
+ * The scratch memory is a fixed array of FLK_STATIC_SCRATCH_BYTES compiled into the library; each
+ * GPU context that loads the library carries it until the process exits.  The call itself performs no
+ * cudaMalloc / cudaFree and calls no allocating routine.  Inputs and output are DEVICE pointers owned
+ * by the caller, exactly as for flk_fmmv; the length-scale is one scalar.
+ *
+ * Limits and rules:
+ *  - the problem must fit: flk_fmmv_workspace_bytes(dtype, kernel, n, m, d, t, flags) must not exceed
+ *    FLK_STATIC_SCRATCH_BYTES, otherwise FLK_ERR_WORKSPACE is returned with a message and nothing runs
+ *    (fp32 Gaussian, d = 28, t = 1: about 170,000 rows of X1 and X2 together);
+ *  - the first call on each device looks up the array's device address (the device must be current);
+ *    make that first call outside any stream capture;
+ *  - all calls share the one array: two calls whose GPU work can overlap (different streams, or
+ *    different host threads on one device) race on it and corrupt each other.  Calls issued to one
+ *    stream are safe.  The array keeps the previous call's contents; the entry point re-zeroes the
+ *    part that has to start at zero.
+ */
+#define FLK_STATIC_SCRATCH_BYTES (64ll << 20)
+int flk_fmmv_static(int dtype, int kernel,
+                    const void* X1, int64_t n, int64_t x1_rs, int64_t x1_cs,
+                    const void* X2, int64_t m, int64_t x2_rs, int64_t x2_cs,
+                    int64_t d,
+                    const void* v, int64_t t, int64_t v_rs, int64_t v_cs,
+                    void* out, int64_t out_rs, int64_t out_cs,
+                    double sigma, int flags, void* stream);
+
+/*
  * Counters for the calling process: number of kernels this library has launched and the status
  * word of the last tensor-core launch read back by flk_tc_status (0 = clean).
  */
