@@ -16,7 +16,7 @@ import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _CSRC = os.path.join(_HERE, "csrc")
-LIB_PATH = os.path.join(_HERE, "libfalkon_b200.so")
+LIB_PATH = os.environ.get("FALKON_B200_LIB") or os.path.join(_HERE, "libfalkon_b200.so")
 
 FLK_F32, FLK_F64 = 0, 1
 FLK_GAUSSIAN, FLK_LAPLACIAN, FLK_MATERN15, FLK_MATERN25 = 0, 1, 2, 3

@@ -175,6 +175,12 @@ struct Layout {
   void* raw1 = nullptr;
   void* raw2 = nullptr;
   SweepPlan s1, s2;
+  // SIMT alternative of the tensor-core path (runs only when the image builder raised the range
+  // flag): its own sweep plans and partial-result buffers; operands in x1.xs / x2.xs.
+  void* fraw1 = nullptr;
+  void* fraw2 = nullptr;
+  SweepPlan f1, f2;
+  int* range_flag() const { return reinterpret_cast<int*>(status) + tc::kStatusRange; }
 };
 
 // need_x1_as_b / need_x2_as_a: which tensor-core images each operand needs.
@@ -189,16 +195,19 @@ static Layout make_layout(void* ws, bool dmmv, bool has_v, int dtype, int kernel
   L.s1 = plan_sweep(L.tc, dtype, n, m, t);  // rows = X1, reduction over X2
   L.s2 = plan_sweep(L.tc, dtype, m, n, t);  // rows = X2, reduction over X1 (fdmmv only)
   const int64_t n_pad = L.s1.r_pad, m_pad = L.s1.s_pad;
+  const bool first = !dmmv || has_v;  // is the first sweep executed?
   if (L.tc) {
     const int64_t kp = tc::padded_k(d);
-    const bool first = !dmmv || has_v;  // is the first sweep executed?
-    if (first) L.x1.img_a = c.take(n_pad * kp * 4);
-    if (first) L.x2.img_b = c.take(m_pad * kp * 4);
+    if (first) L.x1.img_a = c.take(n_pad * kp * 2);
+    if (first) L.x2.img_b = c.take(m_pad * kp * 2);
     if (dmmv) {
-      L.x2.img_a = c.take(m_pad * kp * 4);
-      L.x1.img_b = c.take(n_pad * kp * 4);
+      L.x2.img_a = c.take(m_pad * kp * 2);
+      L.x1.img_b = c.take(n_pad * kp * 2);
     }
-  } else {
+    L.f1 = plan_sweep(false, dtype, n, m, t);
+    L.f2 = plan_sweep(false, dtype, m, n, t);
+  }
+  {
     const int ld = ld_for(dtype, d);
     L.x1.xs = c.take(n_pad * ld * es);
     L.x1.norms = c.take(n_pad * es);
@@ -206,16 +215,15 @@ static Layout make_layout(void* ws, bool dmmv, bool has_v, int dtype, int kernel
     L.x2.norms = c.take(m_pad * es);
   }
   const int tp = L.s1.tp;
-  if (!dmmv) {
+  if (first) {
     L.vbuf = c.take(m_pad * tp * es);
     L.raw1 = c.take(L.s1.raw_elems() * es);
-  } else {
-    if (has_v) {
-      L.vbuf = c.take(m_pad * tp * es);
-      L.raw1 = c.take(L.s1.raw_elems() * es);
-    }
+    if (L.tc) L.fraw1 = c.take(L.f1.raw_elems() * es);
+  }
+  if (dmmv) {
     L.ubuf = c.take(n_pad * tp * es);
     L.raw2 = c.take(L.s2.raw_elems() * es);
+    if (L.tc) L.fraw2 = c.take(L.f2.raw_elems() * es);
   }
   L.total = c.off;
   return L;
@@ -265,12 +273,12 @@ static int upload_sigma(const double* sigma, int64_t sigma_len, void* dst, T* sc
 
 template <typename T>
 static int run_prep_rows(const Mat& X, const T* sigma_dev, T sigma_scalar, int sigma_len, void* xs, int ld,
-                         int64_t rows_pad, void* norms, cudaStream_t stream) {
+                         int64_t rows_pad, void* norms, Gate gate, cudaStream_t stream) {
   int blocks = (int)ceil_div(rows_pad, kPrepRows);
   prep_rows_kernel<T><<<blocks, 256, 0, stream>>>(reinterpret_cast<const T*>(X.ptr), X.rows, (int)X.cols, X.rs,
                                                   X.cs, sigma_dev, sigma_scalar, sigma_len,
                                                   reinterpret_cast<T*>(xs), ld, rows_pad,
-                                                  reinterpret_cast<T*>(norms));
+                                                  reinterpret_cast<T*>(norms), gate);
   count_launch();
   FLK_CUDA_TRY(cudaGetLastError());
   return FLK_OK;
@@ -288,11 +296,11 @@ static int run_prep_vec(const Mat& v, void* vbuf, int64_t s_pad, int tp, int tt,
 
 template <typename T>
 static int run_finalize(const SweepPlan& sp, const void* raw, const Mat* add, void* out, int64_t out_rs,
-                        int64_t out_cs, int64_t t, bool padded, cudaStream_t stream) {
+                        int64_t out_cs, int64_t t, bool padded, Gate gate, cudaStream_t stream) {
   finalize_kernel<T><<<grid_for(sp.r_pad * sp.tp), 256, 0, stream>>>(
       reinterpret_cast<const T*>(raw), sp.n_chunks, sp.r_pad, sp.tp, sp.r, (int)t,
       add ? reinterpret_cast<const T*>(add->ptr) : nullptr, add ? add->rs : 0, add ? add->cs : 0,
-      reinterpret_cast<T*>(out), out_rs, out_cs, padded ? 1 : 0, sp.tt);
+      reinterpret_cast<T*>(out), out_rs, out_cs, padded ? 1 : 0, sp.tt, gate);
   count_launch();
   FLK_CUDA_TRY(cudaGetLastError());
   return FLK_OK;
@@ -300,7 +308,7 @@ static int run_finalize(const SweepPlan& sp, const void* raw, const Mat* add, vo
 
 template <typename T>
 static int run_sweep_simt(int kernel, const SweepPlan& sp, const Operand& a, const Operand& b, int ld,
-                          const void* vec, void* raw, cudaStream_t stream, int sweep_idx) {
+                          const void* vec, void* raw, Gate gate, cudaStream_t stream, int sweep_idx) {
   SimtArgs<T> args;
   args.A = reinterpret_cast<const T*>(a.xs);
   args.an = reinterpret_cast<const T*>(a.norms);
@@ -315,9 +323,11 @@ static int run_sweep_simt(int kernel, const SweepPlan& sp, const Operand& a, con
   args.row_tiles = sp.row_tiles;
   args.n_col_tiles = sp.n_col_tiles;
   args.tiles_per_chunk = sp.tiles_per_chunk;
-  FLK_TRY(timer_mark(2 * sweep_idx, stream));
+  args.gate = gate;
+  const bool timed = gate.flag == nullptr;  // the gated alternative is not the timed kernel
+  if (timed) FLK_TRY(timer_mark(2 * sweep_idx, stream));
   FLK_TRY((launch_simt_any<T>(kernel, args, sp.tt, sp.n_chunks, sp.t_chunks, stream)));
-  FLK_TRY(timer_mark(2 * sweep_idx + 1, stream));
+  if (timed) FLK_TRY(timer_mark(2 * sweep_idx + 1, stream));
   count_launch();
   return FLK_OK;
 }
@@ -325,8 +335,8 @@ static int run_sweep_simt(int kernel, const SweepPlan& sp, const Operand& a, con
 static int run_sweep_tc(int kernel, const SweepPlan& sp, const void* img_a, const void* img_b, int64_t d,
                         const void* vec, void* raw, void* status, cudaStream_t stream, int sweep_idx) {
   tc::SweepArgs args;
-  args.img_a = reinterpret_cast<const float*>(img_a);
-  args.img_b = reinterpret_cast<const float*>(img_b);
+  args.img_a = reinterpret_cast<const __half*>(img_a);
+  args.img_b = reinterpret_cast<const __half*>(img_b);
   args.vec = reinterpret_cast<const float*>(vec);
   args.raw = reinterpret_cast<float*>(raw);
   args.status = reinterpret_cast<int*>(status);
@@ -340,6 +350,51 @@ static int run_sweep_tc(int kernel, const SweepPlan& sp, const void* img_a, cons
   FLK_TRY(tc::launch_sweep(kernel, (int)d, args, sp.tt, sp.n_chunks, sp.t_chunks, stream));
   FLK_TRY(timer_mark(2 * sweep_idx + 1, stream));
   count_launch();
+  return FLK_OK;
+}
+
+// Gates of the two alternatives when the tensor-core path is chosen: the tensor-core results count
+// while the range flag is clear, the SIMT ones when it is set.  Without the tensor-core path the
+// SIMT kernels run unconditionally.
+static inline Gate gate_tc(const Layout& L) { return Gate{L.range_flag(), 0}; }
+static inline Gate gate_simt(const Layout& L) { return L.tc ? Gate{L.range_flag(), 1} : Gate{nullptr, 0}; }
+
+// Builds the operand forms both paths need: tensor-core tile images (which also raise the range
+// flag) and, gated, the scaled rows + norms of the SIMT kernels.
+template <typename T>
+static int prepare_operands(const Layout& L, int kernel, const Mat& X1, const Mat& X2, int64_t d, const T* sig_dev,
+                            T sig_scalar, int sigma_len, int dtype, cudaStream_t stream) {
+  if (L.tc) {
+    FLK_CUDA_TRY(cudaMemsetAsync(L.status, 0, 256, stream));
+    FLK_TRY(tc::prep_images(kernel, X1.ptr, X1.rows, X1.rs, X1.cs, (int)d, (const float*)sig_dev, (float)sig_scalar,
+                            sigma_len, L.s1.r_pad, L.x1.img_a, L.x1.img_b, reinterpret_cast<int*>(L.status), stream));
+    FLK_TRY(tc::prep_images(kernel, X2.ptr, X2.rows, X2.rs, X2.cs, (int)d, (const float*)sig_dev, (float)sig_scalar,
+                            sigma_len, L.s1.s_pad, L.x2.img_a, L.x2.img_b, reinterpret_cast<int*>(L.status), stream));
+    count_launch(2);
+  }
+  const int ld = ld_for(dtype, d);
+  FLK_TRY(run_prep_rows<T>(X1, sig_dev, sig_scalar, sigma_len, L.x1.xs, ld, L.s1.r_pad, L.x1.norms, gate_simt(L), stream));
+  FLK_TRY(run_prep_rows<T>(X2, sig_dev, sig_scalar, sigma_len, L.x2.xs, ld, L.s1.s_pad, L.x2.norms, gate_simt(L), stream));
+  return FLK_OK;
+}
+
+// One sweep + its finalisation, on whichever path(s) the layout holds.  `a`/`b` = output-side and
+// reduction-side operands, `tcp`/`fp` = the tensor-core (or sole SIMT) plan and the SIMT alternative.
+template <typename T>
+static int sweep_and_finalize(const Layout& L, int kernel, int dtype, int64_t d, int64_t t, const SweepPlan& tcp,
+                              const SweepPlan& fp, const Operand& a, const Operand& b, const void* vec, void* raw,
+                              void* fraw, const Mat* add, void* out, int64_t out_rs, int64_t out_cs, bool padded,
+                              cudaStream_t stream, int sweep_idx) {
+  const int ld = ld_for(dtype, d);
+  if (L.tc) {
+    FLK_TRY(run_sweep_tc(kernel, tcp, a.img_a, b.img_b, d, vec, raw, L.status, stream, sweep_idx));
+    FLK_TRY(run_finalize<T>(tcp, raw, add, out, out_rs, out_cs, t, padded, gate_tc(L), stream));
+    FLK_TRY(run_sweep_simt<T>(kernel, fp, a, b, ld, vec, fraw, gate_simt(L), stream, sweep_idx));
+    FLK_TRY(run_finalize<T>(fp, fraw, add, out, out_rs, out_cs, t, padded, gate_simt(L), stream));
+  } else {
+    FLK_TRY(run_sweep_simt<T>(kernel, tcp, a, b, ld, vec, raw, gate_simt(L), stream, sweep_idx));
+    FLK_TRY(run_finalize<T>(tcp, raw, add, out, out_rs, out_cs, t, padded, gate_simt(L), stream));
+  }
   return FLK_OK;
 }
 
@@ -359,22 +414,10 @@ static int fmmv_impl(int dtype, int kernel, const Mat& X1, const Mat& X2, const 
   T sig_scalar;
   const T* sig_dev;
   FLK_TRY(upload_sigma<T>(sigma, sigma_len, L.sigma, &sig_scalar, &sig_dev, stream));
+  FLK_TRY(prepare_operands<T>(L, kernel, X1, X2, d, sig_dev, sig_scalar, (int)sigma_len, dtype, stream));
   FLK_TRY(run_prep_vec<T>(v, L.vbuf, L.s1.s_pad, L.s1.tp, L.s1.tt, stream));
-  if (L.tc) {
-    FLK_CUDA_TRY(cudaMemsetAsync(L.status, 0, 256, stream));
-    FLK_TRY(tc::prep_images(kernel, X1.ptr, X1.rows, X1.rs, X1.cs, (int)d, (const float*)sig_dev,
-                            (float)sig_scalar, (int)sigma_len, L.s1.r_pad, (float*)L.x1.img_a, nullptr, stream));
-    FLK_TRY(tc::prep_images(kernel, X2.ptr, X2.rows, X2.rs, X2.cs, (int)d, (const float*)sig_dev,
-                            (float)sig_scalar, (int)sigma_len, L.s1.s_pad, nullptr, (float*)L.x2.img_b, stream));
-    count_launch(2);
-    FLK_TRY(run_sweep_tc(kernel, L.s1, L.x1.img_a, L.x2.img_b, d, L.vbuf, L.raw1, L.status, stream, 0));
-  } else {
-    const int ld = ld_for(dtype, d);
-    FLK_TRY(run_prep_rows<T>(X1, sig_dev, sig_scalar, (int)sigma_len, L.x1.xs, ld, L.s1.r_pad, L.x1.norms, stream));
-    FLK_TRY(run_prep_rows<T>(X2, sig_dev, sig_scalar, (int)sigma_len, L.x2.xs, ld, L.s1.s_pad, L.x2.norms, stream));
-    FLK_TRY(run_sweep_simt<T>(kernel, L.s1, L.x1, L.x2, ld, L.vbuf, L.raw1, stream, 0));
-  }
-  FLK_TRY(run_finalize<T>(L.s1, L.raw1, nullptr, out, out_rs, out_cs, t, false, stream));
+  FLK_TRY(sweep_and_finalize<T>(L, kernel, dtype, d, t, L.s1, L.f1, L.x1, L.x2, L.vbuf, L.raw1, L.fraw1, nullptr,
+                                out, out_rs, out_cs, false, stream, 0));
   return FLK_OK;
 }
 
@@ -392,39 +435,18 @@ static int fdmmv_impl(int dtype, int kernel, const Mat& X1, const Mat& X2, const
   T sig_scalar;
   const T* sig_dev;
   FLK_TRY(upload_sigma<T>(sigma, sigma_len, L.sigma, &sig_scalar, &sig_dev, stream));
-  const int ld = ld_for(dtype, d);
-  if (L.tc) {
-    FLK_CUDA_TRY(cudaMemsetAsync(L.status, 0, 256, stream));
-    FLK_TRY(tc::prep_images(kernel, X1.ptr, X1.rows, X1.rs, X1.cs, (int)d, (const float*)sig_dev,
-                            (float)sig_scalar, (int)sigma_len, L.s1.r_pad, (float*)L.x1.img_a,
-                            (float*)L.x1.img_b, stream));
-    FLK_TRY(tc::prep_images(kernel, X2.ptr, X2.rows, X2.rs, X2.cs, (int)d, (const float*)sig_dev,
-                            (float)sig_scalar, (int)sigma_len, L.s1.s_pad, (float*)L.x2.img_a,
-                            (float*)L.x2.img_b, stream));
-    count_launch(2);
-  } else {
-    FLK_TRY(run_prep_rows<T>(X1, sig_dev, sig_scalar, (int)sigma_len, L.x1.xs, ld, L.s1.r_pad, L.x1.norms, stream));
-    FLK_TRY(run_prep_rows<T>(X2, sig_dev, sig_scalar, (int)sigma_len, L.x2.xs, ld, L.s1.s_pad, L.x2.norms, stream));
-  }
+  FLK_TRY(prepare_operands<T>(L, kernel, X1, X2, d, sig_dev, sig_scalar, (int)sigma_len, dtype, stream));
   if (has_v) {
     // sweep 1: u = K v (+ w), kept as a padded vector operand
     FLK_TRY(run_prep_vec<T>(v, L.vbuf, L.s1.s_pad, L.s1.tp, L.s1.tt, stream));
-    if (L.tc) {
-      FLK_TRY(run_sweep_tc(kernel, L.s1, L.x1.img_a, L.x2.img_b, d, L.vbuf, L.raw1, L.status, stream, 0));
-    } else {
-      FLK_TRY(run_sweep_simt<T>(kernel, L.s1, L.x1, L.x2, ld, L.vbuf, L.raw1, stream, 0));
-    }
-    FLK_TRY(run_finalize<T>(L.s1, L.raw1, has_w ? &w : nullptr, L.ubuf, 0, 0, t, true, stream));
+    FLK_TRY(sweep_and_finalize<T>(L, kernel, dtype, d, t, L.s1, L.f1, L.x1, L.x2, L.vbuf, L.raw1, L.fraw1,
+                                  has_w ? &w : nullptr, L.ubuf, 0, 0, true, stream, 0));
   } else {
     FLK_TRY(run_prep_vec<T>(w, L.ubuf, L.s1.r_pad, L.s1.tp, L.s1.tt, stream));
   }
   // sweep 2: out = K^T u  (rows = X2, reduction over X1)
-  if (L.tc) {
-    FLK_TRY(run_sweep_tc(kernel, L.s2, L.x2.img_a, L.x1.img_b, d, L.ubuf, L.raw2, L.status, stream, 1));
-  } else {
-    FLK_TRY(run_sweep_simt<T>(kernel, L.s2, L.x2, L.x1, ld, L.ubuf, L.raw2, stream, 1));
-  }
-  FLK_TRY(run_finalize<T>(L.s2, L.raw2, nullptr, out, out_rs, out_cs, t, false, stream));
+  FLK_TRY(sweep_and_finalize<T>(L, kernel, dtype, d, t, L.s2, L.f2, L.x2, L.x1, L.ubuf, L.raw2, L.fraw2, nullptr,
+                                out, out_rs, out_cs, false, stream, 1));
   return FLK_OK;
 }
 

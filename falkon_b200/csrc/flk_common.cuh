@@ -45,8 +45,21 @@ inline int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
 inline int64_t ceil_div(int64_t x, int64_t m) { return (x + m - 1) / m; }
 
 // All padded row counts are multiples of this many rows, so every tile shape used by the
-// SIMT kernel (128 x 128 / 128 x 64) and by the tensor-core kernel (256 x 128) divides them.
-constexpr int64_t kRowPad = 256;
+// SIMT kernel (128 x 128 / 128 x 64) and by the tensor-core kernel (512 x 128) divides them.
+constexpr int64_t kRowPad = 512;
+
+// Device-side gate.  When the tensor-core path is chosen its SIMT alternative is launched behind
+// it; which of the two does the work is decided by a flag the image builder writes in device
+// memory, so the choice costs no host round trip.  A gated kernel returns at once unless
+// (*flag != 0) == want.  flag == nullptr means "always run".
+struct Gate {
+  const int* flag;
+  int want;
+};
+__device__ __forceinline__ bool gate_open(const Gate& g) {
+  if (g.flag == nullptr) return true;
+  return (*reinterpret_cast<const volatile int*>(g.flag) != 0) == (g.want != 0);
+}
 
 // ---------------------------------------------------------------------------------------------
 // Kernel functions on the clamped squared distance (in length-scale units).

@@ -22,7 +22,8 @@ __global__ void __launch_bounds__(256) prep_rows_kernel(const T* __restrict__ X,
                                                         const T* __restrict__ sigma, T sigma_scalar,
                                                         int sigma_len, T* __restrict__ Xs, int ld,
                                                         int64_t n_pad,
-                                                        T* __restrict__ norms) {
+                                                        T* __restrict__ norms, Gate gate) {
+  if (!gate_open(gate)) return;
   __shared__ T tile[kPrepRows][kPrepCols + 1];
   __shared__ T sig[kPrepCols];
   const int tid = threadIdx.x;
@@ -156,7 +157,8 @@ __global__ void __launch_bounds__(256) finalize_kernel(const T* __restrict__ raw
                                                        const T* __restrict__ add, int64_t add_rs,
                                                        int64_t add_cs, T* __restrict__ out,
                                                        int64_t out_rs, int64_t out_cs, int padded_out,
-                                                       int tt) {
+                                                       int tt, Gate gate) {
+  if (!gate_open(gate)) return;
   int64_t total = r_pad * tp;
   for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (int64_t)gridDim.x * blockDim.x) {

@@ -56,6 +56,7 @@ struct SimtArgs {
   int row_tiles;        // ceil(r / BR)
   int n_col_tiles;      // ceil(s / BC)
   int tiles_per_chunk;  // column tiles per chunk
+  Gate gate;            // run only when the gate is open (see flk_common.cuh)
 };
 
 template <typename T, int TT>
@@ -71,6 +72,7 @@ __global__ void __launch_bounds__(256, ((sizeof(T) == 4 && TT == 1) ? 2 : 1)) km
   using Vec = typename C::Vec;
   constexpr int TR = C::TR, TC = C::TC, DK = C::DK, VEC = C::VEC;
   constexpr int BR = 16 * TR, BC = 16 * TC, LD = DK + VEC;
+  if (!gate_open(p.gate)) return;
 
   extern __shared__ __align__(16) unsigned char smem_raw[];
   T* As = reinterpret_cast<T*>(smem_raw);  // [2][BR][LD]

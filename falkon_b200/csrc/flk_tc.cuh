@@ -2,64 +2,87 @@
 //
 //   raw[chunk][i][t] = sum_{j in chunk} k(a_i, b_j) vec[j][t]
 //
-// Idea: the whole exponent of the kernel function is produced by ONE tf32 MMA.  Each data row is
-// pre-scaled by sqrt(alpha)/sigma (alpha depends on the kernel function) and split into a tf32
-// "hi" and "lo" part; the squared norm is split into 2 or 3 tf32 parts.  With the K dimension laid
-// out as
+// Idea: the whole exponent of the kernel function is produced by ONE fp16 MMA with fp32
+// accumulation.  Each data row is pre-scaled by s / sigma (s depends on the kernel function) and
+// split into an fp16 "hi" and an fp16 "lo" part (22 significant bits together); half the squared
+// norm is split into 2 or 3 fp16 parts.  With the K dimension laid out as
 //      A row (output side)    : [ xh | xh | xl | -n1 -n2 (-n3) | 1 1 (1) | 0.. ]
-//      B row (reduction side) : [ 2ch | 2cl | 2ch | 1 1 (1) | -m1 -m2 (-m3) | 0.. ]
-// the fp32 accumulator of  A . B^T  is  2 x.c - |x|^2 - |c|^2 = -alpha * D^2  with fp32-level
-// accuracy (3xTF32: the dropped xl.cl term is below fp32 rounding).  The epilogue then needs only
-// a min/max, one or two MUFU ops and the FMA with `vec` per kernel evaluation, so the FP32 pipe no
-// longer carries the d-long dot product and the MUFU unit becomes the bound.
+//      B row (reduction side) : [ ch | cl | ch | 1 1 (1) | -m1 -m2 (-m3) | 0.. ]
+// the fp32 accumulator of  A . B^T  is  x.c - |x|^2/2 - |c|^2/2 = -(s^2/2) D^2  with fp32-level
+// accuracy (every fp16 x fp16 product is exact in fp32; the dropped xl.cl term is below fp32
+// rounding).  The epilogue then needs only a min/max, one or two MUFU ops and the FMA with `vec`
+// per kernel evaluation: the FP32 pipe no longer carries the d-long dot product, and the MUFU
+// unit (16 lanes per SM) becomes the bound.  Part of the exponentials is therefore evaluated by a
+// degree-5 polynomial on the FMA pipe instead (range reduction with the round-to-integer trick),
+// which runs beside the MUFU unit.
+//
+// fp16 has a narrow exponent: a row whose scaled half squared norm exceeds kNormLimit cannot be
+// represented.  The image builder raises a flag in device memory when it meets such a row; the
+// sweep kernel then does nothing and the caller's SIMT kernels (launched behind it, gated on the
+// same flag) produce the result instead.  No host round trip is involved.
 //
 // Data movement: operands are stored in HBM as ready-made shared-memory images of 128-row tiles
-// (128-byte-swizzled, K-major "core matrix" layout that tcgen05.mma reads), so a tile is one
+// (64-byte-swizzled, K-major "core matrix" layout that tcgen05.mma reads), so a tile is one
 // contiguous bulk copy (cp.async.bulk, the TMA engine, completion on an mbarrier) with no tensor
-// map.  A CTA keeps 256 output rows (two 128-row MMA blocks) resident, streams 128-column B tiles
-// through a ring, and ping-pongs two TMEM accumulators per row block so the MMA of tile j+1
-// overlaps the epilogue of tile j.  Warp roles: warps 0-7 epilogue (one TMEM lane = one output
-// row per thread), warp 8 bulk-copy producer, warp 9 MMA issuer and TMEM owner.
+// map.  A CTA keeps 512 output rows (four 128-row MMA blocks, one 128-column fp32 accumulator each:
+// all 512 TMEM columns) resident and streams 128-column B tiles through a ring.  Sixteen epilogue
+// warps (four per row block, one TMEM lane = one output row per thread) read the accumulator in
+// 32-column pieces, software-pipelined against the evaluation, and hand the accumulator back to
+// the MMA issuer once the second half of it is in registers, so the MMA of tile j+1 of a row
+// block (and the barrier round trips around it) runs under the evaluation of the second half of
+// tile j, and the other three row blocks keep the MUFU and FMA pipes busy meanwhile.
+// Warps 16-19 = MMA issuers, one per row block and per SM sub-partition (a queued tcgen05.mma
+// delays the other warps of its sub-partition, so the issue load is spread evenly; warp 16 also
+// owns the TMEM allocation), warp 20 = bulk-copy producer.
 //
 // Every wait on an mbarrier is bounded; when one gives up the CTA records a code in the status
 // word, stops issuing work, drains its own copies, frees its TMEM and returns.
 #pragma once
+
+#include <cuda_fp16.h>
 
 #include "flk_common.cuh"
 
 namespace flk {
 namespace tc {
 
-constexpr int kRowsPerCta = 256;   // two 128-row MMA blocks
-constexpr int kColsPerTile = 128;  // MMA N
-constexpr int kTileRows = 128;     // rows per operand tile image
-constexpr int kSlabK = 32;         // tf32 elements per 128-byte swizzle row
+constexpr int kRowBlocks = 4;                       // 128-row MMA blocks per CTA
+constexpr int kTileRows = 128;                      // rows per operand tile image (MMA M)
+constexpr int kRowsPerCta = kRowBlocks * kTileRows; // 512
+constexpr int kColsPerTile = 128;                   // MMA N
+constexpr int kSlabK = 32;                          // fp16 elements per 64-byte swizzle row
+constexpr int kMmaK = 16;                           // fp16 elements per MMA K-step
 constexpr int kMaxD = 30;
-constexpr int kThreads = 320;
+constexpr int kEpilogueWarps = 4 * kRowBlocks;
+constexpr int kMmaWarp0 = kEpilogueWarps;                // warps 16..19: MMA issuer of row block (warp - 16)
+constexpr int kProducerWarp = kMmaWarp0 + kRowBlocks;    // warp 20
+constexpr int kThreads = (kEpilogueWarps + kRowBlocks + 1) * 32;
+constexpr int kVecStages = 4;                       // ring of vector tiles
 constexpr uint64_t kWaitTimeoutNs = 1000000000ull;  // every device-side wait gives up after 1 s
+constexpr float kNormLimit = 60000.0f;              // largest half squared norm an image may carry
+#ifndef FLK_TC_POLY
+#define FLK_TC_POLY 8
+#endif
+constexpr int kPolyCols = FLK_TC_POLY;  // of every 32 accumulator columns, how many take the FMA-pipe exponential
+
+// words of the 256-byte status block at the front of the workspace
+enum { kStatusTimeout = 0, kStatusRange = 1 };
 
 inline bool supports_d(int64_t d) { return d >= 1 && d <= kMaxD; }
-// number of tf32 pieces the squared norm is split into (3 when it costs no extra MMA K-step)
-inline int norm_pieces(int64_t d) { return (round_up(3 * d + 6, 8) == round_up(3 * d + 4, 8)) ? 3 : 2; }
+// number of fp16 pieces half the squared norm is split into (3 when it costs no extra MMA K-step)
+inline int norm_pieces(int64_t d) { return (round_up(3 * d + 6, kMmaK) == round_up(3 * d + 4, kMmaK)) ? 3 : 2; }
 inline int used_k(int64_t d) { return (int)(3 * d + 2 * norm_pieces(d)); }
-inline int k_steps(int64_t d) { return (int)(round_up(used_k(d), 8) / 8); }
+inline int k_steps(int64_t d) { return (int)(round_up(used_k(d), kMmaK) / kMmaK); }
 inline int64_t padded_k(int64_t d) { return round_up(used_k(d), kSlabK); }
 inline int n_slabs(int64_t d) { return (int)(padded_k(d) / kSlabK); }
 
-// alpha such that the accumulator equals -alpha * D^2 (D^2 = squared distance in length-scale units)
-inline double alpha_for(int kernel) {
-  const double l2e = 1.4426950408889634;
-  switch (kernel) {
-    case FLK_GAUSSIAN: return 0.5 * l2e;
-    case FLK_LAPLACIAN: return l2e * l2e;
-    case FLK_MATERN15: return 3.0 * l2e * l2e;
-    default: return 5.0 * l2e * l2e;
-  }
-}
+// s^2 such that the accumulator equals -(s^2 / 2) D^2 (D^2 = squared distance in length-scale
+// units): Gaussian -> -(log2(e) / 2) D^2 (ready for ex2); the others -> -D^2.
+inline double scale_sq_for(int kernel) { return kernel == FLK_GAUSSIAN ? 1.4426950408889634 : 2.0; }
 
-// float offset of element (row r, k index e) inside a 128-row tile image
+// fp16-element offset of element (row r, k index e) inside a 128-row tile image
 __host__ __device__ inline int image_offset(int r, int e) {
-  return (e >> 5) * (kTileRows * kSlabK) + r * kSlabK + ((((e & 31) >> 2) ^ (r & 7)) << 2) + (e & 3);
+  return (e >> 5) * (kTileRows * kSlabK) + r * kSlabK + ((((e & 31) >> 3) ^ ((r >> 1) & 3)) << 3) + (e & 7);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -67,10 +90,18 @@ __host__ __device__ inline int image_offset(int r, int e) {
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
-__device__ __forceinline__ float to_tf32(float x) {
-  uint32_t y;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(y) : "f"(x));
-  return __uint_as_float(y);
+// One lane of a converged warp.  Issuing tcgen05.mma / commit / bulk copies under this predicate
+// (instead of `lane == 0` inside a divergent branch) lets the compiler keep descriptors and
+// addresses in uniform registers; a divergent single-lane issue path costs well over a hundred
+// cycles per MMA.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred = 0;
+  asm volatile(
+      "{\n\t.reg .b32 rx;\n\t.reg .pred px;\n\t"
+      "elect.sync rx|px, 0xFFFFFFFF;\n\t"
+      "selp.b32 %0, 1, 0, px;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
 }
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -98,11 +129,18 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-// Bounded wait: false when the phase did not complete within kWaitTimeoutNs.
+// Bounded wait: false when the phase did not complete within kWaitTimeoutNs.  A waiting warp backs
+// off with a short nanosleep between probes: a warp that spins on a barrier competes for issue
+// slots with the epilogue warps of its SM sub-partition (measured: the sub-partition hosting the
+// spinning MMA warp ran its epilogue warps almost 2x slower and set the pace of the whole CTA).
+#ifndef FLK_TC_BACKOFF_NS
+#define FLK_TC_BACKOFF_NS 20
+#endif
 __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity) {
   const uint64_t t0 = global_timer_ns();
-  for (uint32_t it = 0; it < (1u << 30); ++it) {
+  for (uint32_t it = 0; it < (1u << 28); ++it) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (FLK_TC_BACKOFF_NS > 0) __nanosleep(FLK_TC_BACKOFF_NS);
     if ((it & 63u) == 63u && global_timer_ns() - t0 > kWaitTimeoutNs) return false;
   }
   return false;
@@ -133,60 +171,116 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-__device__ __forceinline__ void mma_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                         uint32_t accumulate) {
+__device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                        uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// The two wrappers below carry extra operands whose only purpose is to pin the instruction order the
+// software pipeline needs (the compiler is otherwise free to move independent arithmetic across
+// them): a load is issued BEFORE the evaluation of the piece that is already in registers, and the
+// wait for it comes AFTER that evaluation.
+//   tmem_ld32(taddr, dst, held): issues the load into `dst`; `held` (the piece about to be
+//     evaluated) is tied as read-write, so its evaluation cannot be scheduled above the issue.
+//   tmem_ld_wait_on(dst, acc): waits for the load into `dst`; the running sums `acc` are tied as
+//     read-write, so every evaluation that feeds them is scheduled above the wait.
+#define FLK_R32_OUT(r)                                                                                         \
+  "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),  \
+      "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),   \
+      "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),  \
+      "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+#define FLK_R32_INOUT(r)                                                                                       \
+  "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),  \
+      "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]),   \
+      "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]),  \
+      "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+#define FLK_TMEM_LD32_TEXT                                                                   \
+  "tcgen05.ld.sync.aligned.32x32b.x32.b32 "                                                  \
+  "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "                  \
+  "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
 
-// K-major, 128-byte swizzle shared-memory matrix descriptor (8-row groups 1024 bytes apart).
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(FLK_TMEM_LD32_TEXT : FLK_R32_OUT(r) : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32], uint32_t (&held)[32]) {
+  // operands 0-31 = destination, 32 = address, 33.. = the held piece (tied only)
+  asm volatile(FLK_TMEM_LD32_TEXT
+               : FLK_R32_OUT(r)
+               : "r"(taddr), "r"(held[0]), "r"(held[4]), "r"(held[8]), "r"(held[12]), "r"(held[16]), "r"(held[20]),
+                 "r"(held[24]), "r"(held[28])
+               : "memory");
+}
+template <int NACC>
+__device__ __forceinline__ void tmem_ld_wait_on(uint32_t (&r)[32], float (&acc)[NACC]);
+template <>
+__device__ __forceinline__ void tmem_ld_wait_on<4>(uint32_t (&r)[32], float (&acc)[4]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : FLK_R32_INOUT(r), "+f"(acc[0]), "+f"(acc[1]), "+f"(acc[2]), "+f"(acc[3])
+               :
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait_on(uint32_t (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" : FLK_R32_INOUT(r) : : "memory");
+}
+
+// K-major, 64-byte swizzle shared-memory matrix descriptor (8-row groups 512 bytes apart).
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
   uint64_t desc = 0;
   desc |= (uint64_t)((smem_addr >> 4) & 0x3FFF);  // start address
   desc |= (uint64_t)1 << 16;                      // leading byte offset (unused for swizzled K-major)
-  desc |= (uint64_t)(1024 >> 4) << 32;            // stride byte offset between 8-row groups
+  desc |= (uint64_t)(512 >> 4) << 32;             // stride byte offset between 8-row groups
   desc |= (uint64_t)1 << 46;                      // descriptor version (sm_100)
-  desc |= (uint64_t)2 << 61;                      // SWIZZLE_128B
+  desc |= (uint64_t)4 << 61;                      // SWIZZLE_64B
   return desc;
 }
-// tf32 x tf32 -> f32, M = 128, N = 128, both operands K-major
-constexpr uint32_t kInstrDesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(kColsPerTile >> 3) << 17) |
-                                ((uint32_t)(128 >> 4) << 24);
+// fp16 x fp16 -> f32, M = 128, N = 128, both operands K-major
+constexpr uint32_t kInstrDesc = (1u << 4) | ((uint32_t)(kColsPerTile >> 3) << 17) | ((uint32_t)(kTileRows >> 4) << 24);
 
 // ---------------------------------------------------------------------------------------------
-// Kernel functions on the accumulator (= -alpha D^2)
+// Kernel functions on the accumulator
 // ---------------------------------------------------------------------------------------------
-template <int KT>
+// 2^x for x <= 0 on the FMA pipe: n = round(x) through the 1.5 * 2^23 trick, degree-5 minimax
+// polynomial of 2^f on f = x - n in [-1/2, 1/2] (relative error 2.4e-7), exponent patched in with
+// integer arithmetic.  x is clamped at -126 so the patched exponent never wraps.
+__device__ __forceinline__ float ex2_fma(float x) {
+  x = fmaxf(x, -126.0f);
+  const float t = x + 12582912.0f;
+  const float n = t - 12582912.0f;
+  const float f = x - n;
+  float p = 0.001327647129073739f;
+  p = fmaf(p, f, 0.009675540961325169f);
+  p = fmaf(p, f, 0.05550713092088699f);
+  p = fmaf(p, f, 0.24022120237350464f);
+  p = fmaf(p, f, 0.6931469440460205f);
+  p = fmaf(p, f, 1.0000001192092896f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+
+// POLY selects the FMA-pipe exponential (Gaussian only; the other kernel functions are bound by
+// their two MUFU ops and a longer FMA tail, and always take the MUFU path).
+template <int KT, bool POLY>
 __device__ __forceinline__ float eval_acc(float acc) {
   if (KT == FLK_GAUSSIAN) {
+    // acc = -(log2(e) / 2) D^2.  Rounding can leave it a hair above zero for coincident points; the
+    // reference clamps D^2 at 1e-20 (k <= 1), hence the min.
+    if (POLY) return ex2_fma(fminf(acc, 0.0f));
     return ex2_approx(fminf(acc, 0.0f));
   } else {
-    const float q = sqrt_approx(fmaxf(-acc, 0.0f));  // q = c * D * log2(e), c = 1, sqrt(3), sqrt(5)
-    const float e = ex2_approx(-q);
-    if (KT == FLK_LAPLACIAN) return e;
-    const float s = q * 0.6931471805599453f;
-    if (KT == FLK_MATERN15) return fmaf(q, 0.6931471805599453f, 1.0f) * e;
-    return fmaf(s, fmaf(s, 1.0f / 3.0f, 1.0f), 1.0f) * e;
+    const float dist = sqrt_approx(fmaxf(-acc, 0.0f));  // acc = -D^2
+    if (KT == FLK_LAPLACIAN) return ex2_approx(dist * (-kLog2e));
+    if (KT == FLK_MATERN15) {
+      const float s = dist * 1.7320508075688772f;
+      return (1.0f + s) * ex2_approx(s * (-kLog2e));
+    }
+    const float s = dist * 2.23606797749979f;
+    return fmaf(s, fmaf(s, 1.0f / 3.0f, 1.0f), 1.0f) * ex2_approx(s * (-kLog2e));
   }
 }
 
@@ -197,12 +291,12 @@ __device__ __forceinline__ float eval_acc(float acc) {
 // is coalesced, builds the swizzled image(s) in shared memory, and writes them out linearly.
 __global__ void __launch_bounds__(128) prep_images_kernel(const float* __restrict__ X, int64_t n, int64_t rs,
                                                           int64_t cs, int d, const float* __restrict__ sigma,
-                                                          float sigma_scalar, int sigma_len, float sqrt_alpha,
-                                                          int kp, int npieces, float* __restrict__ img_a,
-                                                          float* __restrict__ img_b) {
-  extern __shared__ __align__(16) float prep_smem[];
-  float* xin = prep_smem;                 // [128][33] scaled inputs
-  float* img = prep_smem + 128 * 33;      // [128 * kp]
+                                                          float sigma_scalar, int sigma_len, float scale,
+                                                          int kp, int npieces, __half* __restrict__ img_a,
+                                                          __half* __restrict__ img_b, int* __restrict__ status) {
+  extern __shared__ __align__(16) unsigned char prep_smem_raw[];
+  float* xin = reinterpret_cast<float*>(prep_smem_raw);            // [128][33] scaled inputs
+  __half* img = reinterpret_cast<__half*>(xin + kTileRows * 33);   // [128 * kp]
   __shared__ float sig[32];
   const int tid = threadIdx.x;
   const int64_t row0 = (int64_t)blockIdx.x * kTileRows;
@@ -223,76 +317,83 @@ __global__ void __launch_bounds__(128) prep_images_kernel(const float* __restric
   __syncthreads();
   const int r = tid;
   const bool live = (row0 + r) < n;
+  // squared norm of the value the two fp16 parts actually represent (keeps coincident points at
+  // an accumulator of -|lo|^2 <= 0 up to rounding)
   double nrm = 0.0;
+  bool out_of_range = false;
   for (int k = 0; k < d; ++k) {
-    float xs = xin[r * 33 + k] / sig[k];  // x / sigma, rounded as in the reference
-    float xt = xs * sqrt_alpha;
+    const float xs = xin[r * 33 + k] / sig[k];  // x / sigma, rounded as in the reference
+    float xt = xs * scale;
+    if (!(fabsf(xt) <= 400.0f)) {  // also catches NaN / inf; 400^2 / 2 > kNormLimit
+      out_of_range = true;
+      xt = 0.0f;
+    }
     xin[r * 33 + k] = xt;
-    nrm += (double)xt * (double)xt;
+    const float hi = __half2float(__float2half_rn(xt));
+    const float lo = __half2float(__float2half_rn(xt - hi));
+    const double rep = (double)hi + (double)lo;
+    nrm += rep * rep;
   }
+  double half_norm = 0.5 * nrm;
+  if (half_norm > (double)kNormLimit) {
+    out_of_range = true;
+    half_norm = 0.0;
+  }
+  if (out_of_range && live) atomicOr(status + kStatusRange, 1);
   float piece[3];
   {
-    double rem = nrm;
+    double rem = half_norm;
     for (int i = 0; i < 3; ++i) {
-      float p = (i < npieces) ? to_tf32((float)rem) : 0.0f;
-      piece[i] = p;
-      rem -= (double)p;
+      const float pc = (i < npieces) ? __half2float(__float2half_rn((float)rem)) : 0.0f;
+      piece[i] = pc;
+      rem -= (double)pc;
     }
   }
   const int tile_elems = kTileRows * kp;
+  const __half one = __float2half_rn(1.0f);
   for (int which = 0; which < 2; ++which) {
-    float* dst = which == 0 ? img_a : img_b;
+    __half* dst = which == 0 ? img_a : img_b;
     if (dst == nullptr) continue;  // uniform across the block
-    for (int idx = tid; idx < tile_elems; idx += 128) img[idx] = 0.0f;
+    {
+      uint32_t* z = reinterpret_cast<uint32_t*>(img);
+      for (int idx = tid; idx < tile_elems / 2; idx += 128) z[idx] = 0u;
+    }
     __syncthreads();
     if (live) {
       for (int k = 0; k < d; ++k) {
         const float xt = xin[r * 33 + k];
-        const float hi = to_tf32(xt);
-        const float lo = to_tf32(xt - hi);
-        if (which == 0) {
-          img[image_offset(r, k)] = hi;
-          img[image_offset(r, d + k)] = hi;
-          img[image_offset(r, 2 * d + k)] = lo;
-        } else {
-          img[image_offset(r, k)] = 2.0f * hi;
-          img[image_offset(r, d + k)] = 2.0f * lo;
-          img[image_offset(r, 2 * d + k)] = 2.0f * hi;
-        }
+        const __half hi = __float2half_rn(xt);
+        const __half lo = __float2half_rn(xt - __half2float(hi));
+        img[image_offset(r, k)] = hi;
+        img[image_offset(r, d + k)] = which == 0 ? hi : lo;
+        img[image_offset(r, 2 * d + k)] = which == 0 ? lo : hi;
       }
       for (int i = 0; i < npieces; ++i) {
         const int e_norm = 3 * d + (which == 0 ? 0 : npieces) + i;
         const int e_one = 3 * d + (which == 0 ? npieces : 0) + i;
-        img[image_offset(r, e_norm)] = -piece[i];
-        img[image_offset(r, e_one)] = 1.0f;
+        img[image_offset(r, e_norm)] = __float2half_rn(-piece[i]);
+        img[image_offset(r, e_one)] = one;
       }
     }
     __syncthreads();
-    float4* out4 = reinterpret_cast<float4*>(dst + (int64_t)blockIdx.x * tile_elems);
-    const float4* in4 = reinterpret_cast<const float4*>(img);
-    for (int idx = tid; idx < tile_elems / 4; idx += 128) out4[idx] = in4[idx];
+    uint4* out4 = reinterpret_cast<uint4*>(dst + (int64_t)blockIdx.x * tile_elems);
+    const uint4* in4 = reinterpret_cast<const uint4*>(img);
+    for (int idx = tid; idx < tile_elems / 8; idx += 128) out4[idx] = in4[idx];
     __syncthreads();
   }
 }
 
 inline int prep_images(int kernel, const void* X, int64_t n, int64_t rs, int64_t cs, int d, const float* sigma_dev,
-                       float sigma_scalar, int sigma_len, int64_t rows_pad, float* img_a, float* img_b,
+                       float sigma_scalar, int sigma_len, int64_t rows_pad, void* img_a, void* img_b, int* status,
                        cudaStream_t stream) {
   const int kp = (int)padded_k(d);
-  const size_t smem = sizeof(float) * (size_t)(128 * 33 + kTileRows * kp);
-  static bool configured[16] = {false};
-  int dev = 0;
-  FLK_CUDA_TRY(cudaGetDevice(&dev));
-  if (dev >= 16 || !configured[dev]) {
-    FLK_CUDA_TRY(cudaFuncSetAttribute(prep_images_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      (int)(sizeof(float) * (128 * 33 + kTileRows * 96))));
-    if (dev < 16) configured[dev] = true;
-  }
-  const float sqrt_alpha = (float)sqrt(alpha_for(kernel));
+  const size_t smem = sizeof(float) * (size_t)(kTileRows * 33) + sizeof(__half) * (size_t)(kTileRows * kp);
+  const float scale = (float)sqrt(scale_sq_for(kernel));
   const int blocks = (int)(rows_pad / kTileRows);
   prep_images_kernel<<<blocks, 128, smem, stream>>>(reinterpret_cast<const float*>(X), n, rs, cs, d, sigma_dev,
-                                                    sigma_scalar, sigma_len, sqrt_alpha, kp, norm_pieces(d), img_a,
-                                                    img_b);
+                                                    sigma_scalar, sigma_len, scale, kp, norm_pieces(d),
+                                                    reinterpret_cast<__half*>(img_a),
+                                                    reinterpret_cast<__half*>(img_b), status);
   FLK_CUDA_TRY(cudaGetLastError());
   return FLK_OK;
 }
@@ -301,59 +402,132 @@ inline int prep_images(int kernel, const void* X, int64_t n, int64_t rs, int64_t
 // Main sweep kernel
 // ---------------------------------------------------------------------------------------------
 struct SweepArgs {
-  const float* img_a;  // [r_pad / 128] tile images (output side)
-  const float* img_b;  // [s_pad / 128] tile images (reduction side)
-  const float* vec;    // [t_chunks][s_pad][TT]
-  float* raw;          // [n_chunks][r_pad][tp]
-  int* status;         // device status word (0 = clean)
+  const __half* img_a;  // [r_pad / 128] tile images (output side)
+  const __half* img_b;  // [s_pad / 128] tile images (reduction side)
+  const float* vec;     // [t_chunks][s_pad][TT]
+  float* raw;           // [n_chunks][r_pad][tp]
+  int* status;          // device status block (word kStatusTimeout, word kStatusRange)
   int tp;
   int64_t r_pad;
   int64_t s_pad;
-  int row_tiles;        // ceil(r / 256)
+  int row_tiles;        // ceil(r / 512)
   int n_col_tiles;      // ceil(s / 128)
   int tiles_per_chunk;
-  int ksteps;           // MMA K-steps (8 tf32 each) actually carrying data
+  int ksteps;           // MMA K-steps (16 fp16 each) actually carrying data
 };
 
 template <int NSLAB>
 struct TcCfg {
   static constexpr int KP = NSLAB * kSlabK;
-  static constexpr int STAGES = NSLAB == 3 ? 2 : (NSLAB == 2 ? 3 : 6);
-  static constexpr int TILE_BYTES = kTileRows * KP * 4;   // one operand tile image
-  static constexpr int A_BYTES = 2 * TILE_BYTES;          // 256 resident rows
+  static constexpr int TILE_BYTES = kTileRows * KP * 2;       // one operand tile image
+  static constexpr int A_BYTES = kRowBlocks * TILE_BYTES;     // 512 resident rows
+  static constexpr int STAGES = NSLAB == 3 ? 4 : (NSLAB == 2 ? 6 : 12);
 };
 
 template <int NSLAB, int TT>
 constexpr size_t tc_smem_bytes() {
   using C = TcCfg<NSLAB>;
   return 1024 /* alignment slack */ + (size_t)C::A_BYTES + (size_t)C::STAGES * C::TILE_BYTES +
-         (size_t)C::STAGES * kColsPerTile * TT * 4 + 256 /* barriers + tmem pointer */;
+         (size_t)kVecStages * kColsPerTile * TT * 4 + 512 /* barriers + tmem pointer */;
 }
 
 // error codes written to the status word: role * 16 + which wait
 enum { kErrProducer = 0x10, kErrMma = 0x20, kErrEpilogue = 0x30 };
 
+// Number of independent accumulation chains per output column (breaks the FMA dependency chain).
+template <int TT>
+struct EpiChains {
+  static constexpr int N = TT == 1 ? 4 : (TT == 2 ? 2 : 1);
+};
+
+// Is accumulator column c (0..31 within a 32-column piece) evaluated on the FMA pipe?  The
+// polynomial columns are spread evenly so both pipes have work throughout the piece.
+template <int KT>
+__host__ __device__ constexpr bool poly_col(int c) {
+  return KT == FLK_GAUSSIAN && kPolyCols > 0 && ((c + 1) * kPolyCols / 32 != c * kPolyCols / 32);
+}
+
+template <int KT, int C>
+__device__ __forceinline__ float eval_col(uint32_t bits) {
+  return eval_acc<KT, poly_col<KT>(C)>(__uint_as_float(bits));
+}
+
+// Kernel function + contraction for 32 accumulator columns held in registers.
+// `vsm` points at the vector-tile entries of the first of those columns.
+template <int KT, int TT, int C0 = 0>
+__device__ __forceinline__ void epilogue_32(const uint32_t (&r)[32], const float* vsm,
+                                            float (&oacc)[EpiChains<TT>::N][TT]) {
+  if constexpr (C0 < 32) {
+    if constexpr (TT == 1) {
+      const float4 v4 = *reinterpret_cast<const float4*>(vsm + C0);
+      oacc[0][0] = fmaf(eval_col<KT, C0 + 0>(r[C0 + 0]), v4.x, oacc[0][0]);
+      oacc[1][0] = fmaf(eval_col<KT, C0 + 1>(r[C0 + 1]), v4.y, oacc[1][0]);
+      oacc[2][0] = fmaf(eval_col<KT, C0 + 2>(r[C0 + 2]), v4.z, oacc[2][0]);
+      oacc[3][0] = fmaf(eval_col<KT, C0 + 3>(r[C0 + 3]), v4.w, oacc[3][0]);
+    } else if constexpr (TT == 2) {
+      const float4 va = *reinterpret_cast<const float4*>(vsm + C0 * 2);
+      const float4 vb = *reinterpret_cast<const float4*>(vsm + C0 * 2 + 4);
+      const float k0 = eval_col<KT, C0 + 0>(r[C0 + 0]);
+      const float k1 = eval_col<KT, C0 + 1>(r[C0 + 1]);
+      const float k2 = eval_col<KT, C0 + 2>(r[C0 + 2]);
+      const float k3 = eval_col<KT, C0 + 3>(r[C0 + 3]);
+      oacc[0][0] = fmaf(k0, va.x, oacc[0][0]);
+      oacc[0][1] = fmaf(k0, va.y, oacc[0][1]);
+      oacc[1][0] = fmaf(k1, va.z, oacc[1][0]);
+      oacc[1][1] = fmaf(k1, va.w, oacc[1][1]);
+      oacc[0][0] = fmaf(k2, vb.x, oacc[0][0]);
+      oacc[0][1] = fmaf(k2, vb.y, oacc[0][1]);
+      oacc[1][0] = fmaf(k3, vb.z, oacc[1][0]);
+      oacc[1][1] = fmaf(k3, vb.w, oacc[1][1]);
+    } else {
+      static_assert(TT == 1 || TT == 2 || TT % 4 == 0, "TT must be 1, 2 or a multiple of 4");
+      const float kv[4] = {eval_col<KT, C0 + 0>(r[C0 + 0]), eval_col<KT, C0 + 1>(r[C0 + 1]),
+                           eval_col<KT, C0 + 2>(r[C0 + 2]), eval_col<KT, C0 + 3>(r[C0 + 3])};
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+#pragma unroll
+        for (int t4 = 0; t4 < TT; t4 += 4) {
+          const float4 v4 = *reinterpret_cast<const float4*>(vsm + (C0 + c) * TT + t4);
+          oacc[0][t4 + 0] = fmaf(kv[c], v4.x, oacc[0][t4 + 0]);
+          oacc[0][t4 + 1] = fmaf(kv[c], v4.y, oacc[0][t4 + 1]);
+          oacc[0][t4 + 2] = fmaf(kv[c], v4.z, oacc[0][t4 + 2]);
+          oacc[0][t4 + 3] = fmaf(kv[c], v4.w, oacc[0][t4 + 3]);
+        }
+      }
+    }
+    epilogue_32<KT, TT, C0 + 4>(r, vsm, oacc);
+  }
+}
+
+// Epilogue warp w: TMEM lane quarter q = w % 4 (hardware rule: a warp may only touch lanes
+// 32 (w % 4) .. +31; warps with the same w % 4 also share an SM sub-partition, so each row block
+// has one warp on every sub-partition), row block rb = w / 4.
 template <int KT, int NSLAB, int TT>
 __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) {
   using C = TcCfg<NSLAB>;
   constexpr int S = C::STAGES;
+  constexpr int VS = kVecStages;
+  constexpr int NCH = EpiChains<TT>::N;
   extern __shared__ unsigned char tc_smem_raw[];
-  // 1024-byte alignment is required by the 128-byte swizzle atoms
+  // the swizzle atoms want a 512-byte aligned base; 1024 keeps every tile image on a round address
   const uint32_t raw_addr = smem_u32(tc_smem_raw);
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
   unsigned char* smem = tc_smem_raw + pad;
   unsigned char* a_smem = smem;
   unsigned char* b_smem = smem + C::A_BYTES;
-  float* vs = reinterpret_cast<float*>(b_smem + S * C::TILE_BYTES);  // [S][128][TT]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(vs) + S * kColsPerTile * TT * 4);
-  // barrier map: [0] a_full, [1..S] b_full, [1+S..2S] b_empty, then tmem_full[4], tmem_empty[4]
+  float* vs = reinterpret_cast<float*>(b_smem + S * C::TILE_BYTES);  // [VS][128][TT]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(vs) + VS * kColsPerTile * TT * 4);
+  // barrier map: a_full | b_full[S] | b_empty[S] | v_full[VS] | v_empty[VS] | t_full[4] | t_empty[4]
   uint64_t* bar_a_full = bars;
   uint64_t* bar_b_full = bars + 1;
-  uint64_t* bar_b_empty = bars + 1 + S;
-  uint64_t* bar_t_full = bars + 1 + 2 * S;
-  uint64_t* bar_t_empty = bars + 5 + 2 * S;
-  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 9 + 2 * S);
+  uint64_t* bar_b_empty = bar_b_full + S;
+  uint64_t* bar_v_full = bar_b_empty + S;
+  uint64_t* bar_v_empty = bar_v_full + VS;
+  uint64_t* bar_t_full = bar_v_empty + VS;
+  uint64_t* bar_t_empty = bar_t_full + kRowBlocks;
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bar_t_empty + kRowBlocks);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
+  static_assert((1 + 2 * S + 2 * VS + 2 * kRowBlocks) * 8 + 8 <= 512, "barrier block overflows its 512 bytes");
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
@@ -364,26 +538,34 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
   const int tile_end = min(tile_begin + p.tiles_per_chunk, p.n_col_tiles);
   const int ntiles = tile_end - tile_begin;
 
-  // a CTA of this launch already gave up: do not start (keeps a failed launch short)
-  __shared__ int launch_already_failed;
-  if (tid == 0) launch_already_failed = (*reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
+  // Do not start when a CTA of this launch already gave up (keeps a failed launch short) or when
+  // the image builder found rows fp16 cannot carry (the SIMT kernels take over).
+  __shared__ int skip_launch;
+  if (tid == 0) {
+    const volatile int* st = reinterpret_cast<const volatile int*>(p.status);
+    skip_launch = (st[kStatusTimeout] != 0 || st[kStatusRange] != 0) ? 1 : 0;
+  }
   __syncthreads();
-  if (launch_already_failed) return;
+  if (skip_launch) return;
 
   if (tid == 0) {
     mbar_init(smem_u32(bar_a_full), 1);
     for (int s = 0; s < S; ++s) {
       mbar_init(smem_u32(bar_b_full + s), 1);
-      mbar_init(smem_u32(bar_b_empty + s), 1 + 8);  // MMA commit + one arrive per epilogue warp
+      mbar_init(smem_u32(bar_b_empty + s), kRowBlocks);  // one MMA commit per row-block issuer
     }
-    for (int i = 0; i < 4; ++i) {
+    for (int s = 0; s < VS; ++s) {
+      mbar_init(smem_u32(bar_v_full + s), 1);
+      mbar_init(smem_u32(bar_v_empty + s), kEpilogueWarps);  // one arrive per epilogue warp
+    }
+    for (int i = 0; i < kRowBlocks; ++i) {
       mbar_init(smem_u32(bar_t_full + i), 1);
-      mbar_init(smem_u32(bar_t_empty + i), 4);  // the 4 warps of the row block's warpgroup
+      mbar_init(smem_u32(bar_t_empty + i), 4);  // the four warps of that row block
     }
     *abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 9) {
+  if (warp == kMmaWarp0) {
     tmem_alloc(smem_u32(tmem_ptr), 512);
     tmem_relinquish();
   }
@@ -392,153 +574,142 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr;
 
-  if (warp == 8) {
+  if (warp == kProducerWarp) {
     // ------------------------------ bulk-copy producer ------------------------------
-    if (lane == 0) {
-      const float* a_src = p.img_a + (int64_t)row_tile * 2 * (kTileRows * C::KP);
+    // The whole warp walks the loop (converged); one elected lane issues the copies.
+    if (elect_one()) {
+      const __half* a_src = p.img_a + (int64_t)row_tile * kRowBlocks * (kTileRows * C::KP);
       mbar_expect_tx(smem_u32(bar_a_full), C::A_BYTES);
-      bulk_copy_g2s(smem_u32(a_smem), a_src, C::TILE_BYTES, smem_u32(bar_a_full));
-      bulk_copy_g2s(smem_u32(a_smem) + C::TILE_BYTES, a_src + kTileRows * C::KP, C::TILE_BYTES,
-                    smem_u32(bar_a_full));
-      const float* vec_base = p.vec + (int64_t)tchunk * p.s_pad * TT;
-      for (int j = 0; j < ntiles; ++j) {
-        const int stage = j % S;
-        if (*abort_flag) break;
-        if (!mbar_wait(smem_u32(bar_b_empty + stage), ((j / S) & 1) ^ 1)) {
-          atomicExch(p.status, kErrProducer | 1);
-          *abort_flag = 1;
-          break;
-        }
+      for (int rb = 0; rb < kRowBlocks; ++rb)
+        bulk_copy_g2s(smem_u32(a_smem) + rb * C::TILE_BYTES, a_src + rb * (kTileRows * C::KP), C::TILE_BYTES,
+                      smem_u32(bar_a_full));
+    }
+    __syncwarp();
+    const float* vec_base = p.vec + (int64_t)tchunk * p.s_pad * TT;
+    for (int j = 0; j < ntiles; ++j) {
+      const int stage = j % S, vstage = j % VS;
+      if (*abort_flag) break;
+      if (!mbar_wait(smem_u32(bar_b_empty + stage), ((j / S) & 1) ^ 1) ||
+          !mbar_wait(smem_u32(bar_v_empty + vstage), ((j / VS) & 1) ^ 1)) {
+        if (lane == 0) atomicExch(p.status + kStatusTimeout, kErrProducer | 1);
+        *abort_flag = 1;
+        break;
+      }
+      if (elect_one()) {
         const int64_t ct = tile_begin + j;
         const uint32_t bar = smem_u32(bar_b_full + stage);
-        mbar_expect_tx(bar, C::TILE_BYTES + kColsPerTile * TT * 4);
+        mbar_expect_tx(bar, C::TILE_BYTES);
         bulk_copy_g2s(smem_u32(b_smem) + stage * C::TILE_BYTES, p.img_b + ct * (kTileRows * C::KP), C::TILE_BYTES,
                       bar);
-        bulk_copy_g2s(smem_u32(vs) + stage * kColsPerTile * TT * 4, vec_base + ct * kColsPerTile * TT,
-                      kColsPerTile * TT * 4, bar);
+        const uint32_t vbar = smem_u32(bar_v_full + vstage);
+        mbar_expect_tx(vbar, kColsPerTile * TT * 4);
+        bulk_copy_g2s(smem_u32(vs) + vstage * kColsPerTile * TT * 4, vec_base + ct * kColsPerTile * TT,
+                      kColsPerTile * TT * 4, vbar);
       }
+      __syncwarp();
     }
-  } else if (warp == 9) {
-    // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0) {
-      bool ok = mbar_wait(smem_u32(bar_a_full), 0);
-      if (!ok) {
-        atomicExch(p.status, kErrMma | 1);
-        *abort_flag = 1;
-      }
-      const uint64_t a_desc0 = make_smem_desc(smem_u32(a_smem));
-      for (int j = 0; ok && j < ntiles; ++j) {
-        const int stage = j % S, buf = j & 1;
-        if (*abort_flag) break;
-        if (!mbar_wait(smem_u32(bar_b_full + stage), (j / S) & 1)) {
-          atomicExch(p.status, kErrMma | 2);
-          *abort_flag = 1;
-          break;
-        }
-        const uint64_t b_desc0 = make_smem_desc(smem_u32(b_smem) + stage * C::TILE_BYTES);
-        for (int rb = 0; rb < 2; ++rb) {
-          if (!mbar_wait(smem_u32(bar_t_empty + rb * 2 + buf), ((j >> 1) & 1) ^ 1)) {
-            atomicExch(p.status, kErrMma | 3);
-            *abort_flag = 1;
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          const uint32_t d_tmem = tmem_base + (uint32_t)((rb * 2 + buf) * kColsPerTile);
-          for (int ks = 0; ks < p.ksteps; ++ks) {
-            // 32 bytes (8 tf32) per K-step inside a 128-byte swizzle row; 16 KiB per 32-wide slab
-            const uint64_t koff = (uint64_t)((ks >> 2) * ((kTileRows * 128) >> 4) + (ks & 3) * 2);
-            const uint64_t adesc = a_desc0 + (uint64_t)(rb * (C::TILE_BYTES >> 4)) + koff;
-            const uint64_t bdesc = b_desc0 + koff;
-            mma_tf32(d_tmem, adesc, bdesc, kInstrDesc, ks > 0 ? 1u : 0u);
-          }
-          mma_commit(smem_u32(bar_t_full + rb * 2 + buf));
-        }
-        if (!ok) break;
-        mma_commit(smem_u32(bar_b_empty + stage));
-      }
+  } else if (warp >= kMmaWarp0) {
+    // ------------------------------ MMA issuers ------------------------------
+    // One issuer warp per row block, each on its own SM sub-partition: a queued tcgen05.mma holds
+    // up the other warps of its sub-partition, so the issue work is spread evenly over the four.
+    // All lanes wait on the barriers together; one elected lane issues the MMAs and commits.
+    const int rb = warp - kMmaWarp0;
+    bool ok = mbar_wait(smem_u32(bar_a_full), 0);
+    if (!ok) {
+      if (lane == 0) atomicExch(p.status + kStatusTimeout, kErrMma | 1);
+      *abort_flag = 1;
     }
-  } else {
-    // ------------------------------ epilogue (warps 0-7) ------------------------------
-    const int rb = warp >> 2;  // row block = warpgroup
-    const int q = warp & 3;    // TMEM lane quarter this warp may access
-    float oacc[TT];
-#pragma unroll
-    for (int t = 0; t < TT; ++t) oacc[t] = 0.0f;
-    bool ok = true;
-    for (int j = 0; j < ntiles; ++j) {
-      const int stage = j % S, buf = j & 1;
-      if (*abort_flag) { ok = false; break; }
+    const uint64_t a_desc0 = make_smem_desc(smem_u32(a_smem) + rb * C::TILE_BYTES);
+    const uint32_t d_tmem = tmem_base + (uint32_t)(rb * kColsPerTile);
+    for (int j = 0; ok && j < ntiles; ++j) {
+      const int stage = j % S;
+      if (*abort_flag) break;
+      // B tile j has landed, and this row block's accumulator is free (its warps pulled tile j-1
+      // into registers)
       if (!mbar_wait(smem_u32(bar_b_full + stage), (j / S) & 1) ||
-          !mbar_wait(smem_u32(bar_t_full + rb * 2 + buf), (j >> 1) & 1)) {
-        atomicExch(p.status, kErrEpilogue | 1);
+          !mbar_wait(smem_u32(bar_t_empty + rb), (j & 1) ^ 1)) {
+        if (lane == 0) atomicExch(p.status + kStatusTimeout, kErrMma | 2);
         *abort_flag = 1;
-        ok = false;
         break;
       }
       tc_fence_after();
-      const float* vsm = vs + stage * kColsPerTile * TT;
-      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)((rb * 2 + buf) * kColsPerTile);
-#pragma unroll 1
-      for (int c0 = 0; c0 < kColsPerTile; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld32(taddr + c0, r);
-        tmem_ld_wait();
-        if constexpr (TT == 1) {
-#pragma unroll
-          for (int c = 0; c < 32; c += 4) {
-            const float4 v4 = *reinterpret_cast<const float4*>(vsm + c0 + c);
-            oacc[0] = fmaf(eval_acc<KT>(__uint_as_float(r[c + 0])), v4.x, oacc[0]);
-            oacc[0] = fmaf(eval_acc<KT>(__uint_as_float(r[c + 1])), v4.y, oacc[0]);
-            oacc[0] = fmaf(eval_acc<KT>(__uint_as_float(r[c + 2])), v4.z, oacc[0]);
-            oacc[0] = fmaf(eval_acc<KT>(__uint_as_float(r[c + 3])), v4.w, oacc[0]);
-          }
-        } else if constexpr (TT == 2) {
-#pragma unroll
-          for (int c = 0; c < 32; c += 2) {
-            const float4 v4 = *reinterpret_cast<const float4*>(vsm + (c0 + c) * 2);
-            const float k0 = eval_acc<KT>(__uint_as_float(r[c + 0]));
-            const float k1 = eval_acc<KT>(__uint_as_float(r[c + 1]));
-            oacc[0] = fmaf(k0, v4.x, oacc[0]);
-            oacc[1] = fmaf(k0, v4.y, oacc[1]);
-            oacc[0] = fmaf(k1, v4.z, oacc[0]);
-            oacc[1] = fmaf(k1, v4.w, oacc[1]);
-          }
-        } else {
-          static_assert(TT % 4 == 0, "TT must be 1, 2 or a multiple of 4");
-#pragma unroll
-          for (int c = 0; c < 32; ++c) {
-            const float kv = eval_acc<KT>(__uint_as_float(r[c]));
-#pragma unroll
-            for (int t4 = 0; t4 < TT; t4 += 4) {
-              const float4 v4 = *reinterpret_cast<const float4*>(vsm + (c0 + c) * TT + t4);
-              oacc[t4 + 0] = fmaf(kv, v4.x, oacc[t4 + 0]);
-              oacc[t4 + 1] = fmaf(kv, v4.y, oacc[t4 + 1]);
-              oacc[t4 + 2] = fmaf(kv, v4.z, oacc[t4 + 2]);
-              oacc[t4 + 3] = fmaf(kv, v4.w, oacc[t4 + 3]);
-            }
-          }
+      if (elect_one()) {
+        const uint64_t b_desc0 = make_smem_desc(smem_u32(b_smem) + stage * C::TILE_BYTES);
+        for (int ks = 0; ks < p.ksteps; ++ks) {
+          // 32 bytes (16 fp16) per K-step, two K-steps per 64-byte swizzle row, 8 KiB per slab
+          const uint64_t koff = (uint64_t)((ks >> 1) * ((kTileRows * 64) >> 4) + (ks & 1) * 2);
+          mma_f16(d_tmem, a_desc0 + koff, b_desc0 + koff, kInstrDesc, ks > 0 ? 1u : 0u);
         }
+        mma_commit(smem_u32(bar_t_full + rb));
+        mma_commit(smem_u32(bar_b_empty + stage));
       }
+      __syncwarp();
+    }
+  } else {
+    // ------------------------------ epilogue warps ------------------------------
+    const int q = warp & 3;    // TMEM lane quarter this warp may access
+    const int rb = warp >> 2;  // row block
+    static_assert(NCH * TT == 4, "the running sums are passed to the load wait as four floats");
+    float oacc[NCH][TT];
+    float(&osum)[4] = reinterpret_cast<float(&)[4]>(oacc);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) osum[i] = 0.0f;
+    const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(rb * kColsPerTile);
+    uint32_t ra[32], rc[32];
+    bool epi_ok = true;
+
+    for (int j = 0; j < ntiles; ++j) {
+      const int vstage = j % VS;
+      if (*abort_flag) { epi_ok = false; break; }
+      if (!mbar_wait(smem_u32(bar_v_full + vstage), (j / VS) & 1) ||
+          !mbar_wait(smem_u32(bar_t_full + rb), j & 1)) {
+        atomicExch(p.status + kStatusTimeout, kErrEpilogue | 1);
+        *abort_flag = 1;
+        epi_ok = false;
+        break;
+      }
+      tc_fence_after();
+      const float* vsm = vs + vstage * kColsPerTile * TT;
+      // pieces 0 and 2 travel in `ra`, 1 and 3 in `rc`; the next piece loads while this one is evaluated
+      tmem_ld32(taddr, ra);
+      tmem_ld_wait_on(ra);
+      tmem_ld32(taddr + 32, rc, ra);
+      epilogue_32<KT, TT>(ra, vsm, oacc);
+      tmem_ld_wait_on(rc, osum);
+      tmem_ld32(taddr + 64, ra, rc);
+      epilogue_32<KT, TT>(rc, vsm + 32 * TT, oacc);
+      tmem_ld_wait_on(ra, osum);
+      tmem_ld32(taddr + 96, rc, ra);
+      tmem_ld_wait_on(rc);
+      // The second half of the accumulator is in registers: hand the accumulator back now, so the
+      // MMA of the next tile (and the barrier round trips either side of it) runs under the
+      // evaluation of these two pieces.
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(smem_u32(bar_t_empty + rb * 2 + buf));
-        mbar_arrive(smem_u32(bar_b_empty + stage));
-      }
+      if (lane == 0) mbar_arrive(smem_u32(bar_t_empty + rb));
+      epilogue_32<KT, TT>(ra, vsm + 64 * TT, oacc);
+      epilogue_32<KT, TT>(rc, vsm + 96 * TT, oacc);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(bar_v_empty + vstage));
     }
-    if (ok) {
-      const int64_t row = (int64_t)row_tile * kRowsPerCta + rb * 128 + q * 32 + lane;
+    if (epi_ok) {
+      const int64_t row = (int64_t)row_tile * kRowsPerCta + rb * kTileRows + q * 32 + lane;
       float* dst = p.raw + ((int64_t)chunk * p.r_pad + row) * p.tp + tchunk * TT;
 #pragma unroll
-      for (int t = 0; t < TT; ++t) dst[t] = oacc[t];
+      for (int t = 0; t < TT; ++t) {
+        float x = 0.0f;
+#pragma unroll
+        for (int ch = 0; ch < NCH; ++ch) x += oacc[ch][t];
+        dst[t] = x;
+      }
     }
   }
 
   // ------------------------------ teardown ------------------------------
   tc_fence_before();
   __syncthreads();
-  if (*abort_flag && warp == 8 && lane == 0) {
+  const bool aborted = (*abort_flag != 0);
+  if (aborted && warp == kProducerWarp && lane == 0) {
     // give this CTA's own bulk copies a bounded chance to land before the shared memory is released
     mbar_wait(smem_u32(bar_a_full), 0);
     for (int s = 0; s < S; ++s) {
@@ -546,9 +717,14 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
         if (mbar_try_wait(smem_u32(bar_b_full + s), par)) break;
       }
     }
+    for (int s = 0; s < VS; ++s) {
+      for (int par = 0; par < 2; ++par) {
+        if (mbar_try_wait(smem_u32(bar_v_full + s), par)) break;
+      }
+    }
   }
   __syncthreads();
-  if (warp == 9) {
+  if (warp == kMmaWarp0) {
     __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
@@ -558,6 +734,8 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
 template <int KT, int NSLAB, int TT>
 int launch_sweep_inst(const SweepArgs& args, int n_chunks, int t_chunks, cudaStream_t stream) {
   constexpr size_t smem = tc_smem_bytes<NSLAB, TT>();
+  static_assert(smem > 116 * 1024, "one CTA per SM is assumed (each CTA takes all 512 TMEM columns)");
+  static_assert(smem <= 227 * 1024, "shared memory budget exceeded");
   static bool configured[16] = {false};
   int dev = 0;
   FLK_CUDA_TRY(cudaGetDevice(&dev));

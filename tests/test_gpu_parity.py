@@ -216,6 +216,35 @@ def test_tensor_core_kernel_is_used_and_clean():
         k64.mmv(X.double(), C.double(), v.double())
 
 
+@pytest.mark.parametrize("kernel,nu", [("gaussian", None), ("matern", 2.5)])
+def test_rows_beyond_fp16_range_take_the_simt_path(kernel, nu):
+    """The tensor-core operand images are fp16; a row whose scaled squared norm does not fit is
+    detected on the device and the SIMT kernels produce the result instead.  The answer must be as
+    accurate as for in-range data, with FORCE_TC set or not (the flag only refuses unsupported
+    dtype / feature counts up front, it does not disable the device-side switch)."""
+    from falkon_b200 import _lib
+    from falkon_b200.kernels import GaussianKernel, MaternKernel
+
+    rng = np.random.default_rng(77)
+    n, m, d = 1500, 700, 12
+    X = rng.standard_normal((n, d)).astype(np.float32)
+    X[7] *= 3000.0       # |x / sigma|^2 ~ 2.7e7: far outside what fp16 images carry
+    X[1203, 3] = 900.0   # a single large coordinate
+    C = X[:m].copy()     # includes row 7, so K has an exact 1 on an out-of-range diagonal entry
+    v = rng.standard_normal((m, 2)).astype(np.float32)
+    w = rng.standard_normal((n, 2)).astype(np.float32)
+    for flags in (0, 2):
+        k = GaussianKernel(2.0) if kernel == "gaussian" else MaternKernel(2.0, nu=nu)
+        k = with_flags(k, flags)
+        got = k.dmmv(dev(X), dev(C), dev(v), dev(w)).cpu().numpy()
+        assert _lib.tc_status(torch.device("cuda", torch.cuda.current_device())) == 0
+        want = fo.dense_fdmmv_fp64(X, C, v, w, kernel, 2.0, nu)
+        assert np.isfinite(got).all()
+        assert fo.rel_l2(got, want) <= 1e-4
+        got = k.mmv(dev(X), dev(C), dev(v)).cpu().numpy()
+        assert fo.rel_l2(got, fo.dense_fmmv_fp64(X, C, v, kernel, 2.0, nu)) <= 1e-4
+
+
 def test_errors_surface_as_python_exceptions():
     from falkon_b200.kernels import GaussianKernel
 
