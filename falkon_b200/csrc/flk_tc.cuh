@@ -60,10 +60,11 @@ constexpr int kThreads = (kEpilogueWarps + kRowBlocks + 1) * 32;
 constexpr int kVecStages = 4;                       // ring of vector tiles
 constexpr uint64_t kWaitTimeoutNs = 1000000000ull;  // every device-side wait gives up after 1 s
 constexpr float kNormLimit = 60000.0f;              // largest half squared norm an image may carry
-#ifndef FLK_TC_POLY
-#define FLK_TC_POLY 8
+#ifndef FLK_TC_POLY_PAIRS
+#define FLK_TC_POLY_PAIRS 6
 #endif
-constexpr int kPolyCols = FLK_TC_POLY;  // of every 32 accumulator columns, how many take the FMA-pipe exponential
+// of the 16 column pairs of every 32-column accumulator piece, how many take the FMA-pipe exponential
+constexpr int kPolyPairs = FLK_TC_POLY_PAIRS;
 
 // words of the 256-byte status block at the front of the workspace
 enum { kStatusTimeout = 0, kStatusRange = 1 };
@@ -217,14 +218,8 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32], uin
                  "r"(held[24]), "r"(held[28])
                : "memory");
 }
-template <int NACC>
-__device__ __forceinline__ void tmem_ld_wait_on(uint32_t (&r)[32], float (&acc)[NACC]);
-template <>
-__device__ __forceinline__ void tmem_ld_wait_on<4>(uint32_t (&r)[32], float (&acc)[4]) {
-  asm volatile("tcgen05.wait::ld.sync.aligned;"
-               : FLK_R32_INOUT(r), "+f"(acc[0]), "+f"(acc[1]), "+f"(acc[2]), "+f"(acc[3])
-               :
-               : "memory");
+__device__ __forceinline__ void tmem_ld_wait_on(uint32_t (&r)[32], uint64_t (&acc)[2]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" : FLK_R32_INOUT(r), "+l"(acc[0]), "+l"(acc[1]) : : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait_on(uint32_t (&r)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" : FLK_R32_INOUT(r) : : "memory");
@@ -244,34 +239,66 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
 constexpr uint32_t kInstrDesc = (1u << 4) | ((uint32_t)(kColsPerTile >> 3) << 17) | ((uint32_t)(kTileRows >> 4) << 24);
 
 // ---------------------------------------------------------------------------------------------
-// Kernel functions on the accumulator
+// Packed fp32 pairs (sm_100 add/sub/fma.f32x2: two fp32 operations per issued instruction).  The
+// epilogue is bound by instruction issue once part of the exponentials leaves the MUFU unit, so
+// everything that can be done on two columns at once is.
 // ---------------------------------------------------------------------------------------------
-// 2^x for x <= 0 on the FMA pipe: n = round(x) through the 1.5 * 2^23 trick, degree-5 minimax
-// polynomial of 2^f on f = x - n in [-1/2, 1/2] (relative error 2.4e-7), exponent patched in with
-// integer arithmetic.  x is clamped at -126 so the patched exponent never wraps.
-__device__ __forceinline__ float ex2_fma(float x) {
-  x = fmaxf(x, -126.0f);
-  const float t = x + 12582912.0f;
-  const float n = t - 12582912.0f;
-  const float f = x - n;
-  float p = 0.001327647129073739f;
-  p = fmaf(p, f, 0.009675540961325169f);
-  p = fmaf(p, f, 0.05550713092088699f);
-  p = fmaf(p, f, 0.24022120237350464f);
-  p = fmaf(p, f, 0.6931469440460205f);
-  p = fmaf(p, f, 1.0000001192092896f);
-  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
 }
 
-// POLY selects the FMA-pipe exponential (Gaussian only; the other kernel functions are bound by
-// their two MUFU ops and a longer FMA tail, and always take the MUFU path).
-template <int KT, bool POLY>
+// ---------------------------------------------------------------------------------------------
+// Kernel functions on the accumulator
+// ---------------------------------------------------------------------------------------------
+// 2^x on the FMA pipe for a pair of arguments: n = round(x) through the 1.5 * 2^23 trick, degree-5
+// minimax polynomial of 2^f on f = x - n in [-1/2, 1/2] (relative error 2.4e-7), exponent patched
+// in with integer arithmetic.  x is clamped at -126 so the patched exponent never wraps; arguments
+// a hair above zero (rounding, coincident points) are fine.
+__device__ __forceinline__ void ex2_fma_pair(float x0, float x1, float& y0, float& y1) {
+  const uint64_t magic = pack2(12582912.0f, 12582912.0f);
+  const uint64_t x = pack2(fmaxf(x0, -126.0f), fmaxf(x1, -126.0f));
+  const uint64_t t = add2(x, magic);
+  const uint64_t f = sub2(x, sub2(t, magic));
+  uint64_t p = pack2(0.001327647129073739f, 0.001327647129073739f);
+  p = fma2(p, f, pack2(0.009675540961325169f, 0.009675540961325169f));
+  p = fma2(p, f, pack2(0.05550713092088699f, 0.05550713092088699f));
+  p = fma2(p, f, pack2(0.24022120237350464f, 0.24022120237350464f));
+  p = fma2(p, f, pack2(0.6931469440460205f, 0.6931469440460205f));
+  p = fma2(p, f, pack2(1.0000001192092896f, 1.0000001192092896f));
+  float p0, p1, t0, t1;
+  unpack2(p, p0, p1);
+  unpack2(t, t0, t1);
+  y0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
+  y1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
+}
+
+template <int KT>
 __device__ __forceinline__ float eval_acc(float acc) {
   if (KT == FLK_GAUSSIAN) {
-    // acc = -(log2(e) / 2) D^2.  Rounding can leave it a hair above zero for coincident points; the
-    // reference clamps D^2 at 1e-20 (k <= 1), hence the min.
-    if (POLY) return ex2_fma(fminf(acc, 0.0f));
-    return ex2_approx(fminf(acc, 0.0f));
+    // acc = -(log2(e) / 2) D^2.  The image builder rounds the norm up, so acc errs on the negative
+    // side; what is left above zero for coincident points is accumulation rounding (k <= 1 + ~1e-7),
+    // which is not worth an extra instruction per evaluation.
+    return ex2_approx(acc);
   } else {
     const float dist = sqrt_approx(fmaxf(-acc, 0.0f));  // acc = -D^2
     if (KT == FLK_LAPLACIAN) return ex2_approx(dist * (-kLog2e));
@@ -281,6 +308,19 @@ __device__ __forceinline__ float eval_acc(float acc) {
     }
     const float s = dist * 2.23606797749979f;
     return fmaf(s, fmaf(s, 1.0f / 3.0f, 1.0f), 1.0f) * ex2_approx(s * (-kLog2e));
+  }
+}
+
+// Two adjacent accumulator columns -> two kernel values.  POLY selects the FMA-pipe exponential
+// (Gaussian only; the other kernel functions are bound by their two MUFU ops and a longer FMA
+// tail, and always take the MUFU path).
+template <int KT, bool POLY>
+__device__ __forceinline__ void eval_pair(uint32_t b0, uint32_t b1, float& k0, float& k1) {
+  if constexpr (KT == FLK_GAUSSIAN && POLY) {
+    ex2_fma_pair(__uint_as_float(b0), __uint_as_float(b1), k0, k1);
+  } else {
+    k0 = eval_acc<KT>(__uint_as_float(b0));
+    k1 = eval_acc<KT>(__uint_as_float(b1));
   }
 }
 
@@ -342,9 +382,15 @@ __global__ void __launch_bounds__(128) prep_images_kernel(const float* __restric
   if (out_of_range && live) atomicOr(status + kStatusRange, 1);
   float piece[3];
   {
+    // the last piece is rounded up: the represented norm is never below the true one, so the
+    // accumulator errs on the negative side (k <= 1 for coincident points up to accumulation rounding)
     double rem = half_norm;
     for (int i = 0; i < 3; ++i) {
-      const float pc = (i < npieces) ? __half2float(__float2half_rn((float)rem)) : 0.0f;
+      float pc = 0.0f;
+      if (i < npieces) {
+        const float remf = __double2float_ru(rem);
+        pc = __half2float(i == npieces - 1 ? __float2half_ru(remf) : __float2half_rn(remf));
+      }
       piece[i] = pc;
       rem -= (double)pc;
     }
@@ -434,68 +480,47 @@ constexpr size_t tc_smem_bytes() {
 // error codes written to the status word: role * 16 + which wait
 enum { kErrProducer = 0x10, kErrMma = 0x20, kErrEpilogue = 0x30 };
 
-// Number of independent accumulation chains per output column (breaks the FMA dependency chain).
-template <int TT>
-struct EpiChains {
-  static constexpr int N = TT == 1 ? 4 : (TT == 2 ? 2 : 1);
-};
-
-// Is accumulator column c (0..31 within a 32-column piece) evaluated on the FMA pipe?  The
-// polynomial columns are spread evenly so both pipes have work throughout the piece.
+// Is column pair pr (0..15 within a 32-column piece) evaluated on the FMA pipe?  The polynomial
+// pairs are spread evenly so both pipes have work throughout the piece.
 template <int KT>
-__host__ __device__ constexpr bool poly_col(int c) {
-  return KT == FLK_GAUSSIAN && kPolyCols > 0 && ((c + 1) * kPolyCols / 32 != c * kPolyCols / 32);
+__host__ __device__ constexpr bool poly_pair(int pr) {
+  return KT == FLK_GAUSSIAN && kPolyPairs > 0 && ((pr + 1) * kPolyPairs / 16 != pr * kPolyPairs / 16);
 }
 
-template <int KT, int C>
-__device__ __forceinline__ float eval_col(uint32_t bits) {
-  return eval_acc<KT, poly_col<KT>(C)>(__uint_as_float(bits));
-}
-
-// Kernel function + contraction for 32 accumulator columns held in registers.
-// `vsm` points at the vector-tile entries of the first of those columns.
+// Kernel function + contraction for 32 accumulator columns held in registers.  `vsm` points at the
+// vector-tile entries of the first of those columns.  The running sums are two packed pairs:
+//   TT = 1: four interleaved partial sums of the single output column (summed at the end);
+//   TT = 2: osum[0] and osum[1] are two partial sums of the (t0, t1) pair;
+//   TT = 4: osum[0] = (t0, t1), osum[1] = (t2, t3).
 template <int KT, int TT, int C0 = 0>
-__device__ __forceinline__ void epilogue_32(const uint32_t (&r)[32], const float* vsm,
-                                            float (&oacc)[EpiChains<TT>::N][TT]) {
+__device__ __forceinline__ void epilogue_32(const uint32_t (&r)[32], const float* vsm, uint64_t (&osum)[2]) {
+  static_assert(TT == 1 || TT == 2 || TT == 4, "TT must be 1, 2 or 4");
   if constexpr (C0 < 32) {
+    float k0, k1, k2, k3;
+    eval_pair<KT, poly_pair<KT>(C0 / 2)>(r[C0], r[C0 + 1], k0, k1);
+    eval_pair<KT, poly_pair<KT>(C0 / 2 + 1)>(r[C0 + 2], r[C0 + 3], k2, k3);
     if constexpr (TT == 1) {
-      const float4 v4 = *reinterpret_cast<const float4*>(vsm + C0);
-      oacc[0][0] = fmaf(eval_col<KT, C0 + 0>(r[C0 + 0]), v4.x, oacc[0][0]);
-      oacc[1][0] = fmaf(eval_col<KT, C0 + 1>(r[C0 + 1]), v4.y, oacc[1][0]);
-      oacc[2][0] = fmaf(eval_col<KT, C0 + 2>(r[C0 + 2]), v4.z, oacc[2][0]);
-      oacc[3][0] = fmaf(eval_col<KT, C0 + 3>(r[C0 + 3]), v4.w, oacc[3][0]);
+      const ulonglong2 v = *reinterpret_cast<const ulonglong2*>(vsm + C0);  // (v0, v1), (v2, v3)
+      osum[0] = fma2(pack2(k0, k1), v.x, osum[0]);
+      osum[1] = fma2(pack2(k2, k3), v.y, osum[1]);
     } else if constexpr (TT == 2) {
-      const float4 va = *reinterpret_cast<const float4*>(vsm + C0 * 2);
-      const float4 vb = *reinterpret_cast<const float4*>(vsm + C0 * 2 + 4);
-      const float k0 = eval_col<KT, C0 + 0>(r[C0 + 0]);
-      const float k1 = eval_col<KT, C0 + 1>(r[C0 + 1]);
-      const float k2 = eval_col<KT, C0 + 2>(r[C0 + 2]);
-      const float k3 = eval_col<KT, C0 + 3>(r[C0 + 3]);
-      oacc[0][0] = fmaf(k0, va.x, oacc[0][0]);
-      oacc[0][1] = fmaf(k0, va.y, oacc[0][1]);
-      oacc[1][0] = fmaf(k1, va.z, oacc[1][0]);
-      oacc[1][1] = fmaf(k1, va.w, oacc[1][1]);
-      oacc[0][0] = fmaf(k2, vb.x, oacc[0][0]);
-      oacc[0][1] = fmaf(k2, vb.y, oacc[0][1]);
-      oacc[1][0] = fmaf(k3, vb.z, oacc[1][0]);
-      oacc[1][1] = fmaf(k3, vb.w, oacc[1][1]);
+      const ulonglong2 va = *reinterpret_cast<const ulonglong2*>(vsm + C0 * 2);      // columns C0, C0 + 1
+      const ulonglong2 vb = *reinterpret_cast<const ulonglong2*>(vsm + C0 * 2 + 4);  // columns C0 + 2, C0 + 3
+      osum[0] = fma2(pack2(k0, k0), va.x, osum[0]);
+      osum[1] = fma2(pack2(k1, k1), va.y, osum[1]);
+      osum[0] = fma2(pack2(k2, k2), vb.x, osum[0]);
+      osum[1] = fma2(pack2(k3, k3), vb.y, osum[1]);
     } else {
-      static_assert(TT == 1 || TT == 2 || TT % 4 == 0, "TT must be 1, 2 or a multiple of 4");
-      const float kv[4] = {eval_col<KT, C0 + 0>(r[C0 + 0]), eval_col<KT, C0 + 1>(r[C0 + 1]),
-                           eval_col<KT, C0 + 2>(r[C0 + 2]), eval_col<KT, C0 + 3>(r[C0 + 3])};
+      const float kv[4] = {k0, k1, k2, k3};
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-#pragma unroll
-        for (int t4 = 0; t4 < TT; t4 += 4) {
-          const float4 v4 = *reinterpret_cast<const float4*>(vsm + (C0 + c) * TT + t4);
-          oacc[0][t4 + 0] = fmaf(kv[c], v4.x, oacc[0][t4 + 0]);
-          oacc[0][t4 + 1] = fmaf(kv[c], v4.y, oacc[0][t4 + 1]);
-          oacc[0][t4 + 2] = fmaf(kv[c], v4.z, oacc[0][t4 + 2]);
-          oacc[0][t4 + 3] = fmaf(kv[c], v4.w, oacc[0][t4 + 3]);
-        }
+        const ulonglong2 v = *reinterpret_cast<const ulonglong2*>(vsm + (C0 + c) * 4);
+        const uint64_t kk = pack2(kv[c], kv[c]);
+        osum[0] = fma2(kk, v.x, osum[0]);
+        osum[1] = fma2(kk, v.y, osum[1]);
       }
     }
-    epilogue_32<KT, TT, C0 + 4>(r, vsm, oacc);
+    epilogue_32<KT, TT, C0 + 4>(r, vsm, osum);
   }
 }
 
@@ -507,7 +532,6 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
   using C = TcCfg<NSLAB>;
   constexpr int S = C::STAGES;
   constexpr int VS = kVecStages;
-  constexpr int NCH = EpiChains<TT>::N;
   extern __shared__ unsigned char tc_smem_raw[];
   // the swizzle atoms want a 512-byte aligned base; 1024 keeps every tile image on a round address
   const uint32_t raw_addr = smem_u32(tc_smem_raw);
@@ -649,11 +673,7 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
     // ------------------------------ epilogue warps ------------------------------
     const int q = warp & 3;    // TMEM lane quarter this warp may access
     const int rb = warp >> 2;  // row block
-    static_assert(NCH * TT == 4, "the running sums are passed to the load wait as four floats");
-    float oacc[NCH][TT];
-    float(&osum)[4] = reinterpret_cast<float(&)[4]>(oacc);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) osum[i] = 0.0f;
+    uint64_t osum[2] = {0ull, 0ull};  // two packed pairs of running sums (see epilogue_32)
     const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(rb * kColsPerTile);
     uint32_t ra[32], rc[32];
     bool epi_ok = true;
@@ -674,10 +694,10 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
       tmem_ld32(taddr, ra);
       tmem_ld_wait_on(ra);
       tmem_ld32(taddr + 32, rc, ra);
-      epilogue_32<KT, TT>(ra, vsm, oacc);
+      epilogue_32<KT, TT>(ra, vsm, osum);
       tmem_ld_wait_on(rc, osum);
       tmem_ld32(taddr + 64, ra, rc);
-      epilogue_32<KT, TT>(rc, vsm + 32 * TT, oacc);
+      epilogue_32<KT, TT>(rc, vsm + 32 * TT, osum);
       tmem_ld_wait_on(ra, osum);
       tmem_ld32(taddr + 96, rc, ra);
       tmem_ld_wait_on(rc);
@@ -687,20 +707,27 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(bar_t_empty + rb));
-      epilogue_32<KT, TT>(ra, vsm + 64 * TT, oacc);
-      epilogue_32<KT, TT>(rc, vsm + 96 * TT, oacc);
+      epilogue_32<KT, TT>(ra, vsm + 64 * TT, osum);
+      epilogue_32<KT, TT>(rc, vsm + 96 * TT, osum);
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(bar_v_empty + vstage));
     }
     if (epi_ok) {
       const int64_t row = (int64_t)row_tile * kRowsPerCta + rb * kTileRows + q * 32 + lane;
       float* dst = p.raw + ((int64_t)chunk * p.r_pad + row) * p.tp + tchunk * TT;
-#pragma unroll
-      for (int t = 0; t < TT; ++t) {
-        float x = 0.0f;
-#pragma unroll
-        for (int ch = 0; ch < NCH; ++ch) x += oacc[ch][t];
-        dst[t] = x;
+      float a0, a1, b0, b1;
+      unpack2(osum[0], a0, a1);
+      unpack2(osum[1], b0, b1);
+      if constexpr (TT == 1) {
+        dst[0] = (a0 + a1) + (b0 + b1);
+      } else if constexpr (TT == 2) {
+        dst[0] = a0 + b0;
+        dst[1] = a1 + b1;
+      } else {
+        dst[0] = a0;
+        dst[1] = a1;
+        dst[2] = b0;
+        dst[3] = b1;
       }
     }
   }
