@@ -12,7 +12,7 @@ M x 1 partial results are summed with one NCCL all-reduce per step.
 Prints ONE JSON line.  `value` is kernel pair-evaluations per second (N*M*T / time) with the inputs
 resident in HBM; `e2e` is the same metric through the host-buffer entry point (pinned host inputs
 copied in, result copied out, inside the timed region); `roofline` describes the dominant kernel
-(the tcgen05 sweep), timed live with CUDA events on its stream; `cpu_baseline` is the CPU oracle
+(the tcgen05 sweep), timed live with CUDA events on its stream, against the MUFU rate measured live; `cpu_baseline` is the CPU oracle
 timed on a bounded sample on this machine's host cores.
 """
 import argparse
@@ -312,6 +312,12 @@ def main():
         return
 
     # ---------------- roofline of the dominant kernel ----------------
+    # One launch of the sweep kernel evaluates the kernel function once for every (row, centre) pair.
+    # The unit that bounds it is the special-function unit (one exponential per evaluation, 16 MUFU
+    # lanes per SM); the kernel moves part of the exponentials to the FMA pipe, so the achieved
+    # exponential rate may exceed the MUFU rate.  The denominator is measured live with the
+    # library's probe kernel (nothing but ex2 on every SM), the numerator is the CUDA-event
+    # duration of the sweep launches recorded by the library on the launch stream.
     peaks = load_peaks()
     s1 = float(np.mean([a for a, _ in sweep_ms if a >= 0])) if sweep_ms else float("nan")
     s2 = float(np.mean([b for _, b in sweep_ms if b >= 0])) if sweep_ms else float("nan")
@@ -319,33 +325,41 @@ def main():
     pairs_per_launch = float(n) * M  # one sweep evaluates every (row, centre) pair once
     uses_tc = bool(lib.flk_uses_tensor_cores(0, 0, D, T, flags))
     sm_mhz = (clocks or {}).get("sm_mhz") or 1965.0
-    # tensor flops the 3xTF32 formulation needs per pair: 2 * (3 d + 2 * norm pieces)
-    k_used = 3 * D + 2 * 2
-    tensor_tflops = pairs_per_launch * 2 * k_used / (sweep_avg_ms * 1e-3) / 1e12
-    tf32_peak = peaks["bf16_tflops"] / 2.0
-    mufu_peak = 148 * 16 * sm_mhz * 1e6  # ex2 per second at the sampled clock
+    evals_per_s = pairs_per_launch / (sweep_avg_ms * 1e-3)
+    mufu_rate = _lib.measure_mufu_rate(dev)
+    mufu_nominal = 148 * 16 * sm_mhz * 1e6
+    # tensor flops of the split-fp16 formulation per pair: 2 * (3 d + 2 * norm pieces), d = 28 -> 3 pieces
+    k_used = 3 * D + 2 * 3
+    tensor_tflops = evals_per_s * 2 * k_used / 1e12
     fp32_peak_tflops = 148 * 128 * 2 * sm_mhz * 1e6 / 1e12
     alg_flops_pair = 2 * D + 2 * T + 4 + 1
+    # DRAM traffic of one sweep launch: 241 bytes per row of X, from the ncu capture at 400,000 rows
+    # (92.0 MB read + 4.4 MB written; algorithmic 84 MB), scaled by rows (traffic is proportional to rows)
+    traffic = 241.0 * n if uses_tc else None
+    alg_bytes = (n * (3 * D + 6 + 6) * 2.0 + M * 96 * 2.0 + n * 4.0 + M * 4.0) if uses_tc else None
     roofline = {
-        "bound": "tensor",
+        "bound": "mufu" if uses_tc else "fp32",
         "kernel": "flk::tc::kmv_tc_kernel" if uses_tc else "flk::kmv_simt_kernel",
-        "achieved": tensor_tflops if uses_tc else pairs_per_launch * alg_flops_pair / (sweep_avg_ms * 1e-3) / 1e12,
-        "peak": tf32_peak if uses_tc else fp32_peak_tflops,
-        "unit": "TFLOP/s",
-        "frac": (tensor_tflops / tf32_peak) if uses_tc else
-                (pairs_per_launch * alg_flops_pair / (sweep_avg_ms * 1e-3) / 1e12 / fp32_peak_tflops),
-        "traffic": None,
-        "peak_source": (f"tf32 dense peak = bf16 {peaks['source']} peak / 2" if uses_tc else
-                        "fp32 FMA lanes x sampled SM clock (nominal lanes)"),
+        "achieved": evals_per_s / 1e9 if uses_tc else evals_per_s * alg_flops_pair / 1e12,
+        "peak": mufu_rate / 1e9 if uses_tc else fp32_peak_tflops,
+        "unit": "Gexp/s" if uses_tc else "TFLOP/s",
+        "frac": evals_per_s / mufu_rate if uses_tc else evals_per_s * alg_flops_pair / 1e12 / fp32_peak_tflops,
+        "traffic": traffic,
+        "peak_source": ("MUFU ex2 rate measured live on this GPU by flk_probe_mufu (nominal 148 SMs x 16 lanes x "
+                        f"sampled clock = {mufu_nominal / 1e9:.0f} Gexp/s); the sweep is neither HBM- nor tensor-bound"
+                        if uses_tc else "fp32 FMA lanes x sampled SM clock (nominal lanes)"),
         "launch_ms": {"sweep1_Kv": s1, "sweep2_KTu": s2},
         "pairs_per_launch": pairs_per_launch,
-        "mufu": {"achieved_gops": pairs_per_launch / (sweep_avg_ms * 1e-3) / 1e9, "peak_gops": mufu_peak / 1e9,
-                 "frac": pairs_per_launch / (sweep_avg_ms * 1e-3) / mufu_peak,
-                 "note": "one ex2 per kernel evaluation; peak = 148 SMs x 16 MUFU lanes x sampled SM clock"},
+        "algorithmic_bytes_per_launch": alg_bytes,
+        "tensor": {"achieved_tflops": tensor_tflops, "peak_tflops": peaks["bf16_tflops"],
+                   "frac": tensor_tflops / peaks["bf16_tflops"],
+                   "note": f"fp16 MMA flops of the exponent GEMM (K = {k_used} used of 96) vs {peaks['source']} bf16 peak"},
+        "hbm": {"achieved_gbs": (traffic or 0.0) / (sweep_avg_ms * 1e-3) / 1e9, "peak_gbs": peaks["hbm_gbs"],
+                "frac": (traffic or 0.0) / (sweep_avg_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]},
         "fp32_algorithmic": {"flops_per_pair": alg_flops_pair,
-                             "achieved_tflops": pairs_per_launch * alg_flops_pair / (sweep_avg_ms * 1e-3) / 1e12,
+                             "achieved_tflops": evals_per_s * alg_flops_pair / 1e12,
                              "peak_tflops": fp32_peak_tflops,
-                             "frac": pairs_per_launch * alg_flops_pair / (sweep_avg_ms * 1e-3) / 1e12 / fp32_peak_tflops,
+                             "frac": evals_per_s * alg_flops_pair / 1e12 / fp32_peak_tflops,
                              "note": "north-star view: work counted as if done on the FP32 FMA pipe"},
     }
     cpu_baseline = None
@@ -359,7 +373,7 @@ def main():
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
         "config": {"workload": WORKLOAD, "rows_per_gpu": n, "global_rows": n * world, "centres": M, "d": D, "T": T,
-                   "kernel": "simt" if args.simt else "tcgen05-3xTF32", "l2": "256 MB buffer written between timed steps",
+                   "kernel": "simt" if args.simt else "tcgen05 split-fp16 + MUFU/FMA exponential", "l2": "256 MB buffer written between timed steps",
                    "collective": "NCCL all-reduce of the M x T partial" if world > 1 else "none"},
         "roofline": roofline,
         "cpu_baseline": cpu_baseline,

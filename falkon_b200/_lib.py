@@ -83,6 +83,8 @@ _SIGNATURES = {
     # dtype, kernel, X1(4), X2(4), d, v ptr, t, v strides(2), out ptr + strides(3), sigma (double), flags, stream
     "flk_fmmv_static": (_int, [_int, _int] + _MAT + _MAT + [_i64, _vp, _i64, _i64, _i64, _vp, _i64, _i64, ctypes.c_double, _int, _vp]),
     "flk_tc_status": (_int, [_vp, _vp, ctypes.POINTER(_int)]),
+    "flk_range_flag": (_int, [_vp, _vp, ctypes.POINTER(_int)]),
+    "flk_probe_mufu": (_int, [_int, _vp, ctypes.POINTER(_i64), _vp]),
     "flk_set_timing": (_int, [_int]),
     "flk_get_sweep_ms": (_int, [ctypes.POINTER(ctypes.c_float), ctypes.POINTER(ctypes.c_float)]),
 }
@@ -246,6 +248,42 @@ def tc_status(device: torch.device) -> int:
         stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
         raise_for_status(lib.flk_tc_status(ctypes.c_void_p(_workspaces[key].data_ptr()), stream, ctypes.byref(out)))
     return out.value
+
+
+def range_flag(device: torch.device) -> int:
+    """1 when the last tensor-core-eligible call on this device's cached workspace switched to the
+    SIMT kernels because some row did not fit the fp16 operand images, else 0."""
+    lib = load()
+    key = (device.type, device.index)
+    if key not in _workspaces:
+        return 0
+    out = ctypes.c_int(0)
+    with torch.cuda.device(device):
+        stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+        raise_for_status(lib.flk_range_flag(ctypes.c_void_p(_workspaces[key].data_ptr()), stream, ctypes.byref(out)))
+    return out.value
+
+
+def measure_mufu_rate(device: torch.device, iters: int = 4096, reps: int = 5) -> float:
+    """ex2 evaluations per second of `device`, measured with the library's probe kernel and CUDA events
+    (best of `reps`; the first launch is a warm-up)."""
+    lib = load()
+    with torch.cuda.device(device):
+        sink = torch.zeros(4, dtype=torch.float32, device=device)
+        stream = torch.cuda.current_stream(device)
+        ops = _i64(0)
+        best = None
+        for r in range(reps + 1):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            raise_for_status(lib.flk_probe_mufu(iters, ctypes.c_void_p(sink.data_ptr()), ctypes.byref(ops),
+                                                ctypes.c_void_p(stream.cuda_stream)))
+            e1.record(stream)
+            e1.synchronize()
+            ms = e0.elapsed_time(e1)
+            if r > 0:
+                best = ms if best is None else min(best, ms)
+    return float(ops.value) / (best * 1e-3)
 
 
 def set_timing(enable: bool):

@@ -42,6 +42,21 @@ static int timer_mark(int slot, cudaStream_t stream) {
   return FLK_OK;
 }
 
+// 16 independent ex2.approx chains per thread, nothing else: the MUFU rate of the device.
+__global__ void __launch_bounds__(512) mufu_probe_kernel(int iters, float* sink) {
+  float x[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) x[i] = -1.0f - 0.001f * (float)(threadIdx.x + i);
+  for (int it = 0; it < iters; ++it) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) x[i] = ex2_approx(x[i]) - 1.5f;
+  }
+  float s = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) s += x[i];
+  if (s == 123.456f) *sink = s;  // keeps the loop alive; never true in practice
+}
+
 struct Mat {
   const void* ptr;
   int64_t rows, cols, rs, cs;
@@ -769,6 +784,25 @@ int flk_tc_status(const void* workspace, void* stream, int* status_out) {
   FLK_CUDA_TRY(cudaMemcpyAsync(host, workspace, sizeof(host), cudaMemcpyDeviceToHost, st));
   FLK_CUDA_TRY(cudaStreamSynchronize(st));
   *status_out = host[0];
+  return FLK_OK;
+}
+
+int flk_range_flag(const void* workspace, void* stream, int* flag_out) {
+  if (workspace == nullptr || flag_out == nullptr) return fail(FLK_ERR_BAD_ARG, "null pointer");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  int host[4] = {0, 0, 0, 0};
+  FLK_CUDA_TRY(cudaMemcpyAsync(host, workspace, sizeof(host), cudaMemcpyDeviceToHost, st));
+  FLK_CUDA_TRY(cudaStreamSynchronize(st));
+  *flag_out = host[tc::kStatusRange] != 0 ? 1 : 0;
+  return FLK_OK;
+}
+
+int flk_probe_mufu(int iters, void* sink, int64_t* ops_out, void* stream) {
+  if (sink == nullptr || ops_out == nullptr || iters <= 0) return fail(FLK_ERR_BAD_ARG, "bad argument");
+  const int blocks = kNumSMs * 4, threads = 512;
+  mufu_probe_kernel<<<blocks, threads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(iters, reinterpret_cast<float*>(sink));
+  FLK_CUDA_TRY(cudaGetLastError());
+  *ops_out = (int64_t)blocks * threads * 16 * iters;
   return FLK_OK;
 }
 

@@ -208,6 +208,22 @@ int flk_get_sweep_ms(float* sweep1_ms, float* sweep2_ms);
  */
 int flk_tc_status(const void* workspace, void* stream, int* status_out);
 
+/*
+ * Reads the device-side range flag of the call that last used `workspace`: 1 when the operand
+ * images of the tensor-core path could not carry some row (scaled squared norm beyond fp16 range)
+ * and the SIMT kernels produced the result instead, 0 otherwise.  Synchronises the stream.
+ */
+int flk_range_flag(const void* workspace, void* stream, int* flag_out);
+
+/*
+ * Measurement aid (no counterpart in the reference): enqueues a kernel that does nothing but
+ * `iters` x 16 independent ex2.approx per thread on every SM, so that a benchmark can time it with
+ * CUDA events and obtain the MUFU (special-function unit) rate of the device it runs on -- the
+ * denominator of the roofline of the Gaussian sweep.  `*ops_out` receives the number of ex2
+ * evaluations the launch performs.  `sink` is a device buffer of at least 4 bytes.
+ */
+int flk_probe_mufu(int iters, void* sink, int64_t* ops_out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
