@@ -9,7 +9,8 @@ The CUDA library (falkon_b200/libfalkon_b200.so, C ABI in include/falkon_b200.h)
 use; there is no CPU fallback.
 """
 from .options import FalkonOptions  # noqa: F401
-from . import kernels, mmv_ops  # noqa: F401
+from . import center_selection, kernels, mmv_ops, models, optim, preconditioner  # noqa: F401
+from .models import Falkon  # noqa: F401
 
-__version__ = "0.1.0"
-__all__ = ("FalkonOptions", "kernels", "mmv_ops")
+__version__ = "0.2.0"
+__all__ = ("FalkonOptions", "Falkon", "kernels", "mmv_ops", "optim", "preconditioner", "models", "center_selection")

@@ -20,7 +20,7 @@ LIB_PATH = os.environ.get("FALKON_B200_LIB") or os.path.join(_HERE, "libfalkon_b
 
 FLK_F32, FLK_F64 = 0, 1
 FLK_GAUSSIAN, FLK_LAPLACIAN, FLK_MATERN15, FLK_MATERN25 = 0, 1, 2, 3
-FLAG_FORCE_SIMT, FLAG_FORCE_TC = 1, 2
+FLAG_FORCE_SIMT, FLAG_FORCE_TC, FLAG_FP64_MATH = 1, 2, 4
 STATIC_SCRATCH_BYTES = 64 << 20
 
 FLK_ERR_BAD_ARG, FLK_ERR_LAYOUT, FLK_ERR_WORKSPACE = -1, -2, -3
@@ -82,6 +82,9 @@ _SIGNATURES = {
     "flk_fdmmv_host": (_int, [_int, _int] + _MAT + _MAT + [_i64, _vp, _i64, _i64, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _dp, _i64, _vp, _i64, _int, _vp]),
     # dtype, kernel, X1(4), X2(4), d, v ptr, t, v strides(2), out ptr + strides(3), sigma (double), flags, stream
     "flk_fmmv_static": (_int, [_int, _int] + _MAT + _MAT + [_i64, _vp, _i64, _i64, _i64, _vp, _i64, _i64, ctypes.c_double, _int, _vp]),
+    "flk_fmm_workspace_bytes": (_i64, [_int, _i64, _i64, _i64, _int]),
+    # dtype, kernel, X1(4), X2(4), d, out ptr + strides(3), sigma, len, ws, bytes, flags, stream
+    "flk_fmm": (_int, [_int, _int] + _MAT + _MAT + [_i64, _vp, _i64, _i64, _dp, _i64, _vp, _i64, _int, _vp]),
     "flk_tc_status": (_int, [_vp, _vp, ctypes.POINTER(_int)]),
     "flk_range_flag": (_int, [_vp, _vp, ctypes.POINTER(_int)]),
     "flk_probe_mufu": (_int, [_int, _vp, ctypes.POINTER(_i64), _vp]),
@@ -232,6 +235,27 @@ def call_fdmmv(kernel_id, sigma, X1, X2, v, w, out, flags=0, host=False, device=
                     *_mat_args(v, with_rows=False), *_mat_args(w, with_rows=False), t,
                     *_mat_args(out, with_rows=False), sig_ptr, sig_len,
                     ctypes.c_void_p(ws.data_ptr()), ws.numel(), flags, stream)
+    del keep
+    raise_for_status(status)
+    return out
+
+
+def call_fmm(kernel_id, sigma, X1, X2, out, flags=0):
+    """out[n, m] = k(X1, X2) through the C ABI (device pointers)."""
+    lib = load()
+    dt = dtype_code(X1.dtype)
+    n, d = X1.shape
+    m = X2.shape[0]
+    dev = X1.device
+    need = lib.flk_fmm_workspace_bytes(dt, n, m, d, flags)
+    if need < 0:
+        raise_for_status(int(need))
+    keep, sig_ptr, sig_len = _sigma_args(sigma)
+    with torch.cuda.device(dev):
+        ws = workspace(dev, need)
+        stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        status = lib.flk_fmm(dt, kernel_id, *_mat_args(X1), *_mat_args(X2), d, *_mat_args(out, with_rows=False),
+                             sig_ptr, sig_len, ctypes.c_void_p(ws.data_ptr()), ws.numel(), flags, stream)
     del keep
     raise_for_status(status)
     return out

@@ -4,6 +4,7 @@
 #include <vector>
 
 #include "flk_common.cuh"
+#include "flk_fmm.cuh"
 #include "flk_prep.cuh"
 #include "flk_simt.cuh"
 #include "flk_tc.cuh"
@@ -286,11 +287,11 @@ static int upload_sigma(const double* sigma, int64_t sigma_len, void* dst, T* sc
   return FLK_OK;
 }
 
-template <typename T>
+template <typename T, typename TIn = T>
 static int run_prep_rows(const Mat& X, const T* sigma_dev, T sigma_scalar, int sigma_len, void* xs, int ld,
                          int64_t rows_pad, void* norms, Gate gate, cudaStream_t stream) {
   int blocks = (int)ceil_div(rows_pad, kPrepRows);
-  prep_rows_kernel<T><<<blocks, 256, 0, stream>>>(reinterpret_cast<const T*>(X.ptr), X.rows, (int)X.cols, X.rs,
+  prep_rows_kernel<T, TIn><<<blocks, 256, 0, stream>>>(reinterpret_cast<const TIn*>(X.ptr), X.rows, (int)X.cols, X.rs,
                                                   X.cs, sigma_dev, sigma_scalar, sigma_len,
                                                   reinterpret_cast<T*>(xs), ld, rows_pad,
                                                   reinterpret_cast<T*>(norms), gate);
@@ -465,6 +466,54 @@ static int fdmmv_impl(int dtype, int kernel, const Mat& X1, const Mat& X2, const
   return FLK_OK;
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// fmm: the kernel matrix itself (needed once per fit for the preconditioner)
+// ---------------------------------------------------------------------------------------------
+struct FmmLayout {
+  int64_t total = 0;
+  void* sigma = nullptr;
+  void *xs1 = nullptr, *n1 = nullptr, *xs2 = nullptr, *n2 = nullptr;
+  int ld = 0;
+  int64_t n_pad = 0, m_pad = 0;
+};
+
+static FmmLayout make_fmm_layout(void* ws, int math_dtype, int64_t n, int64_t m, int64_t d) {
+  FmmLayout L;
+  const int64_t es = esize(math_dtype);
+  Carver c(ws);
+  L.sigma = c.take(std::max<int64_t>(d, 1) * es);
+  L.ld = ld_for(math_dtype, d);
+  L.n_pad = round_up(std::max<int64_t>(n, 1), kRowPad);
+  L.m_pad = round_up(std::max<int64_t>(m, 1), kRowPad);
+  L.xs1 = c.take(L.n_pad * L.ld * es);
+  L.n1 = c.take(L.n_pad * es);
+  L.xs2 = c.take(L.m_pad * L.ld * es);
+  L.n2 = c.take(L.m_pad * es);
+  L.total = c.off;
+  return L;
+}
+
+// T = arithmetic type, TIO = type of the data and of the stored matrix
+template <typename T, typename TIO>
+static int fmm_impl(int math_dtype, int kernel, const Mat& X1, const Mat& X2, void* out, int64_t out_rs,
+                    int64_t out_cs, const double* sigma, int64_t sigma_len, void* ws, int64_t ws_bytes,
+                    cudaStream_t stream) {
+  const int64_t n = X1.rows, m = X2.rows, d = X1.cols;
+  FmmLayout L = make_fmm_layout(ws, math_dtype, n, m, d);
+  FLK_TRY(check_workspace(ws, ws_bytes, L.total));
+  if (n == 0 || m == 0) return FLK_OK;
+  T sig_scalar;
+  const T* sig_dev;
+  FLK_TRY(upload_sigma<T>(sigma, sigma_len, L.sigma, &sig_scalar, &sig_dev, stream));
+  const Gate always{nullptr, 0};
+  FLK_TRY((run_prep_rows<T, TIO>(X1, sig_dev, sig_scalar, (int)sigma_len, L.xs1, L.ld, L.n_pad, L.n1, always, stream)));
+  FLK_TRY((run_prep_rows<T, TIO>(X2, sig_dev, sig_scalar, (int)sigma_len, L.xs2, L.ld, L.m_pad, L.n2, always, stream)));
+  FLK_TRY((launch_kmat<T, TIO>(kernel, (const T*)L.xs1, (const T*)L.n1, (const T*)L.xs2, (const T*)L.n2, L.ld,
+                               reinterpret_cast<TIO*>(out), n, m, out_rs, out_cs, stream)));
+  count_launch();
+  return FLK_OK;
+}
 
 // ---------------------------------------------------------------------------------------------
 // Host-buffer variants: stage dense copies of the operands in the workspace, run, copy back.
@@ -754,6 +803,34 @@ int flk_fdmmv_host(int dtype, int kernel, const void* X1, int64_t n, int64_t x1_
   FLK_CUDA_TRY(cudaStreamSynchronize(st));
   if (tc_eligible(dtype, kernel, d, t, flags)) FLK_TRY(check_tc_status(H.inner));
   return FLK_OK;
+}
+
+int64_t flk_fmm_workspace_bytes(int dtype, int64_t n, int64_t m, int64_t d, int flags) {
+  int s = check_common(dtype, FLK_GAUSSIAN, n, m, d, 0);
+  if (s != FLK_OK) return s;
+  const int math = (dtype == FLK_F32 && (flags & FLK_FLAG_FP64_MATH)) ? FLK_F64 : dtype;
+  return make_fmm_layout(nullptr, math, n, m, d).total;
+}
+
+int flk_fmm(int dtype, int kernel, const void* X1, int64_t n, int64_t x1_rs, int64_t x1_cs, const void* X2, int64_t m,
+            int64_t x2_rs, int64_t x2_cs, int64_t d, void* out, int64_t out_rs, int64_t out_cs,
+            const double* sigma_host, int64_t sigma_len, void* workspace, int64_t workspace_bytes, int flags,
+            void* stream) {
+  FLK_TRY(check_common(dtype, kernel, n, m, d, 0));
+  Mat a{X1, n, d, x1_rs, x1_cs}, b{X2, m, d, x2_rs, x2_cs}, oo{out, n, m, out_rs, out_cs};
+  FLK_TRY(check_mat("X1", a, n == 0));
+  FLK_TRY(check_mat("X2", b, m == 0));
+  FLK_TRY(check_mat("out", oo, n == 0 || m == 0));
+  FLK_TRY(check_sigma(sigma_host, sigma_len, d));
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == FLK_F64)
+    return fmm_impl<double, double>(FLK_F64, kernel, a, b, out, out_rs, out_cs, sigma_host, sigma_len, workspace,
+                                    workspace_bytes, st);
+  if (flags & FLK_FLAG_FP64_MATH)
+    return fmm_impl<double, float>(FLK_F64, kernel, a, b, out, out_rs, out_cs, sigma_host, sigma_len, workspace,
+                                   workspace_bytes, st);
+  return fmm_impl<float, float>(FLK_F32, kernel, a, b, out, out_rs, out_cs, sigma_host, sigma_len, workspace,
+                                workspace_bytes, st);
 }
 
 int flk_set_timing(int enable) {

@@ -8,7 +8,8 @@ namespace flk {
 // ---------------------------------------------------------------------------------------------
 // prep_rows: X[n x d] (any of the two legal layouts) -> Xs[n_pad x ld] row-major with
 //   Xs[i,k] = X[i,k] / sigma[k]   (zero for i >= n or k >= d)   and   norms[i] = sum_k Xs[i,k]^2.
-// This is "mat / sigma" + square_norm of distance_kernel.py:151-154 done in one pass.
+// This is "mat / sigma" + square_norm of distance_kernel.py:151-154 done in one pass.  TIn may be
+// narrower than T (fp32 data prepared for fp64 arithmetic, the reference's `no_single_kernel` upcast).
 // A block handles 64 rows; columns are walked in chunks of 64 through a shared tile so that both
 // the read (along whichever stride is 1) and the write (row-major) are coalesced.  The norm is
 // summed by one thread per row in column order, so it is deterministic.
@@ -16,8 +17,8 @@ namespace flk {
 constexpr int kPrepRows = 64;
 constexpr int kPrepCols = 64;
 
-template <typename T>
-__global__ void __launch_bounds__(256) prep_rows_kernel(const T* __restrict__ X, int64_t n, int d,
+template <typename T, typename TIn = T>
+__global__ void __launch_bounds__(256) prep_rows_kernel(const TIn* __restrict__ X, int64_t n, int d,
                                                         int64_t rs, int64_t cs,
                                                         const T* __restrict__ sigma, T sigma_scalar,
                                                         int sigma_len, T* __restrict__ Xs, int ld,
@@ -43,7 +44,7 @@ __global__ void __launch_bounds__(256) prep_rows_kernel(const T* __restrict__ X,
         int r = idx / kPrepCols, k = idx % kPrepCols;
         int64_t gi = row0 + r;
         T val = 0;
-        if (gi < n && k0 + k < d) val = X[gi * rs + (int64_t)(k0 + k)];
+        if (gi < n && k0 + k < d) val = (T)X[gi * rs + (int64_t)(k0 + k)];
         tile[r][k] = val;
       }
     } else {
@@ -51,7 +52,7 @@ __global__ void __launch_bounds__(256) prep_rows_kernel(const T* __restrict__ X,
         int k = idx / kPrepRows, r = idx % kPrepRows;
         int64_t gi = row0 + r;
         T val = 0;
-        if (gi < n && k0 + k < d) val = X[gi * rs + (int64_t)(k0 + k) * cs];
+        if (gi < n && k0 + k < d) val = (T)X[gi * rs + (int64_t)(k0 + k) * cs];
         tile[r][k] = val;
       }
     }

@@ -12,6 +12,7 @@ from typing import Dict, Optional
 
 import torch
 
+from ..mmv_ops.fmm import fmm
 from ..mmv_ops.fmmv import fdmmv, fmmv
 from ..options import FalkonOptions
 
@@ -99,13 +100,38 @@ class Kernel(torch.nn.Module, ABC):
             return self.params
         return dataclasses.replace(self.params, **dataclasses.asdict(opt))
 
-    # ---- full kernel matrix: not part of the kernel-vector-product path ----
+    # ---- the kernel matrix itself (falkon/kernels/kernel.py:135-193) ----
+    @staticmethod
+    def _check_mm_dimensions(X1, X2, diag, out):
+        if X1.dim() != 2:
+            raise ValueError("Matrix X1 must be 2D.")
+        if X2.dim() != 2:
+            raise ValueError("Matrix X2 must be 2D.")
+        N, M = X1.size(0), X2.size(0)
+        if X1.size(1) != X2.size(1):
+            raise ValueError(f"X1 and X2 must have the same number of features ({X1.size(1)} vs {X2.size(1)}).")
+        if diag:
+            if N != M:
+                raise ValueError(f"With diag=True X1 and X2 must have the same number of rows ({N} vs {M}).")
+            if out is not None and out.shape != (N,):
+                raise ValueError(f"Output dimension is incorrect. Expected ({N},) found {tuple(out.shape)}")
+        elif out is not None and out.shape != (N, M):
+            raise ValueError(f"Output dimension is incorrect. Expected ({N}, {M}) found {tuple(out.shape)}")
+        if not _same_dtype(X1, X2, out):
+            raise TypeError("Data types of input matrices must be equal.")
+        return X1, X2, out
+
     def __call__(self, X1, X2, diag: bool = False, out=None, opt=None, kwargs_m1=None, kwargs_m2=None):
-        raise NotImplementedError(
-            "falkon_b200 implements the implicit products Kernel.mmv / Kernel.dmmv only; forming the "
-            "kernel matrix itself (Kernel.__call__, used for K_MM in the preconditioner) stays with the "
-            "reference package."
-        )
+        """``k(X1, X2)``: X1 (N x D), X2 (M x D) -> (N x M), or the diagonal (N,) with ``diag=True``.
+        ``out`` is written in place when given.  Signature of falkon/kernels/kernel.py:135-193."""
+        X1, X2, out = self._check_mm_dimensions(X1, X2, diag, out)
+        params = self._merged(opt)
+        mm_impl = self._decide_mm_impl(X1, X2, diag, params)
+        return mm_impl(kernel=self, opt=params, out=out, diag=diag, X1=X1, X2=X2, kwargs_m1=kwargs_m1,
+                       kwargs_m2=kwargs_m2)
+
+    def _decide_mm_impl(self, X1, X2, diag: bool, opt: FalkonOptions):
+        return fmm
 
     # ---- K v ----
     def mmv(

@@ -1,3 +1,4 @@
+from .fmm import fmm
 from .fmmv import fdmmv, fmmv
 
-__all__ = ("fmmv", "fdmmv")
+__all__ = ("fmm", "fmmv", "fdmmv")

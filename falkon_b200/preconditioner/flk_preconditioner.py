@@ -1,0 +1,179 @@
+"""Falkon's two-level Cholesky preconditioner, kept on the GPU.
+
+Mathematics and method names follow falkon/preconditioner/flk_preconditioner.py:16-299:
+
+    T = chol(K_MM + eps * M * I)            upper triangular, T^T T = K_MM (+ jitter)
+    A = chol(1/M * T T^T + lambda * I)      upper triangular
+
+and the preconditioner is  B~ = 1/sqrt(n) T^-1 A^-1.  ``invA / invAt / invT / invTt`` solve with
+A, A^T, T, T^T; ``apply(v) = T^-1 A^-1 v`` and ``apply_t(v) = A^-T T^-T v``.
+
+What differs from the reference is where the work runs.  The reference packs T and A into the two
+triangles of one M x M buffer and drives cuSOLVER / its own out-of-core LAUUM and POTRF from Python
+so that M x M may exceed GPU memory.  A B200 holds several M x M matrices at M = 50 000 (10 GB each
+in fp32), so this class keeps T and A as two separate device tensors and uses the library
+factorisation and triangular solves of torch (cuSOLVER / cuBLAS): these steps are outside the
+kernel-vector-product hot path.  K_MM itself comes from this package's CUDA kernel (``Kernel.__call__``
+-> ``flk_fmm``), evaluated in fp64 for fp32 data when ``no_single_kernel`` is set, as in the reference.
+"""
+from abc import ABC, abstractmethod
+from typing import Optional
+
+import torch
+
+from ..options import FalkonOptions
+
+__all__ = ("Preconditioner", "FalkonPreconditioner")
+
+
+class Preconditioner(ABC):
+    """Interface of falkon/preconditioner/preconditioner.py: ``init`` then ``apply`` / ``apply_t``."""
+
+    @abstractmethod
+    def init(self, *args, **kwargs):
+        ...
+
+    @abstractmethod
+    def apply(self, v: torch.Tensor) -> torch.Tensor:
+        ...
+
+    @abstractmethod
+    def apply_t(self, v: torch.Tensor) -> torch.Tensor:
+        ...
+
+
+def _require_init(fn):
+    def wrapper(self, *args, **kwargs):
+        if self.T is None or self.A is None:
+            raise RuntimeError("FalkonPreconditioner is not initialized. Please run `init` before any other method.")
+        return fn(self, *args, **kwargs)
+
+    wrapper.__name__ = fn.__name__
+    wrapper.__doc__ = fn.__doc__
+    return wrapper
+
+
+class FalkonPreconditioner(Preconditioner):
+    """Approximate Cholesky preconditioner of the Nystrom kernel-ridge-regression system.
+
+    Parameters
+    ----------
+    penalty
+        The ridge parameter lambda (> 0).
+    kernel
+        Kernel object; ``kernel(X, X)`` gives K_MM.
+    opt
+        ``pc_epsilon_32 / pc_epsilon_64`` (jitter added to K_MM, multiplied by M as in the reference,
+        flk_preconditioner.py:117) and ``no_single_kernel`` are honoured.  ``cpu_preconditioner`` /
+        ``use_cpu`` are rejected: there is no CPU path in this package.
+    """
+
+    def __init__(self, penalty: float, kernel, opt: Optional[FalkonOptions] = None):
+        self.params = opt or FalkonOptions()
+        if self.params.use_cpu or self.params.cpu_preconditioner:
+            raise RuntimeError("falkon_b200 computes the preconditioner on the GPU only "
+                               "(use_cpu / cpu_preconditioner were requested).")
+        self._lambda = float(penalty)
+        self.kernel = kernel
+        self.T: Optional[torch.Tensor] = None
+        self.A: Optional[torch.Tensor] = None
+
+    # the reference exposes the diagonals it has to save because its two factors share a buffer
+    @property
+    def dT(self):
+        return None if self.T is None else self.T.diagonal()
+
+    @property
+    def dA(self):
+        return None if self.A is None else self.A.diagonal()
+
+    def init(self, X: torch.Tensor, weight_vec: Optional[torch.Tensor] = None):
+        """Builds T and A from the (M x D) centres ``X`` (optionally with per-centre weights for
+        re-weighted least squares, flk_preconditioner.py:131-152)."""
+        if weight_vec is not None and weight_vec.shape[0] != X.shape[0]:
+            raise ValueError(
+                f"Weights and Nystrom centers should have the same first dimension. "
+                f"Found instead {weight_vec.shape[0]}, {X.shape[0]}."
+            )
+        if not torch.cuda.is_available():
+            raise RuntimeError("falkon_b200 needs a CUDA device (B200, sm_100); none is available.")
+        dev = X.device if X.is_cuda else torch.device("cuda", torch.cuda.current_device())
+        with torch.inference_mode():
+            Xd = X.to(dev)
+            M = Xd.shape[0]
+            C = self.kernel(Xd, Xd, opt=self.params)  # M x M, data dtype
+            eps = self.params.pc_epsilon(C.dtype)
+            C.diagonal().add_(eps * M)
+            # T^T T = C.  `cholesky_ex` reports failure as a status instead of a device assert.
+            T, info = torch.linalg.cholesky_ex(C, upper=True)
+            if int(info.item()) != 0:
+                raise RuntimeError(
+                    f"Cholesky factorisation of K_MM failed at leading minor {int(info.item())}: "
+                    f"K_MM is not positive definite; increase pc_epsilon (now {eps})."
+                )
+            del C
+            TTt = T @ T.mT
+            if weight_vec is not None:
+                s = weight_vec.to(dev, TTt.dtype).reshape(-1).sqrt()
+                TTt.mul_(s.reshape(-1, 1)).mul_(s.reshape(1, -1))
+            TTt.mul_(1.0 / M)
+            TTt.diagonal().add_(self._lambda)
+            A, info = torch.linalg.cholesky_ex(TTt, upper=True)
+            if int(info.item()) != 0:
+                raise RuntimeError(
+                    f"Cholesky factorisation of 1/M T T^T + lambda I failed at leading minor {int(info.item())}."
+                )
+            del TTt
+            self.T, self.A = T, A
+        return self
+
+    def to(self, device):
+        if self.T is not None:
+            self.T = self.T.to(device)
+        if self.A is not None:
+            self.A = self.A.to(device)
+        return self
+
+    @staticmethod
+    def _solve(tri: torch.Tensor, v: torch.Tensor, transpose: bool) -> torch.Tensor:
+        vec = v.dim() == 1
+        rhs = v.reshape(-1, 1) if vec else v
+        rhs = rhs.to(tri.device)
+        if transpose:
+            out = torch.linalg.solve_triangular(tri.mT, rhs, upper=False)
+        else:
+            out = torch.linalg.solve_triangular(tri, rhs, upper=True)
+        return out.reshape(-1) if vec else out
+
+    @_require_init
+    def invA(self, v: torch.Tensor) -> torch.Tensor:
+        """Solves A x = v."""
+        return self._solve(self.A, v, transpose=False)
+
+    @_require_init
+    def invAt(self, v: torch.Tensor) -> torch.Tensor:
+        """Solves A^T x = v."""
+        return self._solve(self.A, v, transpose=True)
+
+    @_require_init
+    def invT(self, v: torch.Tensor) -> torch.Tensor:
+        """Solves T x = v."""
+        return self._solve(self.T, v, transpose=False)
+
+    @_require_init
+    def invTt(self, v: torch.Tensor) -> torch.Tensor:
+        """Solves T^T x = v."""
+        return self._solve(self.T, v, transpose=True)
+
+    @_require_init
+    def apply(self, v: torch.Tensor) -> torch.Tensor:
+        """T^-1 A^-1 v: maps a preconditioned solution beta back to the coefficients alpha."""
+        return self.invT(self.invA(v))
+
+    @_require_init
+    def apply_t(self, v: torch.Tensor) -> torch.Tensor:
+        """A^-T T^-T v: applied to the right-hand side K_nm^T y / n."""
+        return self.invAt(self.invTt(v))
+
+    def __str__(self):
+        return f"FalkonPreconditioner(_lambda={self._lambda}, kernel={self.kernel})"

@@ -54,6 +54,7 @@ typedef enum flk_kernel {
 /* Bits of the `flags` argument. */
 #define FLK_FLAG_FORCE_SIMT 1 /* never use the tensor-core kernel (diagnostics / comparison) */
 #define FLK_FLAG_FORCE_TC 2   /* fail with FLK_ERR_UNSUPPORTED instead of using the SIMT kernel */
+#define FLK_FLAG_FP64_MATH 4  /* flk_fmm only: evaluate fp32 data in fp64, round once on store   */
 
 /* Library version (major * 10000 + minor * 100 + patch). */
 int flk_version(void);
@@ -184,6 +185,21 @@ int flk_fmmv_static(int dtype, int kernel,
                     const void* v, int64_t t, int64_t v_rs, int64_t v_cs,
                     void* out, int64_t out_rs, int64_t out_cs,
                     double sigma, int flags, void* stream);
+
+/*
+ * Kernel matrix  out[n x m] = k(X1, X2)  (the reference's fmm, falkon/mmv_ops/fmm.py:298-388, which
+ * the preconditioner calls once per fit on the centres, falkon/preconditioner/flk_preconditioner.py:89).
+ * `out` has the data's dtype and either memory order.  With FLK_FLAG_FP64_MATH fp32 data is
+ * evaluated in fp64 and rounded once on store -- the reference's `no_single_kernel` default
+ * (falkon/mmv_ops/fmm.py:619-622), which keeps the Cholesky factorisations that follow stable.
+ */
+int64_t flk_fmm_workspace_bytes(int dtype, int64_t n, int64_t m, int64_t d, int flags);
+int flk_fmm(int dtype, int kernel,
+            const void* X1, int64_t n, int64_t x1_rs, int64_t x1_cs,
+            const void* X2, int64_t m, int64_t x2_rs, int64_t x2_cs, int64_t d,
+            void* out, int64_t out_rs, int64_t out_cs,
+            const double* sigma_host, int64_t sigma_len,
+            void* workspace, int64_t workspace_bytes, int flags, void* stream);
 
 /*
  * Counters for the calling process: number of kernels this library has launched and the status
