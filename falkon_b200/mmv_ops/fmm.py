@@ -61,15 +61,14 @@ def fmm(
     check_contiguity((X1, "X1"), (X2, "X2"), (out, "out"))
     _require_cuda(opt, X1, X2)
     n, m = X1.shape[0], X2.shape[0]
+    if out is None:  # created outside inference mode, as in the reference: the caller may update it in place
+        out_dev = X1.device
+        if diag:
+            out = torch.empty((n,), dtype=X1.dtype, device=out_dev)
+        else:
+            out = create_same_stride((n, m), X1, X1.dtype, device=out_dev, pin_memory=out_dev.type != "cuda")
     with torch.inference_mode():
-        dev = _pick_device((X1.device, X2.device) + ((out.device,) if out is not None else ()))
-        if out is None:
-            out_dev = X1.device
-            shape = (n,) if diag else (n, m)
-            if diag:
-                out = torch.empty(shape, dtype=X1.dtype, device=out_dev)
-            else:
-                out = create_same_stride(shape, X1, X1.dtype, device=out_dev, pin_memory=out_dev.type != "cuda")
+        dev = _pick_device((X1.device, X2.device, out.device))
         o_dev = out if out.device == dev else torch.empty(out.shape, dtype=out.dtype, device=dev)
         if diag:
             _diag_kernel(_to_dev(X1, dev), _to_dev(X2, dev), kernel_id, sigma, o_dev)

@@ -88,8 +88,9 @@ def fmmv(
         v = v.reshape(-1, 1)
     data_devs = (X1.device, X2.device, v.device)
     n, t = X1.shape[0], v.shape[1]
+    # created outside inference mode, as in the reference (fmmv.py:909-912): the caller may update it in place
+    out = create_output_mat(out, data_devs, (n, t), v.dtype, "cuda", X1)
     with torch.inference_mode():
-        out = create_output_mat(out, data_devs, (n, t), v.dtype, "cuda", X1)
         dev = _pick_device(data_devs + (out.device,))
         all_host = all(d.type == "cpu" for d in data_devs) and out.device.type == "cpu"
         if all_host:
@@ -143,8 +144,8 @@ def fdmmv(
     m = X2.shape[0]
     t = v.shape[1] if v is not None else w.shape[1]
     dtype = v.dtype if v is not None else w.dtype
+    out = create_output_mat(out, data_devs, (m, t), dtype, "cuda", X1)
     with torch.inference_mode():
-        out = create_output_mat(out, data_devs, (m, t), dtype, "cuda", X1)
         dev = _pick_device(tuple(data_devs) + (out.device,))
         all_host = all(d.type == "cpu" for d in data_devs) and out.device.type == "cpu"
         if all_host:

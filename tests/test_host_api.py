@@ -74,8 +74,15 @@ def test_dimension_and_dtype_errors_follow_reference():
         k.dmmv(X, C, v, w, out=torch.empty(10, 2))
     with pytest.raises(TypeError):
         k.mmv(X.double(), C, v)
-    with pytest.raises(NotImplementedError):
-        k(X, C)
+    # the kernel matrix validates like the reference (falkon/kernels/kernel.py:107-133)
+    with pytest.raises(ValueError):
+        k(X, C[:, :2])
+    with pytest.raises(ValueError):
+        k(X, C, out=torch.empty(3, 3))
+    with pytest.raises(TypeError):
+        k(X.double(), C)
+    with pytest.raises(ValueError):
+        k(X, C, diag=True)  # different numbers of rows
 
 
 def test_products_fail_loudly_without_gpu_or_with_use_cpu():

@@ -64,6 +64,58 @@ def test_sharded_products_world2_gloo():
         assert ret[r][0] < 1e-10 and ret[r][1] < 1e-10 and ret[r][2] < 1e-10, ret[r]
 
 
+def _cg_worker(rank, world, port, ret):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests", "golden"))
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from falkon_b200.kernels import GaussianKernel
+        from falkon_b200.optim import FalkonConjugateGradient
+        from falkon_b200.sharded import ShardedKernelOps, shard_rows
+        from oracle import falkon_fit_oracle as ffo
+        from oracle import falkon_oracle as fo
+
+        rng = np.random.default_rng(21)
+        n, m, d, t = 2003, 60, 4, 2
+        X = torch.from_numpy(rng.standard_normal((n, d)))
+        Y = torch.from_numpy(np.sin(X.numpy() @ rng.standard_normal((d, t))))
+        penalty, maxiter, seed = 1e-4, 12, 5
+        alpha_ref, beta_ref, idx = ffo.falkon_fit(X, Y, "gaussian", 2.0, None, penalty, m, maxiter, seed)
+        C = X[torch.from_numpy(idx)]
+        start, length = shard_rows(n, world, rank)
+        Xs, Ys = X[start : start + length], Y[start : start + length]
+
+        def local_mmv(A, B, vec, out=None, opt=None):
+            return fo.fmmv(A, B, vec, "gaussian", 2.0)
+
+        def local_dmmv(A, B, vec, ww, out=None, opt=None):
+            return fo.fdmmv(A, B, vec, ww, "gaussian", 2.0)
+
+        ops = ShardedKernelOps(GaussianKernel(2.0), local_mmv=local_mmv, local_dmmv=local_dmmv)
+        # the CPU oracle's preconditioner has the method names the solver calls (invA, invT, invTt, invAt, apply_t)
+        pc = ffo.Preconditioner(C, "gaussian", 2.0, None, penalty)
+        solver = FalkonConjugateGradient(ops, pc)
+        beta = solver.solve(Xs, C, Ys, penalty, None, maxiter, n=n)
+        ret[rank] = (fo.rel_l2(beta.numpy(), beta_ref.numpy()), fo.rel_l2(pc.apply(beta).numpy(), alpha_ref.numpy()))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_falkon_cg_world2_gloo():
+    """The Falkon CG on two row shards (right-hand side and every dmmv all-reduced, n = global row count)
+    reproduces the single-process solution."""
+    world = 2
+    port = 31500 + (os.getpid() % 2000)
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_cg_worker, args=(world, port, ret), nprocs=world, join=True)
+    assert sorted(ret.keys()) == [0, 1]
+    for r in range(world):
+        assert ret[r][0] < 1e-9 and ret[r][1] < 1e-8, ret[r]
+
+
 def test_shard_rows_partition():
     sys.path.insert(0, ROOT)
     from falkon_b200.sharded import shard_rows
