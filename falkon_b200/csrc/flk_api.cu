@@ -379,9 +379,9 @@ static inline Gate gate_simt(const Layout& L) { return L.tc ? Gate{L.range_flag(
 // flag) and, gated, the scaled rows + norms of the SIMT kernels.
 template <typename T>
 static int prepare_operands(const Layout& L, int kernel, const Mat& X1, const Mat& X2, int64_t d, const T* sig_dev,
-                            T sig_scalar, int sigma_len, int dtype, cudaStream_t stream) {
+                            T sig_scalar, int sigma_len, int dtype, bool reset_status, cudaStream_t stream) {
   if (L.tc) {
-    FLK_CUDA_TRY(cudaMemsetAsync(L.status, 0, 256, stream));
+    if (reset_status) FLK_CUDA_TRY(cudaMemsetAsync(L.status, 0, 256, stream));
     FLK_TRY(tc::prep_images(kernel, X1.ptr, X1.rows, X1.rs, X1.cs, (int)d, (const float*)sig_dev, (float)sig_scalar,
                             sigma_len, L.s1.r_pad, L.x1.img_a, L.x1.img_b, reinterpret_cast<int*>(L.status), stream));
     FLK_TRY(tc::prep_images(kernel, X2.ptr, X2.rows, X2.rs, X2.cs, (int)d, (const float*)sig_dev, (float)sig_scalar,
@@ -420,7 +420,7 @@ static int sweep_and_finalize(const Layout& L, int kernel, int dtype, int64_t d,
 template <typename T>
 static int fmmv_impl(int dtype, int kernel, const Mat& X1, const Mat& X2, const Mat& v, void* out,
                      int64_t out_rs, int64_t out_cs, const double* sigma, int64_t sigma_len, void* ws,
-                     int64_t ws_bytes, int flags, cudaStream_t stream) {
+                     int64_t ws_bytes, int flags, cudaStream_t stream, bool reset_status = true) {
   const int64_t n = X1.rows, m = X2.rows, d = X1.cols, t = v.cols;
   Layout L = make_layout(ws, false, true, dtype, kernel, n, m, d, t, flags);
   if ((flags & FLK_FLAG_FORCE_TC) && !L.tc)
@@ -430,17 +430,21 @@ static int fmmv_impl(int dtype, int kernel, const Mat& X1, const Mat& X2, const 
   T sig_scalar;
   const T* sig_dev;
   FLK_TRY(upload_sigma<T>(sigma, sigma_len, L.sigma, &sig_scalar, &sig_dev, stream));
-  FLK_TRY(prepare_operands<T>(L, kernel, X1, X2, d, sig_dev, sig_scalar, (int)sigma_len, dtype, stream));
+  FLK_TRY(prepare_operands<T>(L, kernel, X1, X2, d, sig_dev, sig_scalar, (int)sigma_len, dtype, reset_status, stream));
   FLK_TRY(run_prep_vec<T>(v, L.vbuf, L.s1.s_pad, L.s1.tp, L.s1.tt, stream));
   FLK_TRY(sweep_and_finalize<T>(L, kernel, dtype, d, t, L.s1, L.f1, L.x1, L.x2, L.vbuf, L.raw1, L.fraw1, nullptr,
                                 out, out_rs, out_cs, false, stream, 0));
   return FLK_OK;
 }
 
+// `accumulate`: add the result to what `out` already holds (row chunks of X1 are summed this way by the
+// host-buffer entry point); `reset_status`: clear the status block first (false for all chunks but the first,
+// so that a timeout code or a raised range flag of an earlier chunk stays visible).
 template <typename T>
 static int fdmmv_impl(int dtype, int kernel, const Mat& X1, const Mat& X2, const Mat& v, const Mat& w, int64_t t,
                       void* out, int64_t out_rs, int64_t out_cs, const double* sigma, int64_t sigma_len,
-                      void* ws, int64_t ws_bytes, int flags, cudaStream_t stream) {
+                      void* ws, int64_t ws_bytes, int flags, cudaStream_t stream, bool accumulate = false,
+                      bool reset_status = true) {
   const int64_t n = X1.rows, m = X2.rows, d = X1.cols;
   const bool has_v = v.ptr != nullptr, has_w = w.ptr != nullptr;
   Layout L = make_layout(ws, true, has_v, dtype, kernel, n, m, d, t, flags);
@@ -451,7 +455,7 @@ static int fdmmv_impl(int dtype, int kernel, const Mat& X1, const Mat& X2, const
   T sig_scalar;
   const T* sig_dev;
   FLK_TRY(upload_sigma<T>(sigma, sigma_len, L.sigma, &sig_scalar, &sig_dev, stream));
-  FLK_TRY(prepare_operands<T>(L, kernel, X1, X2, d, sig_dev, sig_scalar, (int)sigma_len, dtype, stream));
+  FLK_TRY(prepare_operands<T>(L, kernel, X1, X2, d, sig_dev, sig_scalar, (int)sigma_len, dtype, reset_status, stream));
   if (has_v) {
     // sweep 1: u = K v (+ w), kept as a padded vector operand
     FLK_TRY(run_prep_vec<T>(v, L.vbuf, L.s1.s_pad, L.s1.tp, L.s1.tt, stream));
@@ -461,8 +465,9 @@ static int fdmmv_impl(int dtype, int kernel, const Mat& X1, const Mat& X2, const
     FLK_TRY(run_prep_vec<T>(w, L.ubuf, L.s1.r_pad, L.s1.tp, L.s1.tt, stream));
   }
   // sweep 2: out = K^T u  (rows = X2, reduction over X1)
-  FLK_TRY(sweep_and_finalize<T>(L, kernel, dtype, d, t, L.s2, L.f2, L.x2, L.x1, L.ubuf, L.raw2, L.fraw2, nullptr,
-                                out, out_rs, out_cs, false, stream, 1));
+  const Mat prev{out, m, t, out_rs, out_cs};
+  FLK_TRY(sweep_and_finalize<T>(L, kernel, dtype, d, t, L.s2, L.f2, L.x2, L.x1, L.ubuf, L.raw2, L.fraw2,
+                                accumulate ? &prev : nullptr, out, out_rs, out_cs, false, stream, 1));
   return FLK_OK;
 }
 
@@ -586,7 +591,12 @@ struct HostLayout {
   void* inner = nullptr;
   int64_t inner_bytes = 0;
   int64_t total = 0;
+  int n_chunks = 1;        // row chunks of X1: the copy of chunk c + 1 runs under the kernels of chunk c
+  int64_t chunk_rows = 0;  // rows per chunk (the last one may be shorter)
 };
+
+constexpr int kMaxHostChunks = 4;
+constexpr int64_t kMinChunkRows = 131072;
 
 static HostLayout make_host_layout(void* ws, bool dmmv, int dtype, int kernel, const Mat& X1, const Mat& X2,
                                    const Mat& v, const Mat& w, const Mat& out, int64_t t, int flags) {
@@ -598,10 +608,104 @@ static HostLayout make_host_layout(void* ws, bool dmmv, int dtype, int kernel, c
   H.v = plan_stage(v, es, c);
   H.w = plan_stage(w, es, c);
   H.out = plan_stage(out, es, c);
-  H.inner_bytes = make_layout(nullptr, dmmv, v.ptr != nullptr, dtype, kernel, X1.rows, X2.rows, X1.cols, t, flags).total;
+  const int64_t n = X1.rows;
+  H.n_chunks = (int)std::max<int64_t>(1, std::min<int64_t>(kMaxHostChunks, n / kMinChunkRows));
+  H.chunk_rows = round_up(ceil_div(std::max<int64_t>(n, 1), H.n_chunks), kRowPad);
+  H.n_chunks = (int)ceil_div(std::max<int64_t>(n, 1), H.chunk_rows);
+  H.inner_bytes = make_layout(nullptr, dmmv, v.ptr != nullptr, dtype, kernel, std::min(n, H.chunk_rows), X2.rows,
+                              X1.cols, t, flags).total;
   H.inner = c.take(H.inner_bytes);
   H.total = c.off;
   return H;
+}
+
+// Rows [r0, r0 + rows) of a matrix (a view: same strides).
+static Mat row_block(const Mat& m, int64_t r0, int64_t rows, int64_t es) {
+  Mat b = m;
+  if (m.ptr != nullptr) b.ptr = reinterpret_cast<const char*>(m.ptr) + r0 * m.rs * es;
+  b.rows = rows;
+  return b;
+}
+
+// One copy stream and a few events per device, created on first use and kept for the life of the
+// process: the host-buffer entry points push their host->device copies through it so that they
+// overlap the kernels running on the caller's stream.
+struct CopyLane {
+  cudaStream_t stream = nullptr;
+  cudaEvent_t ev[kMaxHostChunks + 2] = {};
+  bool ready = false;
+};
+static CopyLane g_copy_lane[64];
+
+static int copy_lane_for_current_device(CopyLane** out) {
+  int dev = 0;
+  FLK_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(FLK_ERR_UNSUPPORTED, "device ordinal %d not supported", dev);
+  CopyLane& L = g_copy_lane[dev];
+  if (!L.ready) {
+    FLK_CUDA_TRY(cudaStreamCreateWithFlags(&L.stream, cudaStreamNonBlocking));
+    for (auto& e : L.ev) FLK_CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    L.ready = true;
+  }
+  *out = &L;
+  return FLK_OK;
+}
+
+// Shared body of the two host-buffer entry points.
+static int run_host(bool dmmv, int dtype, int kernel, const Mat& a, const Mat& b, const Mat& vv, const Mat& ww,
+                    const Mat& oo, int64_t t, const double* sigma_host, int64_t sigma_len, void* workspace,
+                    int64_t workspace_bytes, int flags, cudaStream_t st) {
+  const int64_t n = a.rows, m = b.rows, d = a.cols;
+  HostLayout H = make_host_layout(workspace, dmmv, dtype, kernel, a, b, vv, ww, oo, t, flags);
+  FLK_TRY(check_workspace(workspace, workspace_bytes, H.total));
+  if (t == 0 || (dmmv ? m == 0 : n == 0)) return FLK_OK;
+  const int64_t es = esize(dtype);
+  CopyLane* lane = nullptr;
+  FLK_TRY(copy_lane_for_current_device(&lane));
+  // the copies must not overtake earlier work of the caller's stream that may still use the workspace
+  FLK_CUDA_TRY(cudaEventRecord(lane->ev[0], st));
+  FLK_CUDA_TRY(cudaStreamWaitEvent(lane->stream, lane->ev[0], 0));
+  FLK_TRY(copy_matrix(H.x2.dev, b, es, cudaMemcpyHostToDevice, lane->stream));
+  FLK_TRY(copy_matrix(H.v.dev, vv, es, cudaMemcpyHostToDevice, lane->stream));
+  FLK_CUDA_TRY(cudaEventRecord(lane->ev[1], lane->stream));
+  for (int c = 0; c < H.n_chunks; ++c) {
+    const int64_t r0 = (int64_t)c * H.chunk_rows, rows = std::min(H.chunk_rows, n - r0);
+    FLK_TRY(copy_matrix(row_block(H.x1.dev, r0, rows, es), row_block(a, r0, rows, es), es, cudaMemcpyHostToDevice,
+                        lane->stream));
+    if (dmmv)
+      FLK_TRY(copy_matrix(row_block(H.w.dev, r0, rows, es), row_block(ww, r0, rows, es), es, cudaMemcpyHostToDevice,
+                          lane->stream));
+    FLK_CUDA_TRY(cudaEventRecord(lane->ev[2 + c], lane->stream));
+  }
+  FLK_CUDA_TRY(cudaStreamWaitEvent(st, lane->ev[1], 0));
+  for (int c = 0; c < H.n_chunks; ++c) {
+    const int64_t r0 = (int64_t)c * H.chunk_rows, rows = std::min(H.chunk_rows, n - r0);
+    FLK_CUDA_TRY(cudaStreamWaitEvent(st, lane->ev[2 + c], 0));
+    const Mat xa = row_block(H.x1.dev, r0, rows, es);
+    if (dmmv) {
+      const Mat wc = row_block(H.w.dev, r0, rows, es);
+      void* o = const_cast<void*>(H.out.dev.ptr);
+      if (dtype == FLK_F32)
+        FLK_TRY(fdmmv_impl<float>(dtype, kernel, xa, H.x2.dev, H.v.dev, wc, t, o, H.out.dev.rs, H.out.dev.cs,
+                                  sigma_host, sigma_len, H.inner, H.inner_bytes, flags, st, c > 0, c == 0));
+      else
+        FLK_TRY(fdmmv_impl<double>(dtype, kernel, xa, H.x2.dev, H.v.dev, wc, t, o, H.out.dev.rs, H.out.dev.cs,
+                                   sigma_host, sigma_len, H.inner, H.inner_bytes, flags, st, c > 0, c == 0));
+    } else {
+      const Mat oc = row_block(H.out.dev, r0, rows, es);
+      void* o = const_cast<void*>(oc.ptr);
+      if (dtype == FLK_F32)
+        FLK_TRY(fmmv_impl<float>(dtype, kernel, xa, H.x2.dev, H.v.dev, o, oc.rs, oc.cs, sigma_host, sigma_len,
+                                 H.inner, H.inner_bytes, flags, st, c == 0));
+      else
+        FLK_TRY(fmmv_impl<double>(dtype, kernel, xa, H.x2.dev, H.v.dev, o, oc.rs, oc.cs, sigma_host, sigma_len,
+                                  H.inner, H.inner_bytes, flags, st, c == 0));
+    }
+  }
+  FLK_TRY(copy_matrix(oo, H.out.dev, es, cudaMemcpyDeviceToHost, st));
+  FLK_CUDA_TRY(cudaStreamSynchronize(st));
+  if (tc_eligible(dtype, kernel, d, t, flags)) FLK_TRY(check_tc_status(H.inner));
+  return FLK_OK;
 }
 
 }  // namespace flk
@@ -754,21 +858,8 @@ int flk_fmmv_host(int dtype, int kernel, const void* X1, int64_t n, int64_t x1_r
   FLK_TRY(check_mat("v", vv, m == 0 || t == 0));
   FLK_TRY(check_mat("out", oo, n == 0 || t == 0));
   FLK_TRY(check_sigma(sigma_host, sigma_len, d));
-  HostLayout H = make_host_layout(workspace, false, dtype, kernel, a, b, vv, ww, oo, t, flags);
-  FLK_TRY(check_workspace(workspace, workspace_bytes, H.total));
-  if (n == 0 || t == 0) return FLK_OK;
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  const int64_t es = esize(dtype);
-  FLK_TRY(copy_matrix(H.x1.dev, a, es, cudaMemcpyHostToDevice, st));
-  FLK_TRY(copy_matrix(H.x2.dev, b, es, cudaMemcpyHostToDevice, st));
-  FLK_TRY(copy_matrix(H.v.dev, vv, es, cudaMemcpyHostToDevice, st));
-  FLK_TRY(flk_fmmv(dtype, kernel, H.x1.dev.ptr, n, H.x1.dev.rs, H.x1.dev.cs, H.x2.dev.ptr, m, H.x2.dev.rs,
-                   H.x2.dev.cs, d, H.v.dev.ptr, t, H.v.dev.rs, H.v.dev.cs, const_cast<void*>(H.out.dev.ptr),
-                   H.out.dev.rs, H.out.dev.cs, sigma_host, sigma_len, H.inner, H.inner_bytes, flags, stream));
-  FLK_TRY(copy_matrix(oo, H.out.dev, es, cudaMemcpyDeviceToHost, st));
-  FLK_CUDA_TRY(cudaStreamSynchronize(st));
-  if (tc_eligible(dtype, kernel, d, t, flags)) FLK_TRY(check_tc_status(H.inner));
-  return FLK_OK;
+  return run_host(false, dtype, kernel, a, b, vv, ww, oo, t, sigma_host, sigma_len, workspace, workspace_bytes, flags,
+                  reinterpret_cast<cudaStream_t>(stream));
 }
 
 int flk_fdmmv_host(int dtype, int kernel, const void* X1, int64_t n, int64_t x1_rs, int64_t x1_cs, const void* X2,
@@ -786,23 +877,8 @@ int flk_fdmmv_host(int dtype, int kernel, const void* X1, int64_t n, int64_t x1_
   FLK_TRY(check_mat("w", ww, true));
   FLK_TRY(check_mat("out", oo, m == 0 || t == 0));
   FLK_TRY(check_sigma(sigma_host, sigma_len, d));
-  HostLayout H = make_host_layout(workspace, true, dtype, kernel, a, b, vv, ww, oo, t, flags);
-  FLK_TRY(check_workspace(workspace, workspace_bytes, H.total));
-  if (m == 0 || t == 0) return FLK_OK;
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  const int64_t es = esize(dtype);
-  FLK_TRY(copy_matrix(H.x1.dev, a, es, cudaMemcpyHostToDevice, st));
-  FLK_TRY(copy_matrix(H.x2.dev, b, es, cudaMemcpyHostToDevice, st));
-  FLK_TRY(copy_matrix(H.v.dev, vv, es, cudaMemcpyHostToDevice, st));
-  FLK_TRY(copy_matrix(H.w.dev, ww, es, cudaMemcpyHostToDevice, st));
-  FLK_TRY(flk_fdmmv(dtype, kernel, H.x1.dev.ptr, n, H.x1.dev.rs, H.x1.dev.cs, H.x2.dev.ptr, m, H.x2.dev.rs,
-                    H.x2.dev.cs, d, H.v.dev.ptr, H.v.dev.rs, H.v.dev.cs, H.w.dev.ptr, H.w.dev.rs, H.w.dev.cs, t,
-                    const_cast<void*>(H.out.dev.ptr), H.out.dev.rs, H.out.dev.cs, sigma_host, sigma_len, H.inner,
-                    H.inner_bytes, flags, stream));
-  FLK_TRY(copy_matrix(oo, H.out.dev, es, cudaMemcpyDeviceToHost, st));
-  FLK_CUDA_TRY(cudaStreamSynchronize(st));
-  if (tc_eligible(dtype, kernel, d, t, flags)) FLK_TRY(check_tc_status(H.inner));
-  return FLK_OK;
+  return run_host(true, dtype, kernel, a, b, vv, ww, oo, t, sigma_host, sigma_len, workspace, workspace_bytes, flags,
+                  reinterpret_cast<cudaStream_t>(stream));
 }
 
 int64_t flk_fmm_workspace_bytes(int dtype, int64_t n, int64_t m, int64_t d, int flags) {

@@ -129,6 +129,12 @@ int flk_fdmmv(int dtype, int kernel,
  * stream has been synchronised, so `out` is valid on return.  This is the reference's
  * "data on the CPU, compute on the GPU" case (falkon/mmv_ops/fmmv.py:798-854, :1080-1125)
  * for one GPU.  The workspace must hold flk_*_host_workspace_bytes bytes of DEVICE memory.
+ *
+ * From 262,144 rows up, X1 (and w) travel in up to four row chunks through a copy stream that
+ * the library creates once per device (with a handful of events) and keeps: the copy of chunk
+ * c + 1 overlaps the kernels of chunk c on the caller's stream; fdmmv sums the per-chunk results
+ * in a fixed order (bit-reproducible, but not bit-identical to the one-piece device call).
+ * Not for concurrent calls from several host threads on one device.
  */
 int64_t flk_fmmv_host_workspace_bytes(int dtype, int kernel, int64_t n, int64_t m, int64_t d,
                                       int64_t t, int flags);
