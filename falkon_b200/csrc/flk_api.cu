@@ -8,6 +8,7 @@
 #include "flk_prep.cuh"
 #include "flk_simt.cuh"
 #include "flk_tc.cuh"
+#include "flk_wide.cuh"
 
 namespace flk {
 
@@ -94,21 +95,26 @@ struct SweepPlan {
   int64_t raw_elems() const { return (int64_t)n_chunks * r_pad * tp; }
 };
 
-static void choose_tt(int64_t t, int* tt, int* tp) {
+// Vector columns per pass: 1, 2 or 4 for the kernels that keep the whole contraction in registers;
+// 32 (the wide kernel, flk_wide.cuh) when the SIMT path is the primary one and there are more than four.
+static void choose_tt(int64_t t, bool allow_wide, int* tt, int* tp) {
   if (t <= 1) *tt = 1;
   else if (t == 2) *tt = 2;
-  else *tt = 4;
+  else if (t <= 4 || !allow_wide) *tt = 4;
+  else *tt = kWideT;
   *tp = (int)round_up(std::max<int64_t>(t, 1), *tt);
 }
 
-static SweepPlan plan_sweep(bool tc, int dtype, int64_t r, int64_t s, int64_t t) {
+// `allow_wide`: the plan may use the wide kernel (never for the tensor-core kernel, and never for its SIMT
+// alternative, which shares the vector buffers of the tensor-core plan and therefore its column grouping).
+static SweepPlan plan_sweep(bool tc, int dtype, int64_t r, int64_t s, int64_t t, bool allow_wide = false) {
   SweepPlan p;
   p.tc = tc;
   p.r = r;
   p.s = s;
   p.r_pad = round_up(std::max<int64_t>(r, 1), kRowPad);
   p.s_pad = round_up(std::max<int64_t>(s, 1), kRowPad);
-  choose_tt(t, &p.tt, &p.tp);
+  choose_tt(t, allow_wide && !tc, &p.tt, &p.tp);
   p.t_chunks = p.tp / p.tt;
   if (tc) {
     p.br = tc::kRowsPerCta;
@@ -122,7 +128,7 @@ static SweepPlan plan_sweep(bool tc, int dtype, int64_t r, int64_t s, int64_t t)
   // Split the reduction side into chunks so that the grid fills whole waves of the 148 SMs:
   // among the chunk counts that give at least two waves (when the problem allows), take the one
   // with the best wave efficiency, preferring fewer chunks (less partial-result traffic).
-  const int64_t resident = tc ? 1 : ((dtype == FLK_F32 && p.tt == 1) ? 2 : 1);
+  const int64_t resident = tc ? 1 : ((dtype == FLK_F32 && p.tt == 1) ? 2 : 1);  // CTAs per SM
   const int64_t slots = kNumSMs * resident;
   const int64_t ctas_rows = (int64_t)p.row_tiles * p.t_chunks;
   const int64_t min_tiles = tc ? 8 : 4;  // keep the row tile's staging cost amortised
@@ -208,8 +214,8 @@ static Layout make_layout(void* ws, bool dmmv, bool has_v, int dtype, int kernel
   Carver c(ws);
   L.status = c.take(256);
   L.sigma = c.take(std::max<int64_t>(d, 1) * es);
-  L.s1 = plan_sweep(L.tc, dtype, n, m, t);  // rows = X1, reduction over X2
-  L.s2 = plan_sweep(L.tc, dtype, m, n, t);  // rows = X2, reduction over X1 (fdmmv only)
+  L.s1 = plan_sweep(L.tc, dtype, n, m, t, !L.tc);  // rows = X1, reduction over X2
+  L.s2 = plan_sweep(L.tc, dtype, m, n, t, !L.tc);  // rows = X2, reduction over X1 (fdmmv only)
   const int64_t n_pad = L.s1.r_pad, m_pad = L.s1.s_pad;
   const bool first = !dmmv || has_v;  // is the first sweep executed?
   if (L.tc) {
@@ -342,7 +348,10 @@ static int run_sweep_simt(int kernel, const SweepPlan& sp, const Operand& a, con
   args.gate = gate;
   const bool timed = gate.flag == nullptr;  // the gated alternative is not the timed kernel
   if (timed) FLK_TRY(timer_mark(2 * sweep_idx, stream));
-  FLK_TRY((launch_simt_any<T>(kernel, args, sp.tt, sp.n_chunks, sp.t_chunks, stream)));
+  if (sp.tt == kWideT)
+    FLK_TRY((launch_wide_any<T>(kernel, args, sp.n_chunks, sp.t_chunks, stream)));
+  else
+    FLK_TRY((launch_simt_any<T>(kernel, args, sp.tt, sp.n_chunks, sp.t_chunks, stream)));
   if (timed) FLK_TRY(timer_mark(2 * sweep_idx + 1, stream));
   count_launch();
   return FLK_OK;
