@@ -241,6 +241,120 @@ def run_fit(args):
     }))
 
 
+def _dense_fdmmv_fp64(X, C, v, w, kind, sigma, rows_per_block=4096):
+    """K^T (K v + w) in fp64 by explicit blocks of torch ops on the GPU (spot-check of the other configurations;
+    explicit differences through cdist, no norm expansion)."""
+    out = torch.zeros(C.shape[0], v.shape[1], dtype=torch.float64, device=X.device)
+    Cs = C.double() / sigma
+    for r0 in range(0, X.shape[0], rows_per_block):
+        Xb = X[r0:r0 + rows_per_block].double() / sigma
+        d = torch.cdist(Xb, Cs, compute_mode="donot_use_mm_for_euclid_dist")
+        if kind == "gaussian":
+            K = torch.exp(-0.5 * d * d)
+        else:  # Matern 2.5
+            r = 5.0 ** 0.5 * d
+            K = (1.0 + r + r * r / 3.0) * torch.exp(-r)
+        u = K @ v.double()
+        if w is not None:
+            u += w[r0:r0 + rows_per_block].double()
+        out += K.T @ u
+    return out
+
+
+def run_config(args):
+    """The other benchmark configurations as measured data points (not the default line):
+    --config 4: fdmmv Gaussian sigma = 1, d = 9 Uniform[0,1), M = 100,000, w = 0, N = 10^8 sharded over the
+                GPUs (12.5e6 rows per GPU at any GPU count), fp32 or fp64 (--dtype);
+    --config 5: fdmmv Matern 2.5 sigma = 10, fp64, N = 2e6 x d = 128 N(0,1), M = 30,000, T = 32, w ~ N(0,1), one GPU."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a GPU (there is no CPU fallback)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    import torch.distributed as dist
+
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    from falkon_b200 import _lib
+    from falkon_b200.kernels import GaussianKernel, MaternKernel
+    from falkon_b200.sharded import ShardedKernelOps
+
+    _lib.build()
+    dtype = torch.float64 if (args.dtype == "f64" or args.config == 5) else torch.float32
+    g = torch.Generator(device=dev).manual_seed(1000 + args.config * 10 + rank)
+    if args.config == 4:
+        n, m, d, t, sigma, kind = (args.rows if args.rows != N_PER_GPU else 12_500_000), 100_000, 9, 1, 1.0, "gaussian"
+        X = torch.rand(n, d, generator=g, device=dev, dtype=dtype)
+        w = None
+        kernel = GaussianKernel(sigma)
+        what = f"config4: fdmmv Gaussian sigma=1 {args.dtype}, N={n} per GPU x d=9 U[0,1), M=100000, T=1, w=0"
+    else:
+        n, m, d, t, sigma, kind = (args.rows if args.rows != N_PER_GPU else 2_000_000), 30_000, 128, 32, 10.0, "matern25"
+        X = torch.randn(n, d, generator=g, device=dev, dtype=dtype)
+        w = torch.randn(n, t, generator=g, device=dev, dtype=dtype)
+        kernel = MaternKernel(sigma, nu=2.5)
+        what = f"config5: fdmmv Matern 2.5 sigma=10 f64, N={n} x d=128 N(0,1), M=30000, T=32, w~N(0,1)"
+    g0 = torch.Generator(device=dev).manual_seed(2000 + args.config)
+    C = X[torch.randperm(n, generator=g0, device=dev)[:m]].contiguous()
+    v = torch.randn(m, t, generator=g0, device=dev, dtype=dtype)
+    if world > 1:
+        dist.broadcast(C, 0)
+        dist.broadcast(v, 0)
+    ops = ShardedKernelOps(kernel)
+    out = torch.empty(m, t, dtype=dtype, device=dev)
+    for _ in range(max(args.warmup, 1)):
+        ops.dmmv(X, C, v, w, out=out)
+    torch.cuda.synchronize()
+    _lib.set_timing(True)
+    sampler = ClockSampler(dev) if rank == 0 else None
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        ops.dmmv(X, C, v, w, out=out)
+    e1.record()
+    torch.cuda.synchronize()
+    sweeps = _lib.sweep_ms()
+    clocks = sampler.stop() if rank == 0 else None
+    tmax = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+    ms = float(tmax.item()) / args.steps
+    # spot-check on the first rows of this rank's shard against an explicit fp64 evaluation
+    ns = min(n, 8192 if args.config == 5 else 16384)
+    got = kernel.dmmv(X[:ns], C, v, None if w is None else w[:ns])
+    want = _dense_fdmmv_fp64(X[:ns], C, v, None if w is None else w[:ns], kind, sigma)
+    err = float((got.double() - want).norm() / want.norm())
+    if rank == 0:
+        sm_mhz = (clocks or {}).get("sm_mhz") or 1965.0
+        line = {"metric": METRIC, "value": float(n) * world * m * t / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
+                "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": ms, "scaling": "weak",
+                "dtype": "f64" if dtype == torch.float64 else "f32", "data": "synthetic",
+                "config": {"workload": what, "rows_per_gpu": n, "centres": m, "d": d, "T": t,
+                           "tensor_core_path": bool(_lib.load().flk_uses_tensor_cores(0 if dtype == torch.float32 else 1, 0, d, t, 0))},
+                "launch_ms": {"sweep1_Kv": sweeps[0], "sweep2_KTu": sweeps[1]},
+                "kernel_evals_per_s_per_gpu": 2.0 * n * m / (ms * 1e-3),
+                "spot_check_rel_l2_vs_fp64": err, "spot_check_rows": ns, "clocks": clocks,
+                "tc_status": _lib.tc_status(dev), "range_flag": _lib.range_flag(dev)}
+        if dtype == torch.float64:
+            dfma_per_pair = d + (t if t > 4 else 4 + t) + 4
+            peak = 148 * 64 * sm_mhz * 1e6
+            line["fp64"] = {"dfma_per_kernel_eval_excluding_transcendentals": dfma_per_pair,
+                            "achieved_tdfma_per_s": 2.0 * n * m * dfma_per_pair / (ms * 1e-3) / 1e12,
+                            "nominal_peak_tdfma_per_s": peak / 1e12,
+                            "frac": 2.0 * n * m * dfma_per_pair / (ms * 1e-3) / peak,
+                            "note": "nominal 64 fp64 FMA lanes per SM x sampled clock; exp / sqrt (software, fp64) not counted"}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -252,12 +366,19 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--fit", action="store_true", help="run benchmark configuration 3 (full Falkon.fit) instead")
     ap.add_argument("--centres", type=int, default=50_000, help="number of Nystrom centres for --fit")
+    ap.add_argument("--config", type=int, default=2, choices=[2, 4, 5],
+                    help="2 = the benchmark line (default); 4 / 5 = the other fdmmv configurations as data points")
+    ap.add_argument("--dtype", default="f32", choices=["f32", "f64"], help="--config 4 only")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
     if args.impl == "reference":
         return run_reference(args)
     if args.fit:
         return run_fit(args)
+    if args.config != 2:
+        if args.steps == 40:
+            args.steps = 3
+        return run_config(args)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))

@@ -92,7 +92,15 @@ struct SweepPlan {
   int tt, tp, t_chunks;
   int br, bc;         // CTA tile (rows x columns)
   int row_tiles, n_col_tiles, tiles_per_chunk, n_chunks;
-  int64_t raw_elems() const { return (int64_t)n_chunks * r_pad * tp; }
+  // Two-segment grids (tensor-core kernel): the first `main_tiles` row tiles use (n_chunks, tiles_per_chunk),
+  // the remaining ones -- the rows that would otherwise form a last, partly filled wave of CTAs -- are cut into
+  // (n_chunks_tail, tiles_per_chunk_tail) shorter pieces.  Uniform plans have main_tiles == row_tiles.
+  int main_tiles, n_chunks_tail, tiles_per_chunk_tail;
+  int max_chunks() const { return n_chunks > n_chunks_tail ? n_chunks : n_chunks_tail; }
+  int64_t grid_x() const {
+    return (int64_t)main_tiles * n_chunks + (int64_t)(row_tiles - main_tiles) * n_chunks_tail;
+  }
+  int64_t raw_elems() const { return (int64_t)max_chunks() * r_pad * tp; }
 };
 
 // Vector columns per pass: 1, 2 or 4 for the kernels that keep the whole contraction in registers;
@@ -125,31 +133,70 @@ static SweepPlan plan_sweep(bool tc, int dtype, int64_t r, int64_t s, int64_t t,
   }
   p.row_tiles = (int)ceil_div(std::max<int64_t>(r, 1), p.br);
   p.n_col_tiles = (int)ceil_div(std::max<int64_t>(s, 1), p.bc);
-  // Split the reduction side into chunks so that the grid fills whole waves of the 148 SMs:
-  // among the chunk counts that give at least two waves (when the problem allows), take the one
-  // with the best wave efficiency, preferring fewer chunks (less partial-result traffic).
   const int64_t resident = tc ? 1 : ((dtype == FLK_F32 && p.tt == 1) ? 2 : 1);  // CTAs per SM
   const int64_t slots = kNumSMs * resident;
-  const int64_t ctas_rows = (int64_t)p.row_tiles * p.t_chunks;
-  const int64_t min_tiles = tc ? 8 : 4;  // keep the row tile's staging cost amortised
-  const int64_t max_chunks = std::max<int64_t>(1, std::min<int64_t>(p.n_col_tiles / min_tiles, 4096));
-  int64_t best_chunks = 1;
-  double best_score = -1.0;
-  for (int64_t want = 1; want <= max_chunks; ++want) {
-    const int64_t tpc = ceil_div(p.n_col_tiles, want);
-    const int64_t chunks = ceil_div(p.n_col_tiles, tpc);
-    const int64_t ctas = ctas_rows * chunks;
-    const int64_t waves = ceil_div(ctas, slots);
-    double eff = (double)ctas / (double)(waves * slots);
-    if (ctas < 2 * slots) eff *= 0.5 * (double)ctas / (double)(2 * slots);  // too few CTAs to balance
-    if (eff > best_score + 0.01) {
-      best_score = eff;
-      best_chunks = chunks;
+  if (!tc) {
+    // SIMT kernels (small CTAs): split the reduction side into chunks so that the grid fills whole waves
+    // of the SMs: among the chunk counts that give at least two waves (when the problem allows), take
+    // the one with the best wave efficiency, preferring fewer chunks (less partial-result traffic).
+    const int64_t ctas_rows = (int64_t)p.row_tiles * p.t_chunks;
+    const int64_t min_tiles = 4;  // keep the row tile's staging cost amortised
+    const int64_t max_chunks = std::max<int64_t>(1, std::min<int64_t>(p.n_col_tiles / min_tiles, 4096));
+    int64_t best_chunks = 1;
+    double best_score = -1.0;
+    for (int64_t want = 1; want <= max_chunks; ++want) {
+      const int64_t tpc = ceil_div(p.n_col_tiles, want);
+      const int64_t chunks = ceil_div(p.n_col_tiles, tpc);
+      const int64_t ctas = ctas_rows * chunks;
+      const int64_t waves = ceil_div(ctas, slots);
+      double eff = (double)ctas / (double)(waves * slots);
+      if (ctas < 2 * slots) eff *= 0.5 * (double)ctas / (double)(2 * slots);  // too few CTAs to balance
+      if (eff > best_score + 0.01) {
+        best_score = eff;
+        best_chunks = chunks;
+      }
+      if (ctas >= 8 * slots) break;
     }
-    if (ctas >= 8 * slots) break;
+    p.tiles_per_chunk = (int)ceil_div(p.n_col_tiles, best_chunks);
+    p.n_chunks = (int)ceil_div(p.n_col_tiles, p.tiles_per_chunk);
+    p.main_tiles = p.row_tiles;
+    p.n_chunks_tail = p.n_chunks;
+    p.tiles_per_chunk_tail = p.tiles_per_chunk;
+    return p;
   }
-  p.tiles_per_chunk = (int)ceil_div(p.n_col_tiles, best_chunks);
-  p.n_chunks = (int)ceil_div(p.n_col_tiles, p.tiles_per_chunk);
+  // Tensor-core kernel: one 512-row CTA per SM at a time, each costing (column tiles + a fixed start-up of
+  // about four tiles: operand load, TMEM allocation, drain).  CTAs of equal length run in waves of 148, so
+  // the time of a plan is waves x length; a plan may cut the rows of the last, partly filled wave into
+  // shorter pieces (second segment).  All candidates are scored with that model; ties go to fewer chunks.
+  const double start_up = 4.0;
+  const int64_t R = p.row_tiles, Ct = p.n_col_tiles, Y = p.t_chunks;
+  const int64_t c_cap = std::max<int64_t>(1, std::min<int64_t>(Ct, 512));
+  double best = 1e300;
+  auto consider = [&](int64_t main_tiles, int64_t cm, int64_t ct) {
+    const int64_t tpc_m = ceil_div(Ct, cm), tpc_t = ceil_div(Ct, ct);
+    const int64_t ch_m = ceil_div(Ct, tpc_m), ch_t = ceil_div(Ct, tpc_t);
+    const int64_t ctas_m = main_tiles * ch_m * Y, ctas_t = (R - main_tiles) * ch_t * Y;
+    double cost = (double)ceil_div(ctas_m, slots) * ((double)tpc_m + start_up);
+    if (ctas_t > 0) cost += (double)ceil_div(ctas_t, slots) * ((double)tpc_t + start_up);
+    cost += 1e-3 * (double)std::max(ch_m, ch_t);
+    if (cost < best) {
+      best = cost;
+      p.main_tiles = (int)main_tiles;
+      p.n_chunks = (int)ch_m;
+      p.tiles_per_chunk = (int)tpc_m;
+      p.n_chunks_tail = (int)(ctas_t > 0 ? ch_t : ch_m);
+      p.tiles_per_chunk_tail = (int)(ctas_t > 0 ? tpc_t : tpc_m);
+    }
+  };
+  for (int64_t c = 1; c <= c_cap; ++c) consider(R, c, c);
+  if (Y == 1) {
+    for (int64_t cm : {1, 2, 4}) {  // divisors of 148, so that the first segment ends on a wave boundary
+      if (cm > c_cap || ceil_div(Ct, ceil_div(Ct, cm)) != cm) continue;
+      const int64_t main_tiles = (R * cm / slots) * (slots / cm);
+      if (main_tiles <= 0 || main_tiles >= R) continue;
+      for (int64_t ct = cm + 1; ct <= std::min<int64_t>(c_cap, 64); ++ct) consider(main_tiles, cm, ct);
+    }
+  }
   return p;
 }
 
@@ -322,7 +369,8 @@ static int run_finalize(const SweepPlan& sp, const void* raw, const Mat* add, vo
   finalize_kernel<T><<<grid_for(sp.r_pad * sp.tp), 256, 0, stream>>>(
       reinterpret_cast<const T*>(raw), sp.n_chunks, sp.r_pad, sp.tp, sp.r, (int)t,
       add ? reinterpret_cast<const T*>(add->ptr) : nullptr, add ? add->rs : 0, add ? add->cs : 0,
-      reinterpret_cast<T*>(out), out_rs, out_cs, padded ? 1 : 0, sp.tt, gate);
+      reinterpret_cast<T*>(out), out_rs, out_cs, padded ? 1 : 0, sp.tt, (int64_t)sp.main_tiles * sp.br,
+      sp.n_chunks_tail, gate);
   count_launch();
   FLK_CUDA_TRY(cudaGetLastError());
   return FLK_OK;
@@ -371,8 +419,11 @@ static int run_sweep_tc(int kernel, const SweepPlan& sp, const void* img_a, cons
   args.row_tiles = sp.row_tiles;
   args.n_col_tiles = sp.n_col_tiles;
   args.tiles_per_chunk = sp.tiles_per_chunk;
+  args.main_tiles = sp.main_tiles;
+  args.main_ctas = sp.main_tiles * sp.n_chunks;
+  args.tiles_per_chunk_tail = sp.tiles_per_chunk_tail;
   FLK_TRY(timer_mark(2 * sweep_idx, stream));
-  FLK_TRY(tc::launch_sweep(kernel, (int)d, args, sp.tt, sp.n_chunks, sp.t_chunks, stream));
+  FLK_TRY(tc::launch_sweep(kernel, (int)d, args, sp.tt, (int)sp.grid_x(), sp.t_chunks, stream));
   FLK_TRY(timer_mark(2 * sweep_idx + 1, stream));
   count_launch();
   return FLK_OK;

@@ -147,7 +147,8 @@ __global__ void __launch_bounds__(256) prep_vec_kernel(const T* __restrict__ v, 
 
 // ---------------------------------------------------------------------------------------------
 // finalize: sums the per-chunk partial results raw[n_chunks][r_pad][tp] (fixed order, so the
-// result is deterministic), optionally adds add[r x t] (the "+ w" of fmmv.py:759), and writes
+// result is deterministic; rows from `main_rows` on have `n_chunks_tail` partials instead, see the
+// two-segment grids of the tensor-core kernel), optionally adds add[r x t] (the "+ w" of fmmv.py:759), and writes
 //   mode 0: out[r x t] with the caller's strides,
 //   mode 1: a padded buffer in the column-chunked layout out[t_chunks][r_pad][tt] whose rows >= r
 //           and columns >= t are zero (it becomes the vector operand of the second sweep of fdmmv).
@@ -158,7 +159,7 @@ __global__ void __launch_bounds__(256) finalize_kernel(const T* __restrict__ raw
                                                        const T* __restrict__ add, int64_t add_rs,
                                                        int64_t add_cs, T* __restrict__ out,
                                                        int64_t out_rs, int64_t out_cs, int padded_out,
-                                                       int tt, Gate gate) {
+                                                       int tt, int64_t main_rows, int n_chunks_tail, Gate gate) {
   if (!gate_open(gate)) return;
   int64_t total = r_pad * tp;
   for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
@@ -168,7 +169,8 @@ __global__ void __launch_bounds__(256) finalize_kernel(const T* __restrict__ raw
     bool live = (i < r && c < t);
     T acc = 0;
     if (live) {
-      for (int ch = 0; ch < n_chunks; ++ch) acc += raw[(int64_t)ch * total + idx];
+      const int nch = i < main_rows ? n_chunks : n_chunks_tail;
+      for (int ch = 0; ch < nch; ++ch) acc += raw[(int64_t)ch * total + idx];
       if (add != nullptr) acc += add[i * add_rs + (int64_t)c * add_cs];
     }
     if (padded_out) {

@@ -459,6 +459,11 @@ struct SweepArgs {
   int row_tiles;        // ceil(r / 512)
   int n_col_tiles;      // ceil(s / 128)
   int tiles_per_chunk;
+  // two-segment grid: CTAs [0, main_ctas) cover row tiles [0, main_tiles) with `tiles_per_chunk` column
+  // tiles each; the remaining CTAs cover the remaining row tiles with `tiles_per_chunk_tail` each
+  int main_tiles;
+  int main_ctas;
+  int tiles_per_chunk_tail;
   int ksteps;           // MMA K-steps (16 fp16 each) actually carrying data
 };
 
@@ -555,11 +560,20 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
-  const int row_tile = blockIdx.x % p.row_tiles;
-  const int chunk = blockIdx.x / p.row_tiles;
+  int row_tile, chunk, tiles_per_chunk;
+  if ((int)blockIdx.x < p.main_ctas) {
+    row_tile = blockIdx.x % p.main_tiles;
+    chunk = blockIdx.x / p.main_tiles;
+    tiles_per_chunk = p.tiles_per_chunk;
+  } else {
+    const int b = blockIdx.x - p.main_ctas, tail_tiles = p.row_tiles - p.main_tiles;
+    row_tile = p.main_tiles + b % tail_tiles;
+    chunk = b / tail_tiles;
+    tiles_per_chunk = p.tiles_per_chunk_tail;
+  }
   const int tchunk = blockIdx.y;
-  const int tile_begin = chunk * p.tiles_per_chunk;
-  const int tile_end = min(tile_begin + p.tiles_per_chunk, p.n_col_tiles);
+  const int tile_begin = chunk * tiles_per_chunk;
+  const int tile_end = min(tile_begin + tiles_per_chunk, p.n_col_tiles);
   const int ntiles = tile_end - tile_begin;
 
   // Do not start when a CTA of this launch already gave up (keeps a failed launch short) or when
@@ -759,7 +773,7 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
 }
 
 template <int KT, int NSLAB, int TT>
-int launch_sweep_inst(const SweepArgs& args, int n_chunks, int t_chunks, cudaStream_t stream) {
+int launch_sweep_inst(const SweepArgs& args, int grid_x, int t_chunks, cudaStream_t stream) {
   constexpr size_t smem = tc_smem_bytes<NSLAB, TT>();
   static_assert(smem > 116 * 1024, "one CTA per SM is assumed (each CTA takes all 512 TMEM columns)");
   static_assert(smem <= 227 * 1024, "shared memory budget exceeded");
@@ -771,40 +785,40 @@ int launch_sweep_inst(const SweepArgs& args, int n_chunks, int t_chunks, cudaStr
                                       (int)smem));
     if (dev < 16) configured[dev] = true;
   }
-  dim3 grid((unsigned)(args.row_tiles * n_chunks), (unsigned)t_chunks, 1);
+  dim3 grid((unsigned)grid_x, (unsigned)t_chunks, 1);
   kmv_tc_kernel<KT, NSLAB, TT><<<grid, kThreads, smem, stream>>>(args);
   FLK_CUDA_TRY(cudaGetLastError());
   return FLK_OK;
 }
 
 template <int KT, int NSLAB>
-int launch_sweep_tt(const SweepArgs& args, int tt, int n_chunks, int t_chunks, cudaStream_t stream) {
+int launch_sweep_tt(const SweepArgs& args, int tt, int grid_x, int t_chunks, cudaStream_t stream) {
   switch (tt) {
-    case 1: return launch_sweep_inst<KT, NSLAB, 1>(args, n_chunks, t_chunks, stream);
-    case 2: return launch_sweep_inst<KT, NSLAB, 2>(args, n_chunks, t_chunks, stream);
-    case 4: return launch_sweep_inst<KT, NSLAB, 4>(args, n_chunks, t_chunks, stream);
+    case 1: return launch_sweep_inst<KT, NSLAB, 1>(args, grid_x, t_chunks, stream);
+    case 2: return launch_sweep_inst<KT, NSLAB, 2>(args, grid_x, t_chunks, stream);
+    case 4: return launch_sweep_inst<KT, NSLAB, 4>(args, grid_x, t_chunks, stream);
   }
   return fail(FLK_ERR_BAD_ARG, "internal: unsupported TT=%d", tt);
 }
 
 template <int KT>
-int launch_sweep_kt(int nslab, const SweepArgs& args, int tt, int n_chunks, int t_chunks, cudaStream_t stream) {
+int launch_sweep_kt(int nslab, const SweepArgs& args, int tt, int grid_x, int t_chunks, cudaStream_t stream) {
   switch (nslab) {
-    case 1: return launch_sweep_tt<KT, 1>(args, tt, n_chunks, t_chunks, stream);
-    case 2: return launch_sweep_tt<KT, 2>(args, tt, n_chunks, t_chunks, stream);
-    case 3: return launch_sweep_tt<KT, 3>(args, tt, n_chunks, t_chunks, stream);
+    case 1: return launch_sweep_tt<KT, 1>(args, tt, grid_x, t_chunks, stream);
+    case 2: return launch_sweep_tt<KT, 2>(args, tt, grid_x, t_chunks, stream);
+    case 3: return launch_sweep_tt<KT, 3>(args, tt, grid_x, t_chunks, stream);
   }
   return fail(FLK_ERR_BAD_ARG, "internal: unsupported slab count %d", nslab);
 }
 
-inline int launch_sweep(int kernel, int d, SweepArgs args, int tt, int n_chunks, int t_chunks, cudaStream_t stream) {
+inline int launch_sweep(int kernel, int d, SweepArgs args, int tt, int grid_x, int t_chunks, cudaStream_t stream) {
   args.ksteps = k_steps(d);
   const int nslab = n_slabs(d);
   switch (kernel) {
-    case FLK_GAUSSIAN: return launch_sweep_kt<FLK_GAUSSIAN>(nslab, args, tt, n_chunks, t_chunks, stream);
-    case FLK_LAPLACIAN: return launch_sweep_kt<FLK_LAPLACIAN>(nslab, args, tt, n_chunks, t_chunks, stream);
-    case FLK_MATERN15: return launch_sweep_kt<FLK_MATERN15>(nslab, args, tt, n_chunks, t_chunks, stream);
-    case FLK_MATERN25: return launch_sweep_kt<FLK_MATERN25>(nslab, args, tt, n_chunks, t_chunks, stream);
+    case FLK_GAUSSIAN: return launch_sweep_kt<FLK_GAUSSIAN>(nslab, args, tt, grid_x, t_chunks, stream);
+    case FLK_LAPLACIAN: return launch_sweep_kt<FLK_LAPLACIAN>(nslab, args, tt, grid_x, t_chunks, stream);
+    case FLK_MATERN15: return launch_sweep_kt<FLK_MATERN15>(nslab, args, tt, grid_x, t_chunks, stream);
+    case FLK_MATERN25: return launch_sweep_kt<FLK_MATERN25>(nslab, args, tt, grid_x, t_chunks, stream);
   }
   return fail(FLK_ERR_BAD_ARG, "unknown kernel id %d", kernel);
 }
