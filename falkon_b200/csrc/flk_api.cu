@@ -4,6 +4,7 @@
 #include <vector>
 
 #include "flk_common.cuh"
+#include "flk_dmma.cuh"
 #include "flk_fmm.cuh"
 #include "flk_prep.cuh"
 #include "flk_simt.cuh"
@@ -396,9 +397,14 @@ static int run_sweep_simt(int kernel, const SweepPlan& sp, const Operand& a, con
   args.gate = gate;
   const bool timed = gate.flag == nullptr;  // the gated alternative is not the timed kernel
   if (timed) FLK_TRY(timer_mark(2 * sweep_idx, stream));
-  if (sp.tt == kWideT)
-    FLK_TRY((launch_wide_any<T>(kernel, args, sp.n_chunks, sp.t_chunks, stream)));
-  else
+  if (sp.tt == kWideT) {
+    if constexpr (sizeof(T) == 8) {
+      // fp64, many vector columns: both products on the fp64 tensor-core instruction (flk_dmma.cuh)
+      FLK_TRY(dmma::launch(kernel, args, sp.n_chunks, sp.t_chunks, stream));
+    } else {
+      FLK_TRY((launch_wide_any<T>(kernel, args, sp.n_chunks, sp.t_chunks, stream)));
+    }
+  } else
     FLK_TRY((launch_simt_any<T>(kernel, args, sp.tt, sp.n_chunks, sp.t_chunks, stream)));
   if (timed) FLK_TRY(timer_mark(2 * sweep_idx + 1, stream));
   count_launch();

@@ -1,0 +1,223 @@
+// fp64 tensor-core (DMMA) kernel-vector product for many vector columns:
+//   raw[chunk][i][t] = sum_{j in chunk} k(a_i, b_j) vec[j][t],  32 vector columns per pass.
+//
+// Same data flow as kmv_wide_kernel (flk_wide.cuh) -- a CTA forms a 128 x 64 block of kernel values from
+// cp.async-staged 16-feature operand chunks, parks it in shared memory and multiplies it with the 64 x 32
+// tile of `vec` -- but both products run on the fp64 tensor-core instruction
+// mma.sync.m8n8k4.f64 (tcgen05 has no fp64 kind): eight multiply-adds per lane and instruction instead of
+// one, which removes the issue and operand-fetch pressure that keeps the DFMA version at 42 % of the pipe.
+// On B200 DMMA and DFMA have the same peak (37 TFLOP/s measured for both), so the gain is efficiency, not
+// a higher ceiling.
+//
+// Fragment layouts of m8n8k4 (lane = 4 g + q): A[8 x 4] row-major: lane holds A[g][q]; B[4 x 8] "col":
+// lane holds B[q][g]; C[8 x 8]: lane holds C[g][2 q], C[g][2 q + 1].  Shared-memory pitches (20, 68 and 36
+// doubles) are chosen so that each half-warp's fragment load touches 16 different banks pairs.
+// Arithmetic order per kernel value is the reference's: (|a|^2 - 2 a.b) + |b|^2, clamp at 1e-20, kernel function.
+#pragma once
+
+#include "flk_common.cuh"
+#include "flk_simt.cuh"
+
+namespace flk {
+namespace dmma {
+
+constexpr int BR = 128, BC = 64, DK = 16, LD = 20, TW = 32, KLD = 68, VLD = 36;
+
+constexpr size_t smem_bytes() {
+  return sizeof(double) * (size_t)(2 * BR * LD + 2 * BC * LD + 2 * BC * VLD + 2 * BC + BR * KLD);
+}
+
+__device__ __forceinline__ void mma884(double (&c)[2], double a, double b) {
+  asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};"
+               : "+d"(c[0]), "+d"(c[1])
+               : "d"(a), "d"(b));
+}
+
+template <int KT>
+__global__ void __launch_bounds__(256, 1) kmv_dmma_kernel(SimtArgs<double> p) {
+  if (!gate_open(p.gate)) return;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  double* As = reinterpret_cast<double*>(smem_raw);  // [2][BR][LD]
+  double* Bs = As + 2 * BR * LD;                      // [2][BC][LD]
+  double* Vs = Bs + 2 * BC * LD;                      // [2][BC][VLD]
+  double* bns = Vs + 2 * BC * VLD;                    // [2][BC]
+  double* Ks = bns + 2 * BC;                          // [BR][KLD] kernel values of the current tile, row-major
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, q = lane & 3;
+  const int wr = warp & 3, wc = warp >> 2;  // first product: warp tile = rows wr*32.., columns wc*32..
+  const int row_tile = blockIdx.x % p.row_tiles;
+  const int chunk = blockIdx.x / p.row_tiles;
+  const int tile_begin = chunk * p.tiles_per_chunk;
+  const int tile_end = min(tile_begin + p.tiles_per_chunk, p.n_col_tiles);
+  const int ntiles = tile_end - tile_begin;
+  const int ld = p.ld;
+  const int nk = (ld + DK - 1) / DK;
+  const int steps = ntiles * nk;
+  const double* Ag = p.A + (int64_t)row_tile * BR * ld;
+
+  double an[4];
+#pragma unroll
+  for (int mt = 0; mt < 4; ++mt) an[mt] = p.an[(int64_t)row_tile * BR + wr * 32 + mt * 8 + g];
+
+  double acc[4][4][2];
+  double oacc[2][4][2];  // second product: rows warp*16 + mt*8 + g, vector columns nt*8 + 2q + {0,1}
+#pragma unroll
+  for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) acc[mt][nt][0] = acc[mt][nt][1] = 0.0;
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) oacc[mt][nt][0] = oacc[mt][nt][1] = 0.0;
+
+  auto issue = [&](int s) {
+    const int tl = s / nk, kc = s - tl * nk;
+    const int buf = s & 1;
+    const int k0 = kc * DK;
+    const int kw = min(DK, ld - k0);   // even (ld is a multiple of 2)
+    const int kw4 = (kw + 3) & ~3;     // the MMA consumes features in groups of four
+    const int pieces = kw / 2;         // 16-byte pieces per row
+    if (nk > 1 || s == 0) {
+      double* dst = As + (nk > 1 ? buf : 0) * BR * LD;
+      for (int x = tid; x < BR * pieces; x += 256) {
+        int r = x / pieces, pc = x - r * pieces;
+        cp_async16(dst + r * LD + pc * 2, Ag + (int64_t)r * ld + k0 + pc * 2);
+      }
+      if (kw4 != kw)  // zero the features the last group of four reads beyond kw
+        for (int r = tid; r < BR; r += 256) dst[r * LD + kw] = dst[r * LD + kw + 1] = 0.0;
+    }
+    const int64_t col0 = (int64_t)(tile_begin + tl) * BC;
+    double* dstb = Bs + buf * BC * LD;
+    const double* Bg = p.B + col0 * ld + k0;
+    for (int x = tid; x < BC * pieces; x += 256) {
+      int r = x / pieces, pc = x - r * pieces;
+      cp_async16(dstb + r * LD + pc * 2, Bg + (int64_t)r * ld + pc * 2);
+    }
+    if (kw4 != kw)
+      for (int r = tid; r < BC; r += 256) dstb[r * LD + kw] = dstb[r * LD + kw + 1] = 0.0;
+    if (kc == 0) {
+      const int vb = tl & 1;
+      const double* vg = p.vec + ((int64_t)blockIdx.y * p.s_pad + col0) * TW;  // BC rows of TW values, contiguous
+      double* vd = Vs + vb * BC * VLD;
+      for (int x = tid; x < BC * (TW / 2); x += 256) {
+        int r = x / (TW / 2), pc = x - r * (TW / 2);
+        cp_async16(vd + r * VLD + pc * 2, vg + r * TW + pc * 2);
+      }
+      if (tid < BC) cp_async_small<8>(bns + vb * BC + tid, p.bn + col0 + tid);
+    }
+  };
+
+  issue(0);
+  cp_async_commit();
+
+  int tl = 0, kc = 0;
+  for (int s = 0; s < steps; ++s) {
+    if (s + 1 < steps) issue(s + 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+
+    const double* a_s = As + (nk > 1 ? (s & 1) : 0) * BR * LD + (wr * 32 + g) * LD + q;
+    const double* b_s = Bs + (s & 1) * BC * LD + (wc * 32 + g) * LD + q;
+    const int kw4 = (min(DK, ld - kc * DK) + 3) & ~3;
+    for (int k = 0; k < kw4; k += 4) {
+      double a[4], b[4];
+#pragma unroll
+      for (int mt = 0; mt < 4; ++mt) a[mt] = a_s[mt * 8 * LD + k];
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) b[nt] = b_s[nt * 8 * LD + k];
+#pragma unroll
+      for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) mma884(acc[mt][nt], a[mt], b[nt]);
+    }
+
+    if (kc == nk - 1) {
+      // 1. kernel values of this tile -> shared memory
+      const double* bn_s = bns + (tl & 1) * BC;
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+        const int c = wc * 32 + nt * 8 + 2 * q;
+        const double bn0 = bn_s[c], bn1 = bn_s[c + 1];
+#pragma unroll
+        for (int mt = 0; mt < 4; ++mt) {
+          double d0 = (an[mt] - 2.0 * acc[mt][nt][0]) + bn0;
+          double d1 = (an[mt] - 2.0 * acc[mt][nt][1]) + bn1;
+          d0 = d0 < 1e-20 ? 1e-20 : d0;
+          d1 = d1 < 1e-20 ? 1e-20 : d1;
+          double2 kv;
+          kv.x = kernel_eval<KT>(d0);
+          kv.y = kernel_eval<KT>(d1);
+          *reinterpret_cast<double2*>(Ks + (wr * 32 + mt * 8 + g) * KLD + c) = kv;
+          acc[mt][nt][0] = acc[mt][nt][1] = 0.0;
+        }
+      }
+      __syncthreads();
+      // 2. out[rows warp*16.., 32 columns] += K[rows, 0..63] vec[0..63, :]
+      const double* k_s = Ks + (warp * 16 + g) * KLD + q;
+      const double* v_s = Vs + (tl & 1) * BC * VLD + q * VLD + g;
+#pragma unroll 4
+      for (int k = 0; k < BC; k += 4) {
+        const double a0 = k_s[k], a1 = k_s[8 * KLD + k];
+        double b[4];
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) b[nt] = v_s[k * VLD + nt * 8];
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+          mma884(oacc[0][nt], a0, b[nt]);
+          mma884(oacc[1][nt], a1, b[nt]);
+        }
+      }
+      kc = 0;
+      ++tl;
+    } else {
+      ++kc;
+    }
+    __syncthreads();
+  }
+
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt) {
+    const int64_t row = (int64_t)row_tile * BR + warp * 16 + mt * 8 + g;
+    double* dst = p.raw + ((int64_t)chunk * p.r_pad + row) * p.tp + blockIdx.y * TW + 2 * q;
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      double2 o;
+      o.x = oacc[mt][nt][0];
+      o.y = oacc[mt][nt][1];
+      *reinterpret_cast<double2*>(dst + nt * 8) = o;
+    }
+  }
+}
+
+template <int KT>
+int launch_inst(const SimtArgs<double>& args, int n_chunks, int t_chunks, cudaStream_t stream) {
+  constexpr size_t smem = smem_bytes();
+  static_assert(smem <= 227 * 1024, "shared memory budget exceeded");
+  static bool configured[16] = {false};
+  int dev = 0;
+  FLK_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev >= 16 || !configured[dev]) {
+    FLK_CUDA_TRY(cudaFuncSetAttribute(kmv_dmma_kernel<KT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    if (dev < 16) configured[dev] = true;
+  }
+  dim3 grid((unsigned)(args.row_tiles * n_chunks), (unsigned)t_chunks, 1);
+  kmv_dmma_kernel<KT><<<grid, 256, smem, stream>>>(args);
+  FLK_CUDA_TRY(cudaGetLastError());
+  return FLK_OK;
+}
+
+inline int launch(int kernel, const SimtArgs<double>& args, int n_chunks, int t_chunks, cudaStream_t stream) {
+  switch (kernel) {
+    case FLK_GAUSSIAN: return launch_inst<FLK_GAUSSIAN>(args, n_chunks, t_chunks, stream);
+    case FLK_LAPLACIAN: return launch_inst<FLK_LAPLACIAN>(args, n_chunks, t_chunks, stream);
+    case FLK_MATERN15: return launch_inst<FLK_MATERN15>(args, n_chunks, t_chunks, stream);
+    case FLK_MATERN25: return launch_inst<FLK_MATERN25>(args, n_chunks, t_chunks, stream);
+  }
+  return fail(FLK_ERR_BAD_ARG, "unknown kernel id %d", kernel);
+}
+
+}  // namespace dmma
+}  // namespace flk
