@@ -245,6 +245,40 @@ def test_rows_beyond_fp16_range_take_the_simt_path(kernel, nu):
         assert fo.rel_l2(got, fo.dense_fmmv_fp64(X, C, v, kernel, 2.0, nu)) <= 1e-4
 
 
+@pytest.mark.parametrize("order", ["C", "F"])
+def test_large_host_inputs_travel_in_row_chunks(order):
+    """From 262,144 rows up the host-buffer entry points copy X1 (and w) in row chunks through a copy stream
+    and, for fdmmv, sum the per-chunk results: the answer must equal the one-piece device call to rounding,
+    for row-major and column-major host matrices and a row count that is not a multiple of anything."""
+    from falkon_b200.kernels import GaussianKernel, MaternKernel
+
+    g = torch.Generator().manual_seed(31)
+    n, m, d, t = 300_017, 257, 11, 2
+    X = torch.randn(n, d, generator=g)
+    C = X[torch.randperm(n, generator=g)[:m]].contiguous()
+    v = torch.randn(m, t, generator=g)
+    w = torch.randn(n, t, generator=g)
+    if order == "F":
+        X = X.T.contiguous().T
+        w = w.T.contiguous().T
+    for k in (GaussianKernel(3.0), MaternKernel(3.0, nu=1.5)):
+        dev_out = k.dmmv(X.cuda(), C.cuda(), v.cuda(), w.cuda()).cpu()
+        host_out = k.dmmv(X, C, v, w)
+        assert host_out.device.type == "cpu"
+        assert float((host_out - dev_out).norm() / dev_out.norm()) <= 2e-6
+        host_out2 = k.dmmv(X, C, None, w)  # w only: K^T w
+        dev_out2 = k.dmmv(X.cuda(), C.cuda(), None, w.cuda()).cpu()
+        assert float((host_out2 - dev_out2).norm() / dev_out2.norm()) <= 2e-6
+        dev_u = k.mmv(X.cuda(), C.cuda(), v.cuda()).cpu()
+        host_u = k.mmv(X, C, v)
+        assert torch.equal(host_u, dev_u)  # K v has no cross-chunk sum: bit-identical
+    # fp64 through the SIMT kernel
+    k = GaussianKernel(3.0)
+    a = k.dmmv(X.double(), C.double(), v.double(), w.double())
+    b = k.dmmv(X.double().cuda(), C.double().cuda(), v.double().cuda(), w.double().cuda()).cpu()
+    assert float((a - b).norm() / b.norm()) <= 1e-13
+
+
 def test_errors_surface_as_python_exceptions():
     from falkon_b200.kernels import GaussianKernel
 
