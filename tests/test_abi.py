@@ -83,6 +83,23 @@ def test_argument_errors_return_status_codes(lib):
     assert st == _lib.FLK_ERR_UNSUPPORTED
 
 
+def test_kernel_matrix_entry_point_checks_arguments(lib):
+    sig = (ctypes.c_double * 1)(1.0)
+    dummy = ctypes.c_void_p(4096)
+    need = lib.flk_fmm_workspace_bytes(0, 1000, 500, 10, 0)
+    need64 = lib.flk_fmm_workspace_bytes(0, 1000, 500, 10, _lib.FLAG_FP64_MATH)
+    assert 0 < need < need64  # fp64 arithmetic on fp32 data needs fp64 operand copies
+    assert lib.flk_fmm_workspace_bytes(1, 1000, 500, 10, 0) == need64
+    st = lib.flk_fmm(0, 0, None, 10, 4, 1, dummy, 5, 4, 1, 4, dummy, 5, 1, sig, 1, dummy, 1 << 30, 0, None)
+    assert st == _lib.FLK_ERR_BAD_ARG and b"X1" in lib.flk_last_error()
+    st = lib.flk_fmm(0, 0, dummy, 10, 4, 1, dummy, 5, 4, 1, 4, dummy, 7, 3, sig, 1, dummy, 1 << 30, 0, None)
+    assert st == _lib.FLK_ERR_LAYOUT  # out: neither stride is 1
+    st = lib.flk_fmm(0, 0, dummy, 10, 4, 1, dummy, 5, 4, 1, 4, dummy, 5, 1, sig, 1, dummy, 16, 0, None)
+    assert st == _lib.FLK_ERR_WORKSPACE
+    st = lib.flk_fmm(0, 5, dummy, 10, 4, 1, dummy, 5, 4, 1, 4, dummy, 5, 1, sig, 1, dummy, 1 << 30, 0, None)
+    assert st == _lib.FLK_ERR_BAD_ARG  # unknown kernel id
+
+
 def test_status_maps_to_reference_exception_types(lib):
     lib.flk_fmmv_workspace_bytes(0, 0, -1, 10, 2, 1, 0)
     with pytest.raises(ValueError):
