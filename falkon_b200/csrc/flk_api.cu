@@ -9,6 +9,7 @@
 #include "flk_prep.cuh"
 #include "flk_simt.cuh"
 #include "flk_tc.cuh"
+#include "flk_tck.cuh"
 #include "flk_wide.cuh"
 
 namespace flk {
@@ -88,6 +89,7 @@ static int check_mat(const char* name, const Mat& m, bool nullable) {
 // ---------------------------------------------------------------------------------------------
 struct SweepPlan {
   bool tc;            // tensor-core kernel?
+  bool kloop;         // ... its K-loop variant for many features (flk_tck.cuh: 256-row CTAs, operands streamed)
   int64_t r, s;       // live rows on the output / reduction side
   int64_t r_pad, s_pad;
   int tt, tp, t_chunks;
@@ -116,9 +118,11 @@ static void choose_tt(int64_t t, bool allow_wide, int* tt, int* tp) {
 
 // `allow_wide`: the plan may use the wide kernel (never for the tensor-core kernel, and never for its SIMT
 // alternative, which shares the vector buffers of the tensor-core plan and therefore its column grouping).
-static SweepPlan plan_sweep(bool tc, int dtype, int64_t r, int64_t s, int64_t t, bool allow_wide = false) {
+static SweepPlan plan_sweep(bool tc, int dtype, int64_t r, int64_t s, int64_t t, bool allow_wide = false,
+                            bool kloop = false) {
   SweepPlan p;
   p.tc = tc;
+  p.kloop = tc && kloop;
   p.r = r;
   p.s = s;
   p.r_pad = round_up(std::max<int64_t>(r, 1), kRowPad);
@@ -126,7 +130,7 @@ static SweepPlan plan_sweep(bool tc, int dtype, int64_t r, int64_t s, int64_t t,
   choose_tt(t, allow_wide && !tc, &p.tt, &p.tp);
   p.t_chunks = p.tp / p.tt;
   if (tc) {
-    p.br = tc::kRowsPerCta;
+    p.br = kloop ? tck::kRowsPerCtaL : tc::kRowsPerCta;
     p.bc = tc::kColsPerTile;
   } else {
     p.br = 128;
@@ -169,7 +173,7 @@ static SweepPlan plan_sweep(bool tc, int dtype, int64_t r, int64_t s, int64_t t,
   // about four tiles: operand load, TMEM allocation, drain).  CTAs of equal length run in waves of 148, so
   // the time of a plan is waves x length; a plan may cut the rows of the last, partly filled wave into
   // shorter pieces (second segment).  All candidates are scored with that model; ties go to fewer chunks.
-  const double start_up = 4.0;
+  const double start_up = p.kloop ? 1.0 : 4.0;  // the K-loop variant has no resident operand to load first
   const int64_t R = p.row_tiles, Ct = p.n_col_tiles, Y = p.t_chunks;
   const int64_t c_cap = std::max<int64_t>(1, std::min<int64_t>(Ct, 512));
   double best = 1e300;
@@ -190,7 +194,7 @@ static SweepPlan plan_sweep(bool tc, int dtype, int64_t r, int64_t s, int64_t t,
     }
   };
   for (int64_t c = 1; c <= c_cap; ++c) consider(R, c, c);
-  if (Y == 1) {
+  if (Y == 1 && !p.kloop) {
     for (int64_t cm : {1, 2, 4}) {  // divisors of 148, so that the first segment ends on a wave boundary
       if (cm > c_cap || ceil_div(Ct, ceil_div(Ct, cm)) != cm) continue;
       const int64_t main_tiles = (R * cm / slots) * (slots / cm);
@@ -206,7 +210,7 @@ static bool tc_eligible(int dtype, int kernel, int64_t d, int64_t t, int flags) 
   (void)t;
   if (flags & FLK_FLAG_FORCE_SIMT) return false;
   if (dtype != FLK_F32) return false;
-  return tc::supports_d(d);
+  return tc::supports_d(d) || tck::supports_d(d);
 }
 
 // Bump allocator over the caller's workspace (256-byte granules).
@@ -262,12 +266,13 @@ static Layout make_layout(void* ws, bool dmmv, bool has_v, int dtype, int kernel
   Carver c(ws);
   L.status = c.take(256);
   L.sigma = c.take(std::max<int64_t>(d, 1) * es);
-  L.s1 = plan_sweep(L.tc, dtype, n, m, t, !L.tc);  // rows = X1, reduction over X2
-  L.s2 = plan_sweep(L.tc, dtype, m, n, t, !L.tc);  // rows = X2, reduction over X1 (fdmmv only)
+  const bool kloop = L.tc && tck::supports_d(d);
+  L.s1 = plan_sweep(L.tc, dtype, n, m, t, !L.tc, kloop);  // rows = X1, reduction over X2
+  L.s2 = plan_sweep(L.tc, dtype, m, n, t, !L.tc, kloop);  // rows = X2, reduction over X1 (fdmmv only)
   const int64_t n_pad = L.s1.r_pad, m_pad = L.s1.s_pad;
   const bool first = !dmmv || has_v;  // is the first sweep executed?
   if (L.tc) {
-    const int64_t kp = tc::padded_k(d);
+    const int64_t kp = kloop ? tck::padded_k(d) : tc::padded_k(d);
     if (first) L.x1.img_a = c.take(n_pad * kp * 2);
     if (first) L.x2.img_b = c.take(m_pad * kp * 2);
     if (dmmv) {
@@ -413,23 +418,39 @@ static int run_sweep_simt(int kernel, const SweepPlan& sp, const Operand& a, con
 
 static int run_sweep_tc(int kernel, const SweepPlan& sp, const void* img_a, const void* img_b, int64_t d,
                         const void* vec, void* raw, void* status, cudaStream_t stream, int sweep_idx) {
-  tc::SweepArgs args;
-  args.img_a = reinterpret_cast<const __half*>(img_a);
-  args.img_b = reinterpret_cast<const __half*>(img_b);
-  args.vec = reinterpret_cast<const float*>(vec);
-  args.raw = reinterpret_cast<float*>(raw);
-  args.status = reinterpret_cast<int*>(status);
-  args.tp = sp.tp;
-  args.r_pad = sp.r_pad;
-  args.s_pad = sp.s_pad;
-  args.row_tiles = sp.row_tiles;
-  args.n_col_tiles = sp.n_col_tiles;
-  args.tiles_per_chunk = sp.tiles_per_chunk;
-  args.main_tiles = sp.main_tiles;
-  args.main_ctas = sp.main_tiles * sp.n_chunks;
-  args.tiles_per_chunk_tail = sp.tiles_per_chunk_tail;
   FLK_TRY(timer_mark(2 * sweep_idx, stream));
-  FLK_TRY(tc::launch_sweep(kernel, (int)d, args, sp.tt, (int)sp.grid_x(), sp.t_chunks, stream));
+  if (sp.kloop) {
+    tck::SweepArgsL args;
+    args.img_a = reinterpret_cast<const __half*>(img_a);
+    args.img_b = reinterpret_cast<const __half*>(img_b);
+    args.vec = reinterpret_cast<const float*>(vec);
+    args.raw = reinterpret_cast<float*>(raw);
+    args.status = reinterpret_cast<int*>(status);
+    args.tp = sp.tp;
+    args.r_pad = sp.r_pad;
+    args.s_pad = sp.s_pad;
+    args.row_tiles = sp.row_tiles;
+    args.n_col_tiles = sp.n_col_tiles;
+    args.tiles_per_chunk = sp.tiles_per_chunk;
+    FLK_TRY(tck::launch_sweep(kernel, (int)d, args, sp.tt, sp.n_chunks, sp.t_chunks, stream));
+  } else {
+    tc::SweepArgs args;
+    args.img_a = reinterpret_cast<const __half*>(img_a);
+    args.img_b = reinterpret_cast<const __half*>(img_b);
+    args.vec = reinterpret_cast<const float*>(vec);
+    args.raw = reinterpret_cast<float*>(raw);
+    args.status = reinterpret_cast<int*>(status);
+    args.tp = sp.tp;
+    args.r_pad = sp.r_pad;
+    args.s_pad = sp.s_pad;
+    args.row_tiles = sp.row_tiles;
+    args.n_col_tiles = sp.n_col_tiles;
+    args.tiles_per_chunk = sp.tiles_per_chunk;
+    args.main_tiles = sp.main_tiles;
+    args.main_ctas = sp.main_tiles * sp.n_chunks;
+    args.tiles_per_chunk_tail = sp.tiles_per_chunk_tail;
+    FLK_TRY(tc::launch_sweep(kernel, (int)d, args, sp.tt, (int)sp.grid_x(), sp.t_chunks, stream));
+  }
   FLK_TRY(timer_mark(2 * sweep_idx + 1, stream));
   count_launch();
   return FLK_OK;
@@ -448,10 +469,11 @@ static int prepare_operands(const Layout& L, int kernel, const Mat& X1, const Ma
                             T sig_scalar, int sigma_len, int dtype, bool reset_status, cudaStream_t stream) {
   if (L.tc) {
     if (reset_status) FLK_CUDA_TRY(cudaMemsetAsync(L.status, 0, 256, stream));
-    FLK_TRY(tc::prep_images(kernel, X1.ptr, X1.rows, X1.rs, X1.cs, (int)d, (const float*)sig_dev, (float)sig_scalar,
-                            sigma_len, L.s1.r_pad, L.x1.img_a, L.x1.img_b, reinterpret_cast<int*>(L.status), stream));
-    FLK_TRY(tc::prep_images(kernel, X2.ptr, X2.rows, X2.rs, X2.cs, (int)d, (const float*)sig_dev, (float)sig_scalar,
-                            sigma_len, L.s1.s_pad, L.x2.img_a, L.x2.img_b, reinterpret_cast<int*>(L.status), stream));
+    auto prep = L.s1.kloop ? tck::prep_images_large : tc::prep_images;
+    FLK_TRY(prep(kernel, X1.ptr, X1.rows, X1.rs, X1.cs, (int)d, (const float*)sig_dev, (float)sig_scalar, sigma_len,
+                 L.s1.r_pad, L.x1.img_a, L.x1.img_b, reinterpret_cast<int*>(L.status), stream));
+    FLK_TRY(prep(kernel, X2.ptr, X2.rows, X2.rs, X2.cs, (int)d, (const float*)sig_dev, (float)sig_scalar, sigma_len,
+                 L.s1.s_pad, L.x2.img_a, L.x2.img_b, reinterpret_cast<int*>(L.status), stream));
     count_launch(2);
   }
   const int ld = ld_for(dtype, d);

@@ -1,0 +1,444 @@
+// Tensor-core kernel-vector product for fp32 data with MANY features (30 < d <= kMaxD):
+//
+//   raw[chunk][i][t] = sum_{j in chunk} k(a_i, b_j) vec[j][t]
+//
+// Same formulation as flk_tc.cuh -- split-fp16 operand images whose MMA accumulator is the exponent of the
+// kernel function, MUFU / FMA-pipe exponential epilogue, the contraction with `vec` fused -- but the K
+// dimension of the exponent GEMM (3 d + 6 fp16 elements) no longer fits shared memory for a resident row
+// block, so this kernel is an ordinary K-loop GEMM pipeline: a CTA owns 256 output rows (two 128-row MMA
+// blocks), walks the 128-column tiles of its chunk, and for every tile streams the operand images slab by slab
+// (32 fp16 = 64 bytes of K per row: 8 KB for each of the two A blocks and for the B tile) through a ring of
+// bulk copies; each slab feeds four tcgen05.mma (2 row blocks x 2 K-steps).  The two row blocks have two TMEM
+// accumulators each (512 columns in all), so the MMAs of tile j+1 run under the epilogue of tile j.  The
+// kernel is bound by the tensor pipe / the L2 traffic of the re-streamed operands (3 x the bytes of a plain
+// GEMM of the same shape, because every feature appears three times in the split), not by MUFU.
+// Warps 0-7: epilogue (row block = warp / 4, TMEM lane quarter = warp % 4); warp 8: MMA issuer and TMEM owner;
+// warp 9: bulk-copy producer.  Every wait is bounded as in flk_tc.cuh.
+#pragma once
+
+#include "flk_tc.cuh"
+
+namespace flk {
+namespace tck {
+
+using namespace tc;  // PTX wrappers, image layout, epilogue helpers
+
+constexpr int kRowBlocksL = 2;
+constexpr int kRowsPerCtaL = kRowBlocksL * kTileRows;  // 256
+constexpr int kMaxDL = 1024;
+constexpr int kSlabBytes = kTileRows * kSlabK * 2;      // 8 KB: one 128-row slab of an operand image
+constexpr int kStageBytes = 3 * kSlabBytes;             // A block 0, A block 1, B tile
+constexpr int kStages = 8;
+constexpr int kEpiWarpsL = 4 * kRowBlocksL;
+constexpr int kMmaWarpL = kEpiWarpsL;
+constexpr int kProducerWarpL = kEpiWarpsL + 1;
+constexpr int kThreadsL = (kEpiWarpsL + 2) * 32;
+
+inline bool supports_d(int64_t d) { return d > tc::kMaxD && d <= kMaxDL; }
+inline int used_k(int64_t d) { return (int)(3 * d + 6); }  // always three norm pieces
+inline int k_steps(int64_t d) { return (int)(round_up(used_k(d), kMmaK) / kMmaK); }
+inline int64_t padded_k(int64_t d) { return round_up(used_k(d), kSlabK); }
+inline int n_slabs(int64_t d) { return (int)(padded_k(d) / kSlabK); }
+
+// ---------------------------------------------------------------------------------------------
+// Operand images for any feature count: one block = one 128-row tile, one thread = one row.  The image is
+// built slab by slab in shared memory (so that the global writes are coalesced 8 KB runs); the row's
+// features are re-read from X for each of the three copies the split needs (they stay in L1 / L2).
+// K layout of a row, as in flk_tc.cuh:  A = [xh | xh | xl | -n1 -n2 -n3 | 1 1 1 | 0..],
+//                                       B = [ch | cl | ch | 1 1 1 | -m1 -m2 -m3 | 0..].
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) prep_images_large_kernel(const float* __restrict__ X, int64_t n, int64_t rs,
+                                                                int64_t cs, int d, const float* __restrict__ sigma,
+                                                                float sigma_scalar, int sigma_len, float scale,
+                                                                int nslab, __half* __restrict__ img_a,
+                                                                __half* __restrict__ img_b, int* __restrict__ status) {
+  __shared__ __align__(16) __half slab[2][kTileRows * kSlabK];  // A and B version of the current slab
+  const int r = threadIdx.x;
+  const int64_t row = (int64_t)blockIdx.x * kTileRows + r;
+  const bool live = row < n;
+  const float* xr = X + (live ? row : 0) * rs;
+  auto scaled = [&](int f) -> float {
+    const float s = sigma != nullptr ? sigma[sigma_len == 1 ? 0 : f] : sigma_scalar;
+    return (xr[(int64_t)f * cs] / s) * scale;  // x / sigma rounded as in the reference, then the kernel's scale
+  };
+  // pass 1: squared norm of the value the two fp16 parts represent, range check
+  double nrm = 0.0;
+  bool out_of_range = false;
+  if (live) {
+    for (int f = 0; f < d; ++f) {
+      float xt = scaled(f);
+      if (!(fabsf(xt) <= 400.0f)) {
+        out_of_range = true;
+        xt = 0.0f;
+      }
+      const float hi = __half2float(__float2half_rn(xt));
+      const float lo = __half2float(__float2half_rn(xt - hi));
+      const double rep = (double)hi + (double)lo;
+      nrm += rep * rep;
+    }
+  }
+  double half_norm = 0.5 * nrm;
+  if (half_norm > (double)kNormLimit) {
+    out_of_range = true;
+    half_norm = 0.0;
+  }
+  if (out_of_range && live) atomicOr(status + kStatusRange, 1);
+  float piece[3];
+  {
+    double rem = half_norm;
+    for (int i = 0; i < 3; ++i) {
+      const float remf = __double2float_ru(rem);
+      const float pc = __half2float(i == 2 ? __float2half_ru(remf) : __float2half_rn(remf));
+      piece[i] = pc;
+      rem -= (double)pc;
+    }
+  }
+  const __half one = __float2half_rn(1.0f), zero = __float2half_rn(0.0f);
+  // pass 2: slabs
+  for (int s = 0; s < nslab; ++s) {
+    for (int e = 0; e < kSlabK; ++e) {
+      const int k = s * kSlabK + e;  // K index
+      __half va = zero, vb = zero;
+      if (live) {
+        if (k < 3 * d) {
+          const int region = k / d, f = k - region * d;
+          float xt = scaled(f);
+          if (!(fabsf(xt) <= 400.0f)) xt = 0.0f;
+          const __half hi = __float2half_rn(xt);
+          const __half lo = __float2half_rn(xt - __half2float(hi));
+          va = region == 2 ? lo : hi;   // A: hi, hi, lo
+          vb = region == 1 ? lo : hi;   // B: hi, lo, hi
+        } else if (k < 3 * d + 3) {
+          va = __float2half_rn(-piece[k - 3 * d]);
+          vb = one;
+        } else if (k < 3 * d + 6) {
+          va = one;
+          vb = __float2half_rn(-piece[k - 3 * d - 3]);
+        }
+      }
+      const int off = r * kSlabK + ((((e >> 3) ^ ((r >> 1) & 3))) << 3) + (e & 7);
+      slab[0][off] = va;
+      slab[1][off] = vb;
+    }
+    __syncthreads();
+    const int64_t base = ((int64_t)blockIdx.x * nslab + s) * (kTileRows * kSlabK);
+    for (int which = 0; which < 2; ++which) {
+      __half* dst = which == 0 ? img_a : img_b;
+      if (dst == nullptr) continue;
+      uint4* out4 = reinterpret_cast<uint4*>(dst + base);
+      const uint4* in4 = reinterpret_cast<const uint4*>(slab[which]);
+      for (int idx = r; idx < kTileRows * kSlabK / 8; idx += 128) out4[idx] = in4[idx];
+    }
+    __syncthreads();
+  }
+}
+
+inline int prep_images_large(int kernel, const void* X, int64_t n, int64_t rs, int64_t cs, int d,
+                             const float* sigma_dev, float sigma_scalar, int sigma_len, int64_t rows_pad, void* img_a,
+                             void* img_b, int* status, cudaStream_t stream) {
+  const float scale = (float)sqrt(scale_sq_for(kernel));
+  const int blocks = (int)(rows_pad / kTileRows);
+  prep_images_large_kernel<<<blocks, 128, 0, stream>>>(reinterpret_cast<const float*>(X), n, rs, cs, d, sigma_dev,
+                                                       sigma_scalar, sigma_len, scale, n_slabs(d),
+                                                       reinterpret_cast<__half*>(img_a),
+                                                       reinterpret_cast<__half*>(img_b), status);
+  FLK_CUDA_TRY(cudaGetLastError());
+  return FLK_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Sweep kernel
+// ---------------------------------------------------------------------------------------------
+struct SweepArgsL {
+  const __half* img_a;  // [r_pad / 128][nslab] slabs (output side)
+  const __half* img_b;  // [s_pad / 128][nslab] slabs (reduction side)
+  const float* vec;     // [t_chunks][s_pad][TT]
+  float* raw;           // [n_chunks][r_pad][tp]
+  int* status;
+  int tp;
+  int64_t r_pad;
+  int64_t s_pad;
+  int row_tiles;        // ceil(r / 256)
+  int n_col_tiles;      // ceil(s / 128)
+  int tiles_per_chunk;
+  int nslab;            // K slabs per operand tile
+  int ksteps;           // MMA K-steps carrying data (two per slab, possibly one in the last slab)
+};
+
+template <int TT>
+constexpr size_t tck_smem_bytes() {
+  return 1024 + (size_t)kStages * kStageBytes + (size_t)kVecStages * kColsPerTile * TT * 4 + 512;
+}
+
+template <int KT, int TT>
+__global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL p) {
+  constexpr int S = kStages, VS = kVecStages;
+  extern __shared__ unsigned char tck_smem_raw[];
+  const uint32_t raw_addr = smem_u32(tck_smem_raw);
+  const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+  unsigned char* smem = tck_smem_raw + pad;
+  unsigned char* ring = smem;                                           // [S][A0 | A1 | B] slabs
+  float* vs = reinterpret_cast<float*>(ring + S * kStageBytes);         // [VS][128][TT]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(vs) + VS * kColsPerTile * TT * 4);
+  // barrier map: s_full[S] | s_empty[S] | v_full[VS] | v_empty[VS] | t_full[4] | t_empty[4]   (index rb * 2 + buf)
+  uint64_t* bar_s_full = bars;
+  uint64_t* bar_s_empty = bar_s_full + S;
+  uint64_t* bar_v_full = bar_s_empty + S;
+  uint64_t* bar_v_empty = bar_v_full + VS;
+  uint64_t* bar_t_full = bar_v_empty + VS;
+  uint64_t* bar_t_empty = bar_t_full + 4;
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bar_t_empty + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
+  static_assert((2 * S + 2 * VS + 8) * 8 + 8 <= 512, "barrier block overflows its 512 bytes");
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+  const int row_tile = blockIdx.x % p.row_tiles;
+  const int chunk = blockIdx.x / p.row_tiles;
+  const int tchunk = blockIdx.y;
+  const int tile_begin = chunk * p.tiles_per_chunk;
+  const int tile_end = min(tile_begin + p.tiles_per_chunk, p.n_col_tiles);
+  const int ntiles = tile_end - tile_begin;
+  const int nslab = p.nslab;
+
+  __shared__ int skip_launch;
+  if (tid == 0) {
+    const volatile int* st = reinterpret_cast<const volatile int*>(p.status);
+    skip_launch = (st[kStatusTimeout] != 0 || st[kStatusRange] != 0) ? 1 : 0;
+  }
+  __syncthreads();
+  if (skip_launch) return;
+
+  if (tid == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(smem_u32(bar_s_full + s), 1);
+      mbar_init(smem_u32(bar_s_empty + s), 1);  // released by the MMA commit
+    }
+    for (int s = 0; s < VS; ++s) {
+      mbar_init(smem_u32(bar_v_full + s), 1);
+      mbar_init(smem_u32(bar_v_empty + s), kEpiWarpsL);
+    }
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(smem_u32(bar_t_full + i), 1);
+      mbar_init(smem_u32(bar_t_empty + i), 4);  // the four warps of that row block
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == kMmaWarpL) {
+    tmem_alloc(smem_u32(tmem_ptr), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr;
+
+  if (warp == kProducerWarpL) {
+    // ------------------------------ bulk-copy producer ------------------------------
+    const __half* a_base = p.img_a + (int64_t)row_tile * kRowBlocksL * nslab * (kTileRows * kSlabK);
+    const float* vec_base = p.vec + (int64_t)tchunk * p.s_pad * TT;
+    int64_t gs = 0;  // running slab counter
+    bool ok = true;
+    for (int j = 0; ok && j < ntiles; ++j) {
+      const int64_t ct = tile_begin + j;
+      const int vstage = j % VS;
+      if (!mbar_wait(smem_u32(bar_v_empty + vstage), ((j / VS) & 1) ^ 1)) {
+        if (lane == 0) atomicExch(p.status + kStatusTimeout, kErrProducer | 2);
+        *abort_flag = 1;
+        break;
+      }
+      if (elect_one()) {
+        const uint32_t vbar = smem_u32(bar_v_full + vstage);
+        mbar_expect_tx(vbar, kColsPerTile * TT * 4);
+        bulk_copy_g2s(smem_u32(vs) + vstage * kColsPerTile * TT * 4, vec_base + ct * kColsPerTile * TT,
+                      kColsPerTile * TT * 4, vbar);
+      }
+      __syncwarp();
+      const __half* b_base = p.img_b + ct * nslab * (kTileRows * kSlabK);
+      for (int s = 0; s < nslab; ++s, ++gs) {
+        const int stage = (int)(gs % S);
+        if (*abort_flag) { ok = false; break; }
+        if (!mbar_wait(smem_u32(bar_s_empty + stage), (uint32_t)(((gs / S) & 1) ^ 1))) {
+          if (lane == 0) atomicExch(p.status + kStatusTimeout, kErrProducer | 1);
+          *abort_flag = 1;
+          ok = false;
+          break;
+        }
+        if (elect_one()) {
+          const uint32_t bar = smem_u32(bar_s_full + stage);
+          const uint32_t dst = smem_u32(ring) + stage * kStageBytes;
+          mbar_expect_tx(bar, kStageBytes);
+          bulk_copy_g2s(dst, a_base + (int64_t)s * (kTileRows * kSlabK), kSlabBytes, bar);
+          bulk_copy_g2s(dst + kSlabBytes, a_base + ((int64_t)nslab + s) * (kTileRows * kSlabK), kSlabBytes, bar);
+          bulk_copy_g2s(dst + 2 * kSlabBytes, b_base + (int64_t)s * (kTileRows * kSlabK), kSlabBytes, bar);
+        }
+        __syncwarp();
+      }
+    }
+  } else if (warp == kMmaWarpL) {
+    // ------------------------------ MMA issuer ------------------------------
+    int64_t gs = 0;
+    bool ok = true;
+    for (int j = 0; ok && j < ntiles; ++j) {
+      const int buf = j & 1;
+      // both accumulators of this buffer must have been drained (tile j - 2)
+      for (int rb = 0; rb < kRowBlocksL; ++rb) {
+        if (!mbar_wait(smem_u32(bar_t_empty + rb * 2 + buf), ((j >> 1) & 1) ^ 1)) {
+          if (lane == 0) atomicExch(p.status + kStatusTimeout, kErrMma | 3);
+          *abort_flag = 1;
+          ok = false;
+        }
+      }
+      if (!ok) break;
+      tc_fence_after();
+      for (int s = 0; s < nslab; ++s, ++gs) {
+        const int stage = (int)(gs % S);
+        if (*abort_flag) { ok = false; break; }
+        if (!mbar_wait(smem_u32(bar_s_full + stage), (uint32_t)((gs / S) & 1))) {
+          if (lane == 0) atomicExch(p.status + kStatusTimeout, kErrMma | 2);
+          *abort_flag = 1;
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        if (elect_one()) {
+          const uint32_t sbase = smem_u32(ring) + stage * kStageBytes;
+          const uint64_t b_desc = make_smem_desc(sbase + 2 * kSlabBytes);
+          const int nks = min(2, p.ksteps - 2 * s);  // K-steps of this slab that carry data
+          for (int rb = 0; rb < kRowBlocksL; ++rb) {
+            const uint64_t a_desc = make_smem_desc(sbase + rb * kSlabBytes);
+            const uint32_t d_tmem = tmem_base + (uint32_t)((rb * 2 + buf) * kColsPerTile);
+            for (int ks = 0; ks < nks; ++ks)
+              mma_f16(d_tmem, a_desc + (uint64_t)(ks * 2), b_desc + (uint64_t)(ks * 2), kInstrDesc,
+                      (s > 0 || ks > 0) ? 1u : 0u);
+          }
+          mma_commit(smem_u32(bar_s_empty + stage));
+          if (s == nslab - 1) {
+            mma_commit(smem_u32(bar_t_full + 0 * 2 + buf));
+            mma_commit(smem_u32(bar_t_full + 1 * 2 + buf));
+          }
+        }
+        __syncwarp();
+      }
+    }
+  } else {
+    // ------------------------------ epilogue warps ------------------------------
+    const int q = warp & 3;
+    const int rb = warp >> 2;
+    uint64_t osum[2] = {0ull, 0ull};
+    uint32_t ra[32], rc[32];
+    bool epi_ok = true;
+    for (int j = 0; j < ntiles; ++j) {
+      const int vstage = j % VS, buf = j & 1;
+      if (*abort_flag) { epi_ok = false; break; }
+      if (!mbar_wait(smem_u32(bar_v_full + vstage), (j / VS) & 1) ||
+          !mbar_wait(smem_u32(bar_t_full + rb * 2 + buf), (j >> 1) & 1)) {
+        atomicExch(p.status + kStatusTimeout, kErrEpilogue | 1);
+        *abort_flag = 1;
+        epi_ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)((rb * 2 + buf) * kColsPerTile);
+      const float* vsm = vs + vstage * kColsPerTile * TT;
+      tmem_ld32(taddr, ra);
+      tmem_ld_wait_on(ra);
+      tmem_ld32(taddr + 32, rc, ra);
+      epilogue_32<KT, TT>(ra, vsm, osum);
+      tmem_ld_wait_on(rc, osum);
+      tmem_ld32(taddr + 64, ra, rc);
+      epilogue_32<KT, TT>(rc, vsm + 32 * TT, osum);
+      tmem_ld_wait_on(ra, osum);
+      tmem_ld32(taddr + 96, rc, ra);
+      tmem_ld_wait_on(rc);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(bar_t_empty + rb * 2 + buf));
+      epilogue_32<KT, TT>(ra, vsm + 64 * TT, osum);
+      epilogue_32<KT, TT>(rc, vsm + 96 * TT, osum);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(bar_v_empty + vstage));
+    }
+    if (epi_ok) {
+      const int64_t row = (int64_t)row_tile * kRowsPerCtaL + rb * kTileRows + q * 32 + lane;
+      float* dst = p.raw + ((int64_t)chunk * p.r_pad + row) * p.tp + tchunk * TT;
+      float a0, a1, b0, b1;
+      unpack2(osum[0], a0, a1);
+      unpack2(osum[1], b0, b1);
+      if constexpr (TT == 1) {
+        dst[0] = (a0 + a1) + (b0 + b1);
+      } else if constexpr (TT == 2) {
+        dst[0] = a0 + b0;
+        dst[1] = a1 + b1;
+      } else {
+        dst[0] = a0;
+        dst[1] = a1;
+        dst[2] = b0;
+        dst[3] = b1;
+      }
+    }
+  }
+
+  // ------------------------------ teardown ------------------------------
+  tc_fence_before();
+  __syncthreads();
+  const bool aborted = (*abort_flag != 0);
+  if (aborted && warp == kProducerWarpL && lane == 0) {
+    // give this CTA's own bulk copies a bounded chance to land before the shared memory is released
+    for (int s = 0; s < S; ++s)
+      for (int par = 0; par < 2; ++par)
+        if (mbar_try_wait(smem_u32(bar_s_full + s), par)) break;
+    for (int s = 0; s < VS; ++s)
+      for (int par = 0; par < 2; ++par)
+        if (mbar_try_wait(smem_u32(bar_v_full + s), par)) break;
+  }
+  __syncthreads();
+  if (warp == kMmaWarpL) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int KT, int TT>
+int launch_inst(const SweepArgsL& args, int n_chunks, int t_chunks, cudaStream_t stream) {
+  constexpr size_t smem = tck_smem_bytes<TT>();
+  static_assert(smem > 116 * 1024 && smem <= 227 * 1024, "one CTA per SM is assumed; shared memory budget");
+  static bool configured[16] = {false};
+  int dev = 0;
+  FLK_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev >= 16 || !configured[dev]) {
+    FLK_CUDA_TRY(cudaFuncSetAttribute(kmv_tck_kernel<KT, TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    if (dev < 16) configured[dev] = true;
+  }
+  dim3 grid((unsigned)(args.row_tiles * n_chunks), (unsigned)t_chunks, 1);
+  kmv_tck_kernel<KT, TT><<<grid, kThreadsL, smem, stream>>>(args);
+  FLK_CUDA_TRY(cudaGetLastError());
+  return FLK_OK;
+}
+
+template <int KT>
+int launch_tt(const SweepArgsL& args, int tt, int n_chunks, int t_chunks, cudaStream_t stream) {
+  switch (tt) {
+    case 1: return launch_inst<KT, 1>(args, n_chunks, t_chunks, stream);
+    case 2: return launch_inst<KT, 2>(args, n_chunks, t_chunks, stream);
+    case 4: return launch_inst<KT, 4>(args, n_chunks, t_chunks, stream);
+  }
+  return fail(FLK_ERR_BAD_ARG, "internal: unsupported TT=%d", tt);
+}
+
+inline int launch_sweep(int kernel, int d, SweepArgsL args, int tt, int n_chunks, int t_chunks, cudaStream_t stream) {
+  args.nslab = n_slabs(d);
+  args.ksteps = k_steps(d);
+  switch (kernel) {
+    case FLK_GAUSSIAN: return launch_tt<FLK_GAUSSIAN>(args, tt, n_chunks, t_chunks, stream);
+    case FLK_LAPLACIAN: return launch_tt<FLK_LAPLACIAN>(args, tt, n_chunks, t_chunks, stream);
+    case FLK_MATERN15: return launch_tt<FLK_MATERN15>(args, tt, n_chunks, t_chunks, stream);
+    case FLK_MATERN25: return launch_tt<FLK_MATERN25>(args, tt, n_chunks, t_chunks, stream);
+  }
+  return fail(FLK_ERR_BAD_ARG, "unknown kernel id %d", kernel);
+}
+
+}  // namespace tck
+}  // namespace flk

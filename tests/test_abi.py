@@ -45,10 +45,13 @@ def test_workspace_queries_are_pure_host_arithmetic(lib):
     assert 0 < small < big < 16 * 2**30
     assert lib.flk_fmmv_workspace_bytes(0, 0, 20000, 1000, 10, 1, 0) <= small
     assert lib.flk_fdmmv_host_workspace_bytes(0, 0, 20000, 1000, 10, 1, 0) > small
-    # fp64 and large d go to the SIMT kernel, fp32 with d <= 30 to the tensor-core kernel
+    # fp64 goes to the SIMT / DMMA kernels, fp32 to the tensor-core kernels (resident operands up to d = 30,
+    # K-loop variant up to d = 1024)
     assert lib.flk_uses_tensor_cores(0, 0, 28, 1, 0) == 1
     assert lib.flk_uses_tensor_cores(0, 3, 30, 4, 0) == 1
-    assert lib.flk_uses_tensor_cores(0, 0, 31, 1, 0) == 0
+    assert lib.flk_uses_tensor_cores(0, 0, 31, 1, 0) == 1
+    assert lib.flk_uses_tensor_cores(0, 0, 1024, 1, 0) == 1
+    assert lib.flk_uses_tensor_cores(0, 0, 1025, 1, 0) == 0
     assert lib.flk_uses_tensor_cores(1, 0, 9, 1, 0) == 0
     assert lib.flk_uses_tensor_cores(0, 0, 28, 1, _lib.FLAG_FORCE_SIMT) == 0
     assert lib.flk_fmmv_workspace_bytes(7, 0, 10, 10, 2, 1, 0) == _lib.FLK_ERR_BAD_ARG
