@@ -12,8 +12,10 @@
 // accumulators each (512 columns in all), so the MMAs of tile j+1 run under the epilogue of tile j.  The
 // kernel is bound by the tensor pipe / the L2 traffic of the re-streamed operands (3 x the bytes of a plain
 // GEMM of the same shape, because every feature appears three times in the split), not by MUFU.
-// Warps 0-7: epilogue (row block = warp / 4, TMEM lane quarter = warp % 4); warp 8: MMA issuer and TMEM owner;
-// warp 9: bulk-copy producer.  Every wait is bounded as in flk_tc.cuh.
+// Warps 0-15: epilogue (TMEM lane quarter = warp % 4, row block = (warp / 4) % 2, column half of the tile =
+// warp / 8; the two halves of a row are added at the end through shared memory); warps 16, 17: MMA issuers, one
+// per row block (the barrier round trip between two slabs of one issuer runs under the MMAs of the other; warp 16
+// owns the TMEM allocation); warp 18: bulk-copy producer.  Every wait is bounded as in flk_tc.cuh.
 #pragma once
 
 #include "flk_tc.cuh"
@@ -27,12 +29,13 @@ constexpr int kRowBlocksL = 2;
 constexpr int kRowsPerCtaL = kRowBlocksL * kTileRows;  // 256
 constexpr int kMaxDL = 1024;
 constexpr int kSlabBytes = kTileRows * kSlabK * 2;      // 8 KB: one 128-row slab of an operand image
-constexpr int kStageBytes = 3 * kSlabBytes;             // A block 0, A block 1, B tile
 constexpr int kStages = 8;
-constexpr int kEpiWarpsL = 4 * kRowBlocksL;
-constexpr int kMmaWarpL = kEpiWarpsL;
-constexpr int kProducerWarpL = kEpiWarpsL + 1;
-constexpr int kThreadsL = (kEpiWarpsL + 2) * 32;
+constexpr int kMaxResidentSlabs = 8;                    // both A blocks stay in shared memory up to this many slabs
+constexpr int kColSplitL = 2;                           // epilogue warps per (row block, lane quarter): each takes 64 columns of a tile
+constexpr int kEpiWarpsL = 4 * kRowBlocksL * kColSplitL;
+constexpr int kMmaWarpL = kEpiWarpsL;                   // warps 16, 17: MMA issuer of row block (warp - 16)
+constexpr int kProducerWarpL = kEpiWarpsL + kRowBlocksL;
+constexpr int kThreadsL = (kEpiWarpsL + kRowBlocksL + 1) * 32;
 
 inline bool supports_d(int64_t d) { return d > tc::kMaxD && d <= kMaxDL; }
 inline int used_k(int64_t d) { return (int)(3 * d + 6); }  // always three norm pieces
@@ -165,31 +168,40 @@ struct SweepArgsL {
   int ksteps;           // MMA K-steps carrying data (two per slab, possibly one in the last slab)
 };
 
-template <int TT>
+// ARES: the two A blocks of the CTA (256 rows x nslab slabs, at most 128 KB) are loaded once and stay resident;
+// a ring stage then carries the B slab only (8 KB instead of 24 KB), which cuts the L2 traffic three-fold.
+template <int TT, bool ARES>
 constexpr size_t tck_smem_bytes() {
-  return 1024 + (size_t)kStages * kStageBytes + (size_t)kVecStages * kColsPerTile * TT * 4 + 512;
+  return 1024 + (ARES ? (size_t)kRowBlocksL * kMaxResidentSlabs * kSlabBytes : 0) +
+         (size_t)kStages * (ARES ? 1 : 3) * kSlabBytes + (size_t)kVecStages * kColsPerTile * TT * 4 + 512 +
+         (size_t)kRowsPerCtaL * TT * 4 /* partial sums of the second column half */;
 }
 
-template <int KT, int TT>
+template <int KT, int TT, bool ARES>
 __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL p) {
   constexpr int S = kStages, VS = kVecStages;
+  constexpr int kStageBytes = (ARES ? 1 : 3) * kSlabBytes;  // [A block 0 | A block 1 |] B tile
+  constexpr int kAResBytes = ARES ? kRowBlocksL * kMaxResidentSlabs * kSlabBytes : 0;
   extern __shared__ unsigned char tck_smem_raw[];
   const uint32_t raw_addr = smem_u32(tck_smem_raw);
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
   unsigned char* smem = tck_smem_raw + pad;
-  unsigned char* ring = smem;                                           // [S][A0 | A1 | B] slabs
+  unsigned char* a_res = smem;                                          // ARES: [2 row blocks][nslab] slabs
+  unsigned char* ring = smem + kAResBytes;                              // [S][A0 | A1 | B] or [S][B] slabs
   float* vs = reinterpret_cast<float*>(ring + S * kStageBytes);         // [VS][128][TT]
   uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(vs) + VS * kColsPerTile * TT * 4);
-  // barrier map: s_full[S] | s_empty[S] | v_full[VS] | v_empty[VS] | t_full[4] | t_empty[4]   (index rb * 2 + buf)
+  // barrier map: s_full[S] | s_empty[S] | v_full[VS] | v_empty[VS] | t_full[4] | t_empty[4] (index rb * 2 + buf) | a_full
   uint64_t* bar_s_full = bars;
   uint64_t* bar_s_empty = bar_s_full + S;
   uint64_t* bar_v_full = bar_s_empty + S;
   uint64_t* bar_v_empty = bar_v_full + VS;
   uint64_t* bar_t_full = bar_v_empty + VS;
   uint64_t* bar_t_empty = bar_t_full + 4;
-  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bar_t_empty + 4);
+  uint64_t* bar_a_full = bar_t_empty + 4;
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bar_a_full + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
-  static_assert((2 * S + 2 * VS + 8) * 8 + 8 <= 512, "barrier block overflows its 512 bytes");
+  static_assert((2 * S + 2 * VS + 9) * 8 + 8 <= 512, "barrier block overflows its 512 bytes");
+  float* combine = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(bars) + 512);  // [256 rows][TT]
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
@@ -212,7 +224,7 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(smem_u32(bar_s_full + s), 1);
-      mbar_init(smem_u32(bar_s_empty + s), 1);  // released by the MMA commit
+      mbar_init(smem_u32(bar_s_empty + s), kRowBlocksL);  // one MMA commit per issuer
     }
     for (int s = 0; s < VS; ++s) {
       mbar_init(smem_u32(bar_v_full + s), 1);
@@ -220,8 +232,9 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
     }
     for (int i = 0; i < 4; ++i) {
       mbar_init(smem_u32(bar_t_full + i), 1);
-      mbar_init(smem_u32(bar_t_empty + i), 4);  // the four warps of that row block
+      mbar_init(smem_u32(bar_t_empty + i), 4 * kColSplitL);  // the eight warps of that row block
     }
+    mbar_init(smem_u32(bar_a_full), 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -238,6 +251,15 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
     // ------------------------------ bulk-copy producer ------------------------------
     const __half* a_base = p.img_a + (int64_t)row_tile * kRowBlocksL * nslab * (kTileRows * kSlabK);
     const float* vec_base = p.vec + (int64_t)tchunk * p.s_pad * TT;
+    if (ARES && elect_one()) {
+      // the CTA's two A blocks are contiguous in the image: [row block][slab]
+      const uint32_t bytes = (uint32_t)(kRowBlocksL * nslab * kSlabBytes);
+      mbar_expect_tx(smem_u32(bar_a_full), bytes);
+      for (int i = 0; i < kRowBlocksL * nslab; ++i)
+        bulk_copy_g2s(smem_u32(a_res) + i * kSlabBytes, a_base + (int64_t)i * (kTileRows * kSlabK), kSlabBytes,
+                      smem_u32(bar_a_full));
+    }
+    __syncwarp();
     int64_t gs = 0;  // running slab counter
     bool ok = true;
     for (int j = 0; ok && j < ntiles; ++j) {
@@ -269,32 +291,37 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
           const uint32_t bar = smem_u32(bar_s_full + stage);
           const uint32_t dst = smem_u32(ring) + stage * kStageBytes;
           mbar_expect_tx(bar, kStageBytes);
-          bulk_copy_g2s(dst, a_base + (int64_t)s * (kTileRows * kSlabK), kSlabBytes, bar);
-          bulk_copy_g2s(dst + kSlabBytes, a_base + ((int64_t)nslab + s) * (kTileRows * kSlabK), kSlabBytes, bar);
-          bulk_copy_g2s(dst + 2 * kSlabBytes, b_base + (int64_t)s * (kTileRows * kSlabK), kSlabBytes, bar);
+          if (!ARES) {
+            bulk_copy_g2s(dst, a_base + (int64_t)s * (kTileRows * kSlabK), kSlabBytes, bar);
+            bulk_copy_g2s(dst + kSlabBytes, a_base + ((int64_t)nslab + s) * (kTileRows * kSlabK), kSlabBytes, bar);
+          }
+          bulk_copy_g2s(dst + (ARES ? 0 : 2) * kSlabBytes, b_base + (int64_t)s * (kTileRows * kSlabK), kSlabBytes, bar);
         }
         __syncwarp();
       }
     }
-  } else if (warp == kMmaWarpL) {
-    // ------------------------------ MMA issuer ------------------------------
+  } else if (warp >= kMmaWarpL) {
+    // ------------------------------ MMA issuers (one per row block) ------------------------------
+    const int rb = warp - kMmaWarpL;
     int64_t gs = 0;
     bool ok = true;
+    if (ARES && !mbar_wait(smem_u32(bar_a_full), 0)) {
+      if (lane == 0) atomicExch(p.status + kStatusTimeout, kErrMma | 1);
+      *abort_flag = 1;
+      ok = false;
+    }
     for (int j = 0; ok && j < ntiles; ++j) {
       const int buf = j & 1;
-      // both accumulators of this buffer must have been drained (tile j - 2)
-      for (int rb = 0; rb < kRowBlocksL; ++rb) {
-        if (!mbar_wait(smem_u32(bar_t_empty + rb * 2 + buf), ((j >> 1) & 1) ^ 1)) {
-          if (lane == 0) atomicExch(p.status + kStatusTimeout, kErrMma | 3);
-          *abort_flag = 1;
-          ok = false;
-        }
+      if (*abort_flag) break;
+      // this row block's accumulator of this buffer must have been drained (tile j - 2)
+      if (!mbar_wait(smem_u32(bar_t_empty + rb * 2 + buf), ((j >> 1) & 1) ^ 1)) {
+        if (lane == 0) atomicExch(p.status + kStatusTimeout, kErrMma | 3);
+        *abort_flag = 1;
+        break;
       }
-      if (!ok) break;
-      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + (uint32_t)((rb * 2 + buf) * kColsPerTile);
       for (int s = 0; s < nslab; ++s, ++gs) {
         const int stage = (int)(gs % S);
-        if (*abort_flag) { ok = false; break; }
         if (!mbar_wait(smem_u32(bar_s_full + stage), (uint32_t)((gs / S) & 1))) {
           if (lane == 0) atomicExch(p.status + kStatusTimeout, kErrMma | 2);
           *abort_flag = 1;
@@ -304,20 +331,15 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
         tc_fence_after();
         if (elect_one()) {
           const uint32_t sbase = smem_u32(ring) + stage * kStageBytes;
-          const uint64_t b_desc = make_smem_desc(sbase + 2 * kSlabBytes);
+          const uint64_t b_desc = make_smem_desc(sbase + (ARES ? 0 : 2) * kSlabBytes);
+          const uint64_t a_desc = make_smem_desc(ARES ? smem_u32(a_res) + (rb * nslab + s) * kSlabBytes
+                                                      : sbase + rb * kSlabBytes);
           const int nks = min(2, p.ksteps - 2 * s);  // K-steps of this slab that carry data
-          for (int rb = 0; rb < kRowBlocksL; ++rb) {
-            const uint64_t a_desc = make_smem_desc(sbase + rb * kSlabBytes);
-            const uint32_t d_tmem = tmem_base + (uint32_t)((rb * 2 + buf) * kColsPerTile);
-            for (int ks = 0; ks < nks; ++ks)
-              mma_f16(d_tmem, a_desc + (uint64_t)(ks * 2), b_desc + (uint64_t)(ks * 2), kInstrDesc,
-                      (s > 0 || ks > 0) ? 1u : 0u);
-          }
+          for (int ks = 0; ks < nks; ++ks)
+            mma_f16(d_tmem, a_desc + (uint64_t)(ks * 2), b_desc + (uint64_t)(ks * 2), kInstrDesc,
+                    (s > 0 || ks > 0) ? 1u : 0u);
           mma_commit(smem_u32(bar_s_empty + stage));
-          if (s == nslab - 1) {
-            mma_commit(smem_u32(bar_t_full + 0 * 2 + buf));
-            mma_commit(smem_u32(bar_t_full + 1 * 2 + buf));
-          }
+          if (s == nslab - 1) mma_commit(smem_u32(bar_t_full + rb * 2 + buf));
         }
         __syncwarp();
       }
@@ -325,7 +347,8 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
   } else {
     // ------------------------------ epilogue warps ------------------------------
     const int q = warp & 3;
-    const int rb = warp >> 2;
+    const int rb = (warp >> 2) & 1;
+    const int half = warp >> 3;  // columns half * 64 .. + 63 of every tile
     uint64_t osum[2] = {0ull, 0ull};
     uint32_t ra[32], rc[32];
     bool epi_ok = true;
@@ -340,43 +363,49 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
         break;
       }
       tc_fence_after();
-      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)((rb * 2 + buf) * kColsPerTile);
-      const float* vsm = vs + vstage * kColsPerTile * TT;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) +
+                             (uint32_t)((rb * 2 + buf) * kColsPerTile + half * 64);
+      const float* vsm = vs + (vstage * kColsPerTile + half * 64) * TT;
       tmem_ld32(taddr, ra);
       tmem_ld_wait_on(ra);
       tmem_ld32(taddr + 32, rc, ra);
-      epilogue_32<KT, TT>(ra, vsm, osum);
-      tmem_ld_wait_on(rc, osum);
-      tmem_ld32(taddr + 64, ra, rc);
-      epilogue_32<KT, TT>(rc, vsm + 32 * TT, osum);
-      tmem_ld_wait_on(ra, osum);
-      tmem_ld32(taddr + 96, rc, ra);
       tmem_ld_wait_on(rc);
+      // this warp's 64 columns are in registers: hand the accumulator back before evaluating them
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(bar_t_empty + rb * 2 + buf));
-      epilogue_32<KT, TT>(ra, vsm + 64 * TT, osum);
-      epilogue_32<KT, TT>(rc, vsm + 96 * TT, osum);
+      epilogue_32<KT, TT>(ra, vsm, osum);
+      epilogue_32<KT, TT>(rc, vsm + 32 * TT, osum);
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(bar_v_empty + vstage));
     }
-    if (epi_ok) {
-      const int64_t row = (int64_t)row_tile * kRowsPerCtaL + rb * kTileRows + q * 32 + lane;
+    // per-thread sums of this column half
+    float a0, a1, b0, b1, o[4];
+    unpack2(osum[0], a0, a1);
+    unpack2(osum[1], b0, b1);
+    if constexpr (TT == 1) {
+      o[0] = (a0 + a1) + (b0 + b1);
+    } else if constexpr (TT == 2) {
+      o[0] = a0 + b0;
+      o[1] = a1 + b1;
+    } else {
+      o[0] = a0;
+      o[1] = a1;
+      o[2] = b0;
+      o[3] = b1;
+    }
+    const int rloc = rb * kTileRows + q * 32 + lane;
+    if (half == 1) {
+#pragma unroll
+      for (int t = 0; t < TT; ++t) combine[rloc * TT + t] = o[t];
+    }
+    // all sixteen epilogue warps meet here (named barrier 1; the issuer and producer warps do not take part)
+    asm volatile("bar.sync 1, %0;" ::"n"(kEpiWarpsL * 32) : "memory");
+    if (half == 0 && epi_ok && *abort_flag == 0) {
+      const int64_t row = (int64_t)row_tile * kRowsPerCtaL + rloc;
       float* dst = p.raw + ((int64_t)chunk * p.r_pad + row) * p.tp + tchunk * TT;
-      float a0, a1, b0, b1;
-      unpack2(osum[0], a0, a1);
-      unpack2(osum[1], b0, b1);
-      if constexpr (TT == 1) {
-        dst[0] = (a0 + a1) + (b0 + b1);
-      } else if constexpr (TT == 2) {
-        dst[0] = a0 + b0;
-        dst[1] = a1 + b1;
-      } else {
-        dst[0] = a0;
-        dst[1] = a1;
-        dst[2] = b0;
-        dst[3] = b1;
-      }
+#pragma unroll
+      for (int t = 0; t < TT; ++t) dst[t] = o[t] + combine[rloc * TT + t];
     }
   }
 
@@ -386,6 +415,7 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
   const bool aborted = (*abort_flag != 0);
   if (aborted && warp == kProducerWarpL && lane == 0) {
     // give this CTA's own bulk copies a bounded chance to land before the shared memory is released
+    if (ARES) mbar_wait(smem_u32(bar_a_full), 0);
     for (int s = 0; s < S; ++s)
       for (int par = 0; par < 2; ++par)
         if (mbar_try_wait(smem_u32(bar_s_full + s), par)) break;
@@ -401,29 +431,34 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
   }
 }
 
-template <int KT, int TT>
+template <int KT, int TT, bool ARES>
 int launch_inst(const SweepArgsL& args, int n_chunks, int t_chunks, cudaStream_t stream) {
-  constexpr size_t smem = tck_smem_bytes<TT>();
+  constexpr size_t smem = tck_smem_bytes<TT, ARES>();
   static_assert(smem > 116 * 1024 && smem <= 227 * 1024, "one CTA per SM is assumed; shared memory budget");
   static bool configured[16] = {false};
   int dev = 0;
   FLK_CUDA_TRY(cudaGetDevice(&dev));
   if (dev >= 16 || !configured[dev]) {
-    FLK_CUDA_TRY(cudaFuncSetAttribute(kmv_tck_kernel<KT, TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    FLK_CUDA_TRY(cudaFuncSetAttribute(kmv_tck_kernel<KT, TT, ARES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)smem));
     if (dev < 16) configured[dev] = true;
   }
   dim3 grid((unsigned)(args.row_tiles * n_chunks), (unsigned)t_chunks, 1);
-  kmv_tck_kernel<KT, TT><<<grid, kThreadsL, smem, stream>>>(args);
+  kmv_tck_kernel<KT, TT, ARES><<<grid, kThreadsL, smem, stream>>>(args);
   FLK_CUDA_TRY(cudaGetLastError());
   return FLK_OK;
 }
 
 template <int KT>
 int launch_tt(const SweepArgsL& args, int tt, int n_chunks, int t_chunks, cudaStream_t stream) {
+  const bool ares = args.nslab <= kMaxResidentSlabs;
   switch (tt) {
-    case 1: return launch_inst<KT, 1>(args, n_chunks, t_chunks, stream);
-    case 2: return launch_inst<KT, 2>(args, n_chunks, t_chunks, stream);
-    case 4: return launch_inst<KT, 4>(args, n_chunks, t_chunks, stream);
+    case 1: return ares ? launch_inst<KT, 1, true>(args, n_chunks, t_chunks, stream)
+                        : launch_inst<KT, 1, false>(args, n_chunks, t_chunks, stream);
+    case 2: return ares ? launch_inst<KT, 2, true>(args, n_chunks, t_chunks, stream)
+                        : launch_inst<KT, 2, false>(args, n_chunks, t_chunks, stream);
+    case 4: return ares ? launch_inst<KT, 4, true>(args, n_chunks, t_chunks, stream)
+                        : launch_inst<KT, 4, false>(args, n_chunks, t_chunks, stream);
   }
   return fail(FLK_ERR_BAD_ARG, "internal: unsupported TT=%d", tt);
 }
