@@ -308,6 +308,7 @@ static int check_common(int dtype, int kernel, int64_t n, int64_t m, int64_t d, 
   if (dtype != FLK_F32 && dtype != FLK_F64) return fail(FLK_ERR_BAD_ARG, "unknown dtype %d", dtype);
   if (kernel < FLK_GAUSSIAN || kernel > FLK_MATERN25) return fail(FLK_ERR_BAD_ARG, "unknown kernel id %d", kernel);
   if (n < 0 || m < 0 || d < 0 || t < 0) return fail(FLK_ERR_BAD_ARG, "negative dimension");
+  if (d == 0 && (n > 0 || m > 0)) return fail(FLK_ERR_BAD_ARG, "data with zero features (d = 0)");
   if (d > (1 << 20) || t > (1 << 20)) return fail(FLK_ERR_UNSUPPORTED, "d or t too large");
   if (n > (int64_t)1 << 40 || m > (int64_t)1 << 40) return fail(FLK_ERR_UNSUPPORTED, "n or m too large");
   return FLK_OK;

@@ -292,35 +292,53 @@ __device__ __forceinline__ void ex2_fma_pair(float x0, float x1, float& y0, floa
   y1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
 }
 
+// Distance-type kernel functions: everything but the final exponential.  acc = -D^2; returns the argument of
+// the exponential in base 2 and the polynomial factor in front of it.
 template <int KT>
-__device__ __forceinline__ float eval_acc(float acc) {
-  if (KT == FLK_GAUSSIAN) {
-    // acc = -(log2(e) / 2) D^2.  The image builder rounds the norm up, so acc errs on the negative
-    // side; what is left above zero for coincident points is accumulation rounding (k <= 1 + ~1e-7),
-    // which is not worth an extra instruction per evaluation.
-    return ex2_approx(acc);
+__device__ __forceinline__ void pre_exp(float acc, float& arg2, float& factor) {
+  const float dist = sqrt_approx(fmaxf(-acc, 0.0f));
+  if (KT == FLK_LAPLACIAN) {
+    arg2 = dist * (-kLog2e);
+    factor = 1.0f;
+  } else if (KT == FLK_MATERN15) {
+    const float s = dist * 1.7320508075688772f;
+    arg2 = s * (-kLog2e);
+    factor = 1.0f + s;
   } else {
-    const float dist = sqrt_approx(fmaxf(-acc, 0.0f));  // acc = -D^2
-    if (KT == FLK_LAPLACIAN) return ex2_approx(dist * (-kLog2e));
-    if (KT == FLK_MATERN15) {
-      const float s = dist * 1.7320508075688772f;
-      return (1.0f + s) * ex2_approx(s * (-kLog2e));
-    }
     const float s = dist * 2.23606797749979f;
-    return fmaf(s, fmaf(s, 1.0f / 3.0f, 1.0f), 1.0f) * ex2_approx(s * (-kLog2e));
+    arg2 = s * (-kLog2e);
+    factor = fmaf(s, fmaf(s, 1.0f / 3.0f, 1.0f), 1.0f);
   }
 }
 
-// Two adjacent accumulator columns -> two kernel values.  POLY selects the FMA-pipe exponential
-// (Gaussian only; the other kernel functions are bound by their two MUFU ops and a longer FMA
-// tail, and always take the MUFU path).
+// Two adjacent accumulator columns -> two kernel values.  POLY selects the FMA-pipe exponential for this pair
+// (the square root of the Laplacian / Matern kernels always runs on the MUFU unit).
+// Gaussian: acc = -(log2(e) / 2) D^2.  The image builder rounds the norm up, so acc errs on the negative side;
+// what is left above zero for coincident points is accumulation rounding (k <= 1 + ~1e-7), which is not worth
+// an extra instruction per evaluation.
 template <int KT, bool POLY>
 __device__ __forceinline__ void eval_pair(uint32_t b0, uint32_t b1, float& k0, float& k1) {
-  if constexpr (KT == FLK_GAUSSIAN && POLY) {
-    ex2_fma_pair(__uint_as_float(b0), __uint_as_float(b1), k0, k1);
+  if constexpr (KT == FLK_GAUSSIAN) {
+    if constexpr (POLY) {
+      ex2_fma_pair(__uint_as_float(b0), __uint_as_float(b1), k0, k1);
+    } else {
+      k0 = ex2_approx(__uint_as_float(b0));
+      k1 = ex2_approx(__uint_as_float(b1));
+    }
   } else {
-    k0 = eval_acc<KT>(__uint_as_float(b0));
-    k1 = eval_acc<KT>(__uint_as_float(b1));
+    float a0, a1, f0, f1;
+    pre_exp<KT>(__uint_as_float(b0), a0, f0);
+    pre_exp<KT>(__uint_as_float(b1), a1, f1);
+    if constexpr (POLY) {
+      ex2_fma_pair(a0, a1, k0, k1);
+    } else {
+      k0 = ex2_approx(a0);
+      k1 = ex2_approx(a1);
+    }
+    if constexpr (KT != FLK_LAPLACIAN) {
+      k0 *= f0;
+      k1 *= f1;
+    }
   }
 }
 
@@ -485,11 +503,17 @@ constexpr size_t tc_smem_bytes() {
 // error codes written to the status word: role * 16 + which wait
 enum { kErrProducer = 0x10, kErrMma = 0x20, kErrEpilogue = 0x30 };
 
-// Is column pair pr (0..15 within a 32-column piece) evaluated on the FMA pipe?  The polynomial
-// pairs are spread evenly so both pipes have work throughout the piece.
+// Which column pairs (0..15 within a 32-column piece) take the FMA-pipe exponential: a per-kernel-function
+// count (measured optima on config-2 data; the Laplacian / Matern epilogues carry a MUFU square root and more
+// FMA work per value), spread evenly over the piece so both pipes have work throughout.
+template <int KT>
+__host__ __device__ constexpr int poly_pairs_of() {
+  return KT == FLK_GAUSSIAN ? kPolyPairs : (KT == FLK_MATERN25 ? 5 : 8);
+}
 template <int KT>
 __host__ __device__ constexpr bool poly_pair(int pr) {
-  return KT == FLK_GAUSSIAN && kPolyPairs > 0 && ((pr + 1) * kPolyPairs / 16 != pr * kPolyPairs / 16);
+  constexpr int np = poly_pairs_of<KT>();
+  return np > 0 && ((pr + 1) * np / 16 != pr * np / 16);
 }
 
 // Kernel function + contraction for 32 accumulator columns held in registers.  `vsm` points at the
