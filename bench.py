@@ -195,14 +195,22 @@ def run_fit(args):
     inside the dmmv calls (the hot path) and the training accuracy."""
     if not torch.cuda.is_available():
         raise RuntimeError("bench.py needs a GPU (there is no CPU fallback)")
-    dev = torch.device("cuda", 0)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
+    import torch.distributed as dist
+
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
     from falkon_b200 import Falkon, FalkonOptions, _lib
     from falkon_b200.kernels import GaussianKernel
 
     _lib.build()
-    n, m = args.rows if args.rows != N_PER_GPU else 10_000_000, args.centres
-    g = torch.Generator(device=dev).manual_seed(1003)
+    n_total, m = args.rows if args.rows != N_PER_GPU else 10_000_000, args.centres
+    n = n_total // world  # rows of this rank's shard (strong scaling: the data set is fixed)
+    g = torch.Generator(device=dev).manual_seed(1003 + rank)
     z = (torch.rand(n, 1, generator=g, device=dev) < 0.5).to(torch.float32)
     X = torch.randn(n, D, generator=g, device=dev) + (2.0 * z - 1.0) * 0.5
     flip = torch.rand(n, 1, generator=g, device=dev) < 0.05
@@ -221,24 +229,34 @@ def run_fit(args):
         return out
 
     kernel.dmmv = timed_dmmv
-    model = Falkon(kernel=kernel, penalty=1e-7, M=m, maxiter=20, seed=3, options=FalkonOptions())
+    model = Falkon(kernel=kernel, penalty=1e-7, M=m, maxiter=20, seed=3, options=FalkonOptions(),
+                   group=dist.group.WORLD if world > 1 else None)
+    if world > 1:
+        dist.barrier()
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     model.fit(X, Y)
     torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
     wall = time.perf_counter() - t0
-    pred = model.predict(X[:1_000_000])
-    acc = float(((pred > 0) == (Y[:1_000_000] > 0)).float().mean())
+    n_eval = min(n, 1_000_000)
+    pred = model.predict(X[:n_eval])
+    acc = float(((pred > 0) == (Y[:n_eval] > 0)).float().mean())
     iters = model.maxiter + 2  # 20 CG products + the full-gradient refreshes at iterations 10 and 20
-    print(json.dumps({
-        "workload": f"config3: Falkon.fit, N={n} x d={D} mixture, +-1 labels (5% flips), Gaussian sigma=5, M={m}, "
-                    "lambda=1e-7, fp32, 20 CG iterations, preconditioner included",
-        "fit_wall_s": wall, "preconditioner_s": model.fit_times_[0], "dmmv_s_total": dmmv_s[0],
-        "dmmv_calls": iters, "dmmv_pair_evals_per_s": iters * float(n) * m / dmmv_s[0],
-        "train_accuracy_first_1e6_rows": acc, "bayes_accuracy_note": "labels carry 5 % flips; the mixture itself overlaps",
-        "tc_status": _lib.tc_status(dev), "range_flag": _lib.range_flag(dev),
-        "peak_mem_gb": torch.cuda.max_memory_allocated(dev) / 1e9,
-    }))
+    if rank == 0:
+        print(json.dumps({
+            "workload": f"config3: Falkon.fit, N={n_total} x d={D} mixture, +-1 labels (5% flips), Gaussian sigma=5, "
+                        f"M={m}, lambda=1e-7, fp32, 20 CG iterations, preconditioner included",
+            "n_gpus": world, "scaling": "strong", "rows_per_gpu": n,
+            "fit_wall_s": wall, "preconditioner_s": model.fit_times_[0], "dmmv_s_total": dmmv_s[0],
+            "dmmv_calls": iters, "dmmv_pair_evals_per_s": iters * float(n) * world * m / dmmv_s[0],
+            "train_accuracy_first_rows": acc, "accuracy_note": "labels carry 5 % flips",
+            "tc_status": _lib.tc_status(dev), "range_flag": _lib.range_flag(dev),
+            "peak_mem_gb": torch.cuda.max_memory_allocated(dev) / 1e9,
+        }))
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def _dense_fdmmv_fp64(X, C, v, w, kind, sigma, rows_per_block=4096):
