@@ -116,8 +116,9 @@ static void choose_tt(int64_t t, bool allow_wide, int* tt, int* tp) {
   *tp = (int)round_up(std::max<int64_t>(t, 1), *tt);
 }
 
-// `allow_wide`: the plan may use the wide kernel (never for the tensor-core kernel, and never for its SIMT
-// alternative, which shares the vector buffers of the tensor-core plan and therefore its column grouping).
+// `allow_wide`: the plan may group 32 vector columns per pass (SIMT wide / DMMA kernels, K-loop tensor-core kernel;
+// never the resident tensor-core kernel).  The SIMT alternative of a tensor-core plan shares its vector buffers
+// and therefore must be planned with the same column grouping.
 static SweepPlan plan_sweep(bool tc, int dtype, int64_t r, int64_t s, int64_t t, bool allow_wide = false,
                             bool kloop = false) {
   SweepPlan p;
@@ -127,7 +128,7 @@ static SweepPlan plan_sweep(bool tc, int dtype, int64_t r, int64_t s, int64_t t,
   p.s = s;
   p.r_pad = round_up(std::max<int64_t>(r, 1), kRowPad);
   p.s_pad = round_up(std::max<int64_t>(s, 1), kRowPad);
-  choose_tt(t, allow_wide && !tc, &p.tt, &p.tp);
+  choose_tt(t, allow_wide && (!tc || kloop), &p.tt, &p.tp);
   p.t_chunks = p.tp / p.tt;
   if (tc) {
     p.br = kloop ? tck::kRowsPerCtaL : tc::kRowsPerCta;
@@ -267,8 +268,9 @@ static Layout make_layout(void* ws, bool dmmv, bool has_v, int dtype, int kernel
   L.status = c.take(256);
   L.sigma = c.take(std::max<int64_t>(d, 1) * es);
   const bool kloop = L.tc && tck::supports_d(d);
-  L.s1 = plan_sweep(L.tc, dtype, n, m, t, !L.tc, kloop);  // rows = X1, reduction over X2
-  L.s2 = plan_sweep(L.tc, dtype, m, n, t, !L.tc, kloop);  // rows = X2, reduction over X1 (fdmmv only)
+  const bool wide_ok = !L.tc || kloop;
+  L.s1 = plan_sweep(L.tc, dtype, n, m, t, wide_ok, kloop);  // rows = X1, reduction over X2
+  L.s2 = plan_sweep(L.tc, dtype, m, n, t, wide_ok, kloop);  // rows = X2, reduction over X1 (fdmmv only)
   const int64_t n_pad = L.s1.r_pad, m_pad = L.s1.s_pad;
   const bool first = !dmmv || has_v;  // is the first sweep executed?
   if (L.tc) {
@@ -279,8 +281,8 @@ static Layout make_layout(void* ws, bool dmmv, bool has_v, int dtype, int kernel
       L.x2.img_a = c.take(m_pad * kp * 2);
       L.x1.img_b = c.take(n_pad * kp * 2);
     }
-    L.f1 = plan_sweep(false, dtype, n, m, t);
-    L.f2 = plan_sweep(false, dtype, m, n, t);
+    L.f1 = plan_sweep(false, dtype, n, m, t, wide_ok);
+    L.f2 = plan_sweep(false, dtype, m, n, t, wide_ok);
   }
   {
     const int ld = ld_for(dtype, d);

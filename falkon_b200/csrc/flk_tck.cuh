@@ -30,6 +30,7 @@ constexpr int kRowsPerCtaL = kRowBlocksL * kTileRows;  // 256
 constexpr int kMaxDL = 1024;
 constexpr int kSlabBytes = kTileRows * kSlabK * 2;      // 8 KB: one 128-row slab of an operand image
 constexpr int kStages = 8;
+constexpr int kWideTT = 32;                             // vector columns per pass of the many-column variant
 constexpr int kMaxResidentSlabs = 8;                    // both A blocks stay in shared memory up to this many slabs
 constexpr int kColSplitL = 2;                           // epilogue warps per (row block, lane quarter): each takes 64 columns of a tile
 constexpr int kEpiWarpsL = 4 * kRowBlocksL * kColSplitL;
@@ -170,16 +171,47 @@ struct SweepArgsL {
 
 // ARES: the two A blocks of the CTA (256 rows x nslab slabs, at most 128 KB) are loaded once and stay resident;
 // a ring stage then carries the B slab only (8 KB instead of 24 KB), which cuts the L2 traffic three-fold.
+// With 32 vector columns per pass the vector tiles are 16 KB each: two of them and a six-stage operand ring.
+template <int TT>
+struct RingCfg {
+  static constexpr int S = TT == kWideTT ? 6 : kStages;
+  static constexpr int VS = TT == kWideTT ? 2 : kVecStages;
+};
+
 template <int TT, bool ARES>
 constexpr size_t tck_smem_bytes() {
   return 1024 + (ARES ? (size_t)kRowBlocksL * kMaxResidentSlabs * kSlabBytes : 0) +
-         (size_t)kStages * (ARES ? 1 : 3) * kSlabBytes + (size_t)kVecStages * kColsPerTile * TT * 4 + 512 +
+         (size_t)RingCfg<TT>::S * (ARES ? 1 : 3) * kSlabBytes + (size_t)RingCfg<TT>::VS * kColsPerTile * TT * 4 + 512 +
          (size_t)kRowsPerCtaL * TT * 4 /* partial sums of the second column half */;
+}
+
+// Kernel function + contraction with 32 vector columns for 32 accumulator columns held in registers: per kernel
+// value one exponential, then 16 packed multiply-adds against the 32 vector entries of that column (read as
+// eight 16-byte broadcasts from shared memory).
+template <int KT, int C0 = 0>
+__device__ __forceinline__ void epilogue_wide32(const uint32_t (&r)[32], const float* vsm, uint64_t (&osum)[16]) {
+  if constexpr (C0 < 32) {
+    float k0, k1;
+    eval_pair<KT, poly_pair<KT>(C0 / 2)>(r[C0], r[C0 + 1], k0, k1);
+    const float kv[2] = {k0, k1};
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      const uint64_t kk = pack2(kv[c], kv[c]);
+      const ulonglong2* v = reinterpret_cast<const ulonglong2*>(vsm + (C0 + c) * kWideTT);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const ulonglong2 vv = v[i];
+        osum[2 * i] = fma2(kk, vv.x, osum[2 * i]);
+        osum[2 * i + 1] = fma2(kk, vv.y, osum[2 * i + 1]);
+      }
+    }
+    epilogue_wide32<KT, C0 + 2>(r, vsm, osum);
+  }
 }
 
 template <int KT, int TT, bool ARES>
 __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL p) {
-  constexpr int S = kStages, VS = kVecStages;
+  constexpr int S = RingCfg<TT>::S, VS = RingCfg<TT>::VS;
   constexpr int kStageBytes = (ARES ? 1 : 3) * kSlabBytes;  // [A block 0 | A block 1 |] B tile
   constexpr int kAResBytes = ARES ? kRowBlocksL * kMaxResidentSlabs * kSlabBytes : 0;
   extern __shared__ unsigned char tck_smem_raw[];
@@ -349,8 +381,10 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
     const int q = warp & 3;
     const int rb = (warp >> 2) & 1;
     const int half = warp >> 3;  // columns half * 64 .. + 63 of every tile
-    uint64_t osum[2] = {0ull, 0ull};
-    uint32_t ra[32], rc[32];
+    constexpr int NSUM = TT == kWideTT ? 16 : 2;
+    uint64_t osum[NSUM];
+#pragma unroll
+    for (int i = 0; i < NSUM; ++i) osum[i] = 0ull;
     bool epi_ok = true;
     for (int j = 0; j < ntiles; ++j) {
       const int vstage = j % VS, buf = j & 1;
@@ -366,33 +400,54 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) +
                              (uint32_t)((rb * 2 + buf) * kColsPerTile + half * 64);
       const float* vsm = vs + (vstage * kColsPerTile + half * 64) * TT;
-      tmem_ld32(taddr, ra);
-      tmem_ld_wait_on(ra);
-      tmem_ld32(taddr + 32, rc, ra);
-      tmem_ld_wait_on(rc);
-      // this warp's 64 columns are in registers: hand the accumulator back before evaluating them
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(bar_t_empty + rb * 2 + buf));
-      epilogue_32<KT, TT>(ra, vsm, osum);
-      epilogue_32<KT, TT>(rc, vsm + 32 * TT, osum);
+      if constexpr (TT == kWideTT) {
+        // 32 running sums per thread leave room for one 32-column piece at a time
+        uint32_t ra[32];
+        tmem_ld32(taddr, ra);
+        tmem_ld_wait_on(ra);
+        epilogue_wide32<KT>(ra, vsm, osum);
+        tmem_ld32(taddr + 32, ra);
+        tmem_ld_wait_on(ra);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(bar_t_empty + rb * 2 + buf));
+        epilogue_wide32<KT>(ra, vsm + 32 * TT, osum);
+      } else {
+        uint32_t ra[32], rc[32];
+        tmem_ld32(taddr, ra);
+        tmem_ld_wait_on(ra);
+        tmem_ld32(taddr + 32, rc, ra);
+        tmem_ld_wait_on(rc);
+        // this warp's 64 columns are in registers: hand the accumulator back before evaluating them
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(bar_t_empty + rb * 2 + buf));
+        epilogue_32<KT, TT>(ra, vsm, osum);
+        epilogue_32<KT, TT>(rc, vsm + 32 * TT, osum);
+      }
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(bar_v_empty + vstage));
     }
     // per-thread sums of this column half
-    float a0, a1, b0, b1, o[4];
-    unpack2(osum[0], a0, a1);
-    unpack2(osum[1], b0, b1);
-    if constexpr (TT == 1) {
-      o[0] = (a0 + a1) + (b0 + b1);
-    } else if constexpr (TT == 2) {
-      o[0] = a0 + b0;
-      o[1] = a1 + b1;
+    float o[TT];
+    if constexpr (TT == kWideTT) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) unpack2(osum[i], o[2 * i], o[2 * i + 1]);
     } else {
-      o[0] = a0;
-      o[1] = a1;
-      o[2] = b0;
-      o[3] = b1;
+      float a0, a1, b0, b1;
+      unpack2(osum[0], a0, a1);
+      unpack2(osum[1], b0, b1);
+      if constexpr (TT == 1) {
+        o[0] = (a0 + a1) + (b0 + b1);
+      } else if constexpr (TT == 2) {
+        o[0] = a0 + b0;
+        o[1] = a1 + b1;
+      } else {
+        o[0] = a0;
+        o[1] = a1;
+        o[2] = b0;
+        o[3] = b1;
+      }
     }
     const int rloc = rb * kTileRows + q * 32 + lane;
     if (half == 1) {
@@ -459,6 +514,8 @@ int launch_tt(const SweepArgsL& args, int tt, int n_chunks, int t_chunks, cudaSt
                         : launch_inst<KT, 2, false>(args, n_chunks, t_chunks, stream);
     case 4: return ares ? launch_inst<KT, 4, true>(args, n_chunks, t_chunks, stream)
                         : launch_inst<KT, 4, false>(args, n_chunks, t_chunks, stream);
+    case kWideTT:  // 16 KB vector tiles and 32 KB of partial sums leave no room for resident A blocks
+      return launch_inst<KT, kWideTT, false>(args, n_chunks, t_chunks, stream);
   }
   return fail(FLK_ERR_BAD_ARG, "internal: unsupported TT=%d", tt);
 }
