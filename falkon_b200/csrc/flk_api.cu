@@ -106,19 +106,36 @@ struct SweepPlan {
   int64_t raw_elems() const { return (int64_t)max_chunks() * r_pad * tp; }
 };
 
-// Vector columns per pass: 1, 2 or 4 for the kernels that keep the whole contraction in registers;
-// 32 (the wide kernel, flk_wide.cuh) when the SIMT path is the primary one and there are more than four.
-static void choose_tt(int64_t t, bool allow_wide, int* tt, int* tp) {
+// Vector columns per pass: 1, 2 or 4 for the epilogues that keep two packed pairs of running sums, or 32
+// (`use_wide`; one kernel evaluation serves all of them, but the contraction then costs 32 columns of work
+// whatever t is).
+static void choose_tt(int64_t t, bool use_wide, int* tt, int* tp) {
   if (t <= 1) *tt = 1;
   else if (t == 2) *tt = 2;
-  else if (t <= 4 || !allow_wide) *tt = 4;
+  else if (t <= 4 || !use_wide) *tt = 4;
   else *tt = kWideT;
   *tp = (int)round_up(std::max<int64_t>(t, 1), *tt);
 }
 
-// `allow_wide`: the plan may group 32 vector columns per pass (SIMT wide / DMMA kernels, K-loop tensor-core kernel;
-// never the resident tensor-core kernel).  The SIMT alternative of a tensor-core plan shares its vector buffers
-// and therefore must be planned with the same column grouping.
+// Is one pass over groups of 32 columns cheaper than passes over groups of 4?  Relative costs per kernel value
+// and pass, from measurements on B200: tensor-core paths pay max(epilogue, exponent GEMM ~ 0.0065 d) for 4
+// columns and about 1.9 + 0.003 d for 32 (the 32-column epilogue is bound by its multiply-adds and shared-memory
+// reads); the SIMT / DMMA paths pay d + 4 + E against d + 32 + E multiply-adds (E = the exponential: about 4 in
+// fp32, 40 in software fp64).
+static bool wide_pays_off(bool tc, int dtype, int kernel, int64_t d, int64_t t) {
+  if (t <= 4) return false;
+  const double passes4 = (double)ceil_div(t, 4), passes32 = (double)ceil_div(t, kWideT);
+  if (tc) {
+    const double epi4 = kernel == FLK_GAUSSIAN ? 0.33 : 0.6;  // the other kernel functions carry a square root
+    const double cost4 = std::max(epi4, 0.0065 * (double)d), cost32 = 1.9 + 0.003 * (double)d;
+    return passes32 * cost32 < passes4 * cost4;
+  }
+  const double e = dtype == FLK_F64 ? 40.0 : 4.0;
+  return passes32 * ((double)d + 32.0 + e) < passes4 * ((double)d + 4.0 + e);
+}
+
+// `allow_wide`: the plan may group 32 vector columns per pass.  The SIMT alternative of a tensor-core plan shares
+// its vector buffers and therefore must be planned with the same column grouping.
 static SweepPlan plan_sweep(bool tc, int dtype, int64_t r, int64_t s, int64_t t, bool allow_wide = false,
                             bool kloop = false) {
   SweepPlan p;
@@ -128,7 +145,7 @@ static SweepPlan plan_sweep(bool tc, int dtype, int64_t r, int64_t s, int64_t t,
   p.s = s;
   p.r_pad = round_up(std::max<int64_t>(r, 1), kRowPad);
   p.s_pad = round_up(std::max<int64_t>(s, 1), kRowPad);
-  choose_tt(t, allow_wide && (!tc || kloop), &p.tt, &p.tp);
+  choose_tt(t, allow_wide, &p.tt, &p.tp);
   p.t_chunks = p.tp / p.tt;
   if (tc) {
     p.br = kloop ? tck::kRowsPerCtaL : tc::kRowsPerCta;
@@ -268,7 +285,7 @@ static Layout make_layout(void* ws, bool dmmv, bool has_v, int dtype, int kernel
   L.status = c.take(256);
   L.sigma = c.take(std::max<int64_t>(d, 1) * es);
   const bool kloop = L.tc && tck::supports_d(d);
-  const bool wide_ok = !L.tc || kloop;
+  const bool wide_ok = wide_pays_off(L.tc, dtype, kernel, d, t);  // every path has a 32-columns-per-pass kernel
   L.s1 = plan_sweep(L.tc, dtype, n, m, t, wide_ok, kloop);  // rows = X1, reduction over X2
   L.s2 = plan_sweep(L.tc, dtype, m, n, t, wide_ok, kloop);  // rows = X2, reduction over X1 (fdmmv only)
   const int64_t n_pad = L.s1.r_pad, m_pad = L.s1.s_pad;

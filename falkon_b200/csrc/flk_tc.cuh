@@ -224,6 +224,23 @@ __device__ __forceinline__ void tmem_ld_wait_on(uint32_t (&r)[32], uint64_t (&ac
 __device__ __forceinline__ void tmem_ld_wait_on(uint32_t (&r)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" : FLK_R32_INOUT(r) : : "memory");
 }
+// 16-column variants for the many-column epilogue (its 32 running sums leave room for 16 accumulator columns).
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait_on(uint32_t (&r)[16]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+               :
+               : "memory");
+}
 
 // K-major, 64-byte swizzle shared-memory matrix descriptor (8-row groups 512 bytes apart).
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
@@ -493,11 +510,20 @@ struct TcCfg {
   static constexpr int STAGES = NSLAB == 3 ? 4 : (NSLAB == 2 ? 6 : 12);
 };
 
+constexpr int kWideTT = 32;  // vector columns per pass of the many-column epilogue
+
+// Ring depths: with 32 vector columns per pass a vector tile is 16 KB, so two of them and one B stage fewer.
+template <int NSLAB, int TT>
+struct RingOf {
+  static constexpr int S = TT == kWideTT ? (NSLAB == 3 ? 3 : (NSLAB == 2 ? 5 : 10)) : TcCfg<NSLAB>::STAGES;
+  static constexpr int VS = TT == kWideTT ? 2 : kVecStages;
+};
+
 template <int NSLAB, int TT>
 constexpr size_t tc_smem_bytes() {
   using C = TcCfg<NSLAB>;
-  return 1024 /* alignment slack */ + (size_t)C::A_BYTES + (size_t)C::STAGES * C::TILE_BYTES +
-         (size_t)kVecStages * kColsPerTile * TT * 4 + 512 /* barriers + tmem pointer */;
+  return 1024 /* alignment slack */ + (size_t)C::A_BYTES + (size_t)RingOf<NSLAB, TT>::S * C::TILE_BYTES +
+         (size_t)RingOf<NSLAB, TT>::VS * kColsPerTile * TT * 4 + 512 /* barriers + tmem pointer */;
 }
 
 // error codes written to the status word: role * 16 + which wait
@@ -553,14 +579,39 @@ __device__ __forceinline__ void epilogue_32(const uint32_t (&r)[32], const float
   }
 }
 
+// Many-column epilogue: kernel function + contraction with 32 vector columns for 16 accumulator columns held in
+// registers: per kernel value one exponential, then 16 packed multiply-adds against the 32 vector entries of that
+// column (eight 16-byte broadcasts from shared memory).  PR0 = index of the first column pair within its 32-column
+// piece (selects which pairs take the FMA-pipe exponential).
+template <int KT, int PR0, int C0 = 0>
+__device__ __forceinline__ void epilogue_wide16(const uint32_t (&r)[16], const float* vsm, uint64_t (&osum)[16]) {
+  if constexpr (C0 < 16) {
+    float k0, k1;
+    eval_pair<KT, poly_pair<KT>(PR0 + C0 / 2)>(r[C0], r[C0 + 1], k0, k1);
+    const float kv[2] = {k0, k1};
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      const uint64_t kk = pack2(kv[c], kv[c]);
+      const ulonglong2* v = reinterpret_cast<const ulonglong2*>(vsm + (C0 + c) * kWideTT);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const ulonglong2 vv = v[i];
+        osum[2 * i] = fma2(kk, vv.x, osum[2 * i]);
+        osum[2 * i + 1] = fma2(kk, vv.y, osum[2 * i + 1]);
+      }
+    }
+    epilogue_wide16<KT, PR0, C0 + 2>(r, vsm, osum);
+  }
+}
+
 // Epilogue warp w: TMEM lane quarter q = w % 4 (hardware rule: a warp may only touch lanes
 // 32 (w % 4) .. +31; warps with the same w % 4 also share an SM sub-partition, so each row block
 // has one warp on every sub-partition), row block rb = w / 4.
 template <int KT, int NSLAB, int TT>
 __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) {
   using C = TcCfg<NSLAB>;
-  constexpr int S = C::STAGES;
-  constexpr int VS = kVecStages;
+  constexpr int S = RingOf<NSLAB, TT>::S;
+  constexpr int VS = RingOf<NSLAB, TT>::VS;
   extern __shared__ unsigned char tc_smem_raw[];
   // the swizzle atoms want a 512-byte aligned base; 1024 keeps every tile image on a round address
   const uint32_t raw_addr = smem_u32(tc_smem_raw);
@@ -711,9 +762,11 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
     // ------------------------------ epilogue warps ------------------------------
     const int q = warp & 3;    // TMEM lane quarter this warp may access
     const int rb = warp >> 2;  // row block
-    uint64_t osum[2] = {0ull, 0ull};  // two packed pairs of running sums (see epilogue_32)
+    constexpr int NSUM = TT == kWideTT ? 16 : 2;  // packed pairs of running sums (see epilogue_32 / epilogue_wide16)
+    uint64_t osum[NSUM];
+#pragma unroll
+    for (int i = 0; i < NSUM; ++i) osum[i] = 0ull;
     const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(rb * kColsPerTile);
-    uint32_t ra[32], rc[32];
     bool epi_ok = true;
 
     for (int j = 0; j < ntiles; ++j) {
@@ -728,44 +781,74 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
       }
       tc_fence_after();
       const float* vsm = vs + vstage * kColsPerTile * TT;
-      // pieces 0 and 2 travel in `ra`, 1 and 3 in `rc`; the next piece loads while this one is evaluated
-      tmem_ld32(taddr, ra);
-      tmem_ld_wait_on(ra);
-      tmem_ld32(taddr + 32, rc, ra);
-      epilogue_32<KT, TT>(ra, vsm, osum);
-      tmem_ld_wait_on(rc, osum);
-      tmem_ld32(taddr + 64, ra, rc);
-      epilogue_32<KT, TT>(rc, vsm + 32 * TT, osum);
-      tmem_ld_wait_on(ra, osum);
-      tmem_ld32(taddr + 96, rc, ra);
-      tmem_ld_wait_on(rc);
-      // The second half of the accumulator is in registers: hand the accumulator back now, so the
-      // MMA of the next tile (and the barrier round trips either side of it) runs under the
-      // evaluation of these two pieces.
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(bar_t_empty + rb));
-      epilogue_32<KT, TT>(ra, vsm + 64 * TT, osum);
-      epilogue_32<KT, TT>(rc, vsm + 96 * TT, osum);
+      if constexpr (TT == kWideTT) {
+        // eight 16-column pieces; the accumulator goes back to its issuer once the last one is in registers
+        uint32_t rw[16];
+#pragma unroll
+        for (int pc = 0; pc < 8; ++pc) {
+          tmem_ld16(taddr + pc * 16, rw);
+          tmem_ld_wait_on(rw);
+          if (pc == 7) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(bar_t_empty + rb));
+          }
+          if (pc & 1)
+            epilogue_wide16<KT, 8>(rw, vsm + pc * 16 * TT, osum);
+          else
+            epilogue_wide16<KT, 0>(rw, vsm + pc * 16 * TT, osum);
+        }
+      } else {
+        uint32_t ra[32], rc[32];
+        // pieces 0 and 2 travel in `ra`, 1 and 3 in `rc`; the next piece loads while this one is evaluated
+        tmem_ld32(taddr, ra);
+        tmem_ld_wait_on(ra);
+        tmem_ld32(taddr + 32, rc, ra);
+        epilogue_32<KT, TT>(ra, vsm, osum);
+        tmem_ld_wait_on(rc, osum);
+        tmem_ld32(taddr + 64, ra, rc);
+        epilogue_32<KT, TT>(rc, vsm + 32 * TT, osum);
+        tmem_ld_wait_on(ra, osum);
+        tmem_ld32(taddr + 96, rc, ra);
+        tmem_ld_wait_on(rc);
+        // The second half of the accumulator is in registers: hand the accumulator back now, so the
+        // MMA of the next tile (and the barrier round trips either side of it) runs under the
+        // evaluation of these two pieces.
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(bar_t_empty + rb));
+        epilogue_32<KT, TT>(ra, vsm + 64 * TT, osum);
+        epilogue_32<KT, TT>(rc, vsm + 96 * TT, osum);
+      }
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(bar_v_empty + vstage));
     }
     if (epi_ok) {
       const int64_t row = (int64_t)row_tile * kRowsPerCta + rb * kTileRows + q * 32 + lane;
       float* dst = p.raw + ((int64_t)chunk * p.r_pad + row) * p.tp + tchunk * TT;
-      float a0, a1, b0, b1;
-      unpack2(osum[0], a0, a1);
-      unpack2(osum[1], b0, b1);
-      if constexpr (TT == 1) {
-        dst[0] = (a0 + a1) + (b0 + b1);
-      } else if constexpr (TT == 2) {
-        dst[0] = a0 + b0;
-        dst[1] = a1 + b1;
+      if constexpr (TT == kWideTT) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float lo, hi;
+          unpack2(osum[i], lo, hi);
+          dst[2 * i] = lo;
+          dst[2 * i + 1] = hi;
+        }
       } else {
-        dst[0] = a0;
-        dst[1] = a1;
-        dst[2] = b0;
-        dst[3] = b1;
+        float a0, a1, b0, b1;
+        unpack2(osum[0], a0, a1);
+        unpack2(osum[1], b0, b1);
+        if constexpr (TT == 1) {
+          dst[0] = (a0 + a1) + (b0 + b1);
+        } else if constexpr (TT == 2) {
+          dst[0] = a0 + b0;
+          dst[1] = a1 + b1;
+        } else {
+          dst[0] = a0;
+          dst[1] = a1;
+          dst[2] = b0;
+          dst[3] = b1;
+        }
       }
     }
   }
@@ -821,6 +904,7 @@ int launch_sweep_tt(const SweepArgs& args, int tt, int grid_x, int t_chunks, cud
     case 1: return launch_sweep_inst<KT, NSLAB, 1>(args, grid_x, t_chunks, stream);
     case 2: return launch_sweep_inst<KT, NSLAB, 2>(args, grid_x, t_chunks, stream);
     case 4: return launch_sweep_inst<KT, NSLAB, 4>(args, grid_x, t_chunks, stream);
+    case kWideTT: return launch_sweep_inst<KT, NSLAB, kWideTT>(args, grid_x, t_chunks, stream);
   }
   return fail(FLK_ERR_BAD_ARG, "internal: unsupported TT=%d", tt);
 }

@@ -30,7 +30,6 @@ constexpr int kRowsPerCtaL = kRowBlocksL * kTileRows;  // 256
 constexpr int kMaxDL = 1024;
 constexpr int kSlabBytes = kTileRows * kSlabK * 2;      // 8 KB: one 128-row slab of an operand image
 constexpr int kStages = 8;
-constexpr int kWideTT = 32;                             // vector columns per pass of the many-column variant
 constexpr int kMaxResidentSlabs = 8;                    // both A blocks stay in shared memory up to this many slabs
 constexpr int kColSplitL = 2;                           // epilogue warps per (row block, lane quarter): each takes 64 columns of a tile
 constexpr int kEpiWarpsL = 4 * kRowBlocksL * kColSplitL;
