@@ -125,6 +125,8 @@ SHAPES = [
     (300, 70, 31, 5),
     (513, 300, 9, 4),
     (1000, 17, 3, 33),
+    (300, 700, 12, 70),   # fp32: resident tensor-core kernel with 32 vector columns per pass
+    (400, 300, 100, 40),  # fp32: K-loop tensor-core kernel with 32 vector columns per pass
     (70, 1000, 64, 1),
     (260, 130, 130, 2),
 ]
