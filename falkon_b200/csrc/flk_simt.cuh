@@ -1,7 +1,8 @@
 // SIMT (FP32 / FP64 FMA-pipe) kernel-vector product:  raw[chunk][i][t] = sum_{j in chunk} k(a_i, b_j) vec[j][t]
 //
-// Serves every dtype / feature count / kernel function; the tensor-core kernel (flk_tc.cuh)
-// takes over for fp32 with small feature counts.  The (rows x columns) kernel block lives only
+// Serves every dtype / feature count / kernel function; the tensor-core kernels (flk_tc.cuh,
+// flk_tck.cuh) take over for fp32 with up to 1024 features, flk_wide.cuh / flk_dmma.cuh for many
+// vector columns.  The (rows x columns) kernel block lives only
 // in registers: a CTA owns a tile of BR rows, keeps it in shared memory, streams tiles of BC
 // columns through a cp.async double buffer, forms the BR x BC dot products with an 8 x TC
 // register micro-tile per thread, applies  d2 = max(|a|^2 + |b|^2 - 2 a.b, 1e-20)  and the

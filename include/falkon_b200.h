@@ -68,7 +68,8 @@ const char* flk_status_name(int status);
 /* FLK_OK when the current CUDA device can run this library (compute capability 10.x). */
 int flk_check_device(void);
 
-/* 1 when the tensor-core (tcgen05) kernel serves this problem, 0 when the SIMT kernel does. */
+/* 1 when a tcgen05 tensor-core kernel serves this problem (fp32 data, 1 <= d <= 1024), 0 when the SIMT / fp64
+ * kernels do. */
 int flk_uses_tensor_cores(int dtype, int kernel, int64_t d, int64_t t, int flags);
 
 /*
