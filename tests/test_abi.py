@@ -103,6 +103,24 @@ def test_kernel_matrix_entry_point_checks_arguments(lib):
     assert st == _lib.FLK_ERR_BAD_ARG  # unknown kernel id
 
 
+def test_plain_c_client(lib, tmp_path):
+    """The boundary is usable from C with nothing but the header and the shared library."""
+    import shutil
+    import subprocess
+
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    libdir = os.path.dirname(_lib.LIB_PATH)
+    exe = str(tmp_path / "abi_client")
+    cmd = [gcc, "-std=c99", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"),
+           os.path.join(ROOT, "tests", "abi_client.c"), "-o", exe, "-L", libdir, "-lfalkon_b200",
+           "-Wl,-rpath," + libdir]
+    subprocess.run(cmd, check=True, capture_output=True, text=True)
+    res = subprocess.run([exe], capture_output=True, text=True)
+    assert res.returncode == 0 and res.stdout.startswith("ok"), res.stdout + res.stderr
+
+
 def test_status_maps_to_reference_exception_types(lib):
     lib.flk_fmmv_workspace_bytes(0, 0, -1, 10, 2, 1, 0)
     with pytest.raises(ValueError):
