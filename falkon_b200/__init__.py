@@ -10,7 +10,7 @@ use; there is no CPU fallback.
 """
 from .options import FalkonOptions  # noqa: F401
 from . import center_selection, kernels, mmv_ops, models, optim, preconditioner  # noqa: F401
-from .models import Falkon  # noqa: F401
+from .models import Falkon, InCoreFalkon  # noqa: F401
 
 __version__ = "0.2.0"
-__all__ = ("FalkonOptions", "Falkon", "kernels", "mmv_ops", "optim", "preconditioner", "models", "center_selection")
+__all__ = ("FalkonOptions", "Falkon", "InCoreFalkon", "kernels", "mmv_ops", "optim", "preconditioner", "models", "center_selection")

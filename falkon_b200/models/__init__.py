@@ -1,3 +1,3 @@
-from .falkon import Falkon
+from .falkon import Falkon, InCoreFalkon
 
-__all__ = ("Falkon",)
+__all__ = ("Falkon", "InCoreFalkon")

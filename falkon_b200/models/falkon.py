@@ -23,7 +23,7 @@ from ..optim import FalkonConjugateGradient
 from ..options import FalkonOptions
 from ..preconditioner import FalkonPreconditioner
 
-__all__ = ("Falkon",)
+__all__ = ("Falkon", "InCoreFalkon")
 
 
 class Falkon:
@@ -226,3 +226,27 @@ class Falkon:
     def __repr__(self):
         return (f"Falkon(kernel={self.kernel}, penalty={self.penalty}, M={self.M}, maxiter={self.maxiter}, "
                 f"seed={self.seed})")
+
+
+class InCoreFalkon(Falkon):
+    """``Falkon`` for data that already lives on the GPU (falkon/models/incore_falkon.py:22-270).
+
+    On a B200 the plain ``Falkon`` keeps everything on the device as well; this class only adds the
+    reference's input contract: all tensors given to ``fit`` must be CUDA tensors on one device
+    (``ValueError`` otherwise), and ``predict`` expects its input on the model's device.
+    """
+
+    @staticmethod
+    def _same_cuda_device(*tensors) -> bool:
+        devs = {t.device for t in tensors if t is not None}
+        return len(devs) == 1 and next(iter(devs)).type == "cuda"
+
+    def fit(self, X, Y, Xts=None, Yts=None, warm_start=None):
+        if not self._same_cuda_device(X, Y, Xts, Yts):
+            raise ValueError("All tensors for fitting InCoreFalkon must be CUDA tensors, located on the same GPU.")
+        return super().fit(X, Y, Xts, Yts, warm_start)
+
+    def predict(self, X):
+        if self.alpha_ is not None and X.device != self.alpha_.device:
+            raise ValueError(f"X must be on device {self.alpha_.device}")
+        return super().predict(X)

@@ -119,3 +119,27 @@ def test_output_allocation_rules():
     assert o.stride() == (1, 6) and o.dtype == torch.float64
     given = torch.empty(6, 2)
     assert create_output_mat(given, [cpu], (6, 2), torch.float32, "cuda", Xc) is given
+
+
+def test_incore_falkon_requires_cuda_tensors():
+    from falkon_b200 import InCoreFalkon
+
+    model = InCoreFalkon(kernel=GaussianKernel(1.0), penalty=1e-3, M=5)
+    with pytest.raises(ValueError, match="CUDA tensors"):
+        model.fit(torch.randn(20, 3), torch.randn(20, 1))
+
+
+def test_falkon_constructor_validation():
+    from falkon_b200 import Falkon, FalkonOptions
+
+    with pytest.raises(ValueError, match="M must be specified"):
+        Falkon(kernel=GaussianKernel(1.0), penalty=1e-3, M=None)
+    with pytest.raises(ValueError, match="not valid"):
+        Falkon(kernel=GaussianKernel(1.0), penalty=1e-3, M=5, center_selection="kmeans")
+    with pytest.raises(RuntimeError, match="no CPU implementation"):
+        Falkon(kernel=GaussianKernel(1.0), penalty=1e-3, M=5, options=FalkonOptions(use_cpu=True))
+    model = Falkon(kernel=GaussianKernel(1.0), penalty=1e-3, M=5)
+    with pytest.raises(RuntimeError, match="has not been trained"):
+        model.predict(torch.randn(4, 3))
+    with pytest.raises(ValueError, match="same number of samples"):
+        model.fit(torch.randn(20, 3), torch.randn(19, 1))
