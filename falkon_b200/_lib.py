@@ -84,6 +84,7 @@ _SIGNATURES = {
     "flk_fmmv_static": (_int, [_int, _int] + _MAT + _MAT + [_i64, _vp, _i64, _i64, _i64, _vp, _i64, _i64, ctypes.c_double, _int, _vp]),
     "flk_fmm_workspace_bytes": (_i64, [_int, _i64, _i64, _i64, _int]),
     # dtype, kernel, X1(4), X2(4), d, out ptr + strides(3), sigma, len, ws, bytes, flags, stream
+    "flk_kgrad": (_int, [_int, _int] + _MAT + _MAT + [_i64, _vp, _i64, _i64, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _dp, _i64, _vp, _i64, _int, _vp]),
     "flk_fmm": (_int, [_int, _int] + _MAT + _MAT + [_i64, _vp, _i64, _i64, _dp, _i64, _vp, _i64, _int, _vp]),
     "flk_tc_status": (_int, [_vp, _vp, ctypes.POINTER(_int)]),
     "flk_range_flag": (_int, [_vp, _vp, ctypes.POINTER(_int)]),
@@ -256,6 +257,33 @@ def call_fmm(kernel_id, sigma, X1, X2, out, flags=0):
         stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
         status = lib.flk_fmm(dt, kernel_id, *_mat_args(X1), *_mat_args(X2), d, *_mat_args(out, with_rows=False),
                              sig_ptr, sig_len, ctypes.c_void_p(ws.data_ptr()), ws.numel(), flags, stream)
+    del keep
+    raise_for_status(status)
+    return out
+
+
+def call_kgrad(kernel_id, sigma, X1, X2, G, v, out, flags=0):
+    """out[n, m] = 2 k'(D2_ij) s_ij through the C ABI: s = G v^T (G n x t, v m x t) or, with v None, s = G (n x m)."""
+    lib = load()
+    dt = dtype_code(X1.dtype)
+    n, d = X1.shape
+    m = X2.shape[0]
+    dev = X1.device
+    need = lib.flk_fmm_workspace_bytes(dt, n, m, d, flags)
+    if need < 0:
+        raise_for_status(int(need))
+    keep, sig_ptr, sig_len = _sigma_args(sigma)
+    with torch.cuda.device(dev):
+        ws = workspace(dev, need)
+        stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        if v is None:
+            v_args = (None, 0, 0, 0)
+        else:
+            v_args = (ctypes.c_void_p(v.data_ptr()), v.shape[1], v.stride(0), v.stride(1))
+        status = lib.flk_kgrad(dt, kernel_id, *_mat_args(X1), *_mat_args(X2), d,
+                               ctypes.c_void_p(G.data_ptr()), G.stride(0), G.stride(1), *v_args,
+                               *_mat_args(out, with_rows=False), sig_ptr, sig_len,
+                               ctypes.c_void_p(ws.data_ptr()), ws.numel(), flags, stream)
     del keep
     raise_for_status(status)
     return out

@@ -6,6 +6,7 @@
 #include "flk_common.cuh"
 #include "flk_dmma.cuh"
 #include "flk_fmm.cuh"
+#include "flk_grad.cuh"
 #include "flk_prep.cuh"
 #include "flk_simt.cuh"
 #include "flk_tc.cuh"
@@ -628,6 +629,30 @@ static int fmm_impl(int math_dtype, int kernel, const Mat& X1, const Mat& X2, vo
   return FLK_OK;
 }
 
+// Backward-pass pair weights (flk_grad.cuh) on the same prepared operands as fmm.
+template <typename T, typename TIO>
+static int kgrad_impl(int math_dtype, int kernel, const Mat& X1, const Mat& X2, const Mat& G, const Mat& V, int64_t t,
+                      void* out, int64_t out_rs, int64_t out_cs, const double* sigma, int64_t sigma_len, void* ws,
+                      int64_t ws_bytes, cudaStream_t stream) {
+  const int64_t n = X1.rows, m = X2.rows, d = X1.cols;
+  FmmLayout L = make_fmm_layout(ws, math_dtype, n, m, d);
+  FLK_TRY(check_workspace(ws, ws_bytes, L.total));
+  if (n == 0 || m == 0) return FLK_OK;
+  T sig_scalar;
+  const T* sig_dev;
+  FLK_TRY(upload_sigma<T>(sigma, sigma_len, L.sigma, &sig_scalar, &sig_dev, stream));
+  const Gate always{nullptr, 0};
+  FLK_TRY((run_prep_rows<T, TIO>(X1, sig_dev, sig_scalar, (int)sigma_len, L.xs1, L.ld, L.n_pad, L.n1, always, stream)));
+  FLK_TRY((run_prep_rows<T, TIO>(X2, sig_dev, sig_scalar, (int)sigma_len, L.xs2, L.ld, L.m_pad, L.n2, always, stream)));
+  const bool factors = t > 0;
+  FLK_TRY((launch_kgrad<T, TIO>(kernel, (const T*)L.xs1, (const T*)L.n1, (const T*)L.xs2, (const T*)L.n2, L.ld,
+                                factors ? (const TIO*)G.ptr : nullptr, G.rs, G.cs, (const TIO*)V.ptr, V.rs, V.cs,
+                                (int)t, factors ? nullptr : (const TIO*)G.ptr, G.rs, G.cs,
+                                reinterpret_cast<TIO*>(out), n, m, out_rs, out_cs, stream)));
+  count_launch();
+  return FLK_OK;
+}
+
 // ---------------------------------------------------------------------------------------------
 // Host-buffer variants: stage dense copies of the operands in the workspace, run, copy back.
 // ---------------------------------------------------------------------------------------------
@@ -1015,6 +1040,37 @@ int flk_fmm(int dtype, int kernel, const void* X1, int64_t n, int64_t x1_rs, int
                                    workspace_bytes, st);
   return fmm_impl<float, float>(FLK_F32, kernel, a, b, out, out_rs, out_cs, sigma_host, sigma_len, workspace,
                                 workspace_bytes, st);
+}
+
+int flk_kgrad(int dtype, int kernel, const void* X1, int64_t n, int64_t x1_rs, int64_t x1_cs, const void* X2,
+              int64_t m, int64_t x2_rs, int64_t x2_cs, int64_t d, const void* G, int64_t g_rs, int64_t g_cs,
+              const void* v, int64_t t, int64_t v_rs, int64_t v_cs, void* out, int64_t out_rs, int64_t out_cs,
+              const double* sigma_host, int64_t sigma_len, void* workspace, int64_t workspace_bytes, int flags,
+              void* stream) {
+  FLK_TRY(check_common(dtype, kernel, n, m, d, 0));
+  if (t < 0 || t > INT32_MAX) return fail(FLK_ERR_BAD_ARG, "t = %lld is out of range", (long long)t);
+  if (ceil_div(n, 64) > 65535)
+    return fail(FLK_ERR_UNSUPPORTED, "flk_kgrad: n = %lld exceeds 64 * 65535 rows per call; split the rows",
+                (long long)n);
+  if (t == 0 && v != nullptr)
+    return fail(FLK_ERR_BAD_ARG, "v must be NULL when t == 0 (G is then the dense n x m upstream gradient)");
+  Mat a{X1, n, d, x1_rs, x1_cs}, b{X2, m, d, x2_rs, x2_cs}, oo{out, n, m, out_rs, out_cs};
+  Mat gg{G, n, t > 0 ? t : m, g_rs, g_cs}, vv{v, m, t, v_rs, v_cs};
+  FLK_TRY(check_mat("X1", a, n == 0));
+  FLK_TRY(check_mat("X2", b, m == 0));
+  FLK_TRY(check_mat("G", gg, n == 0 || m == 0));
+  FLK_TRY(check_mat("v", vv, t == 0 || m == 0));
+  FLK_TRY(check_mat("out", oo, n == 0 || m == 0));
+  FLK_TRY(check_sigma(sigma_host, sigma_len, d));
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == FLK_F64)
+    return kgrad_impl<double, double>(FLK_F64, kernel, a, b, gg, vv, t, out, out_rs, out_cs, sigma_host, sigma_len,
+                                      workspace, workspace_bytes, st);
+  if (flags & FLK_FLAG_FP64_MATH)
+    return kgrad_impl<double, float>(FLK_F64, kernel, a, b, gg, vv, t, out, out_rs, out_cs, sigma_host, sigma_len,
+                                     workspace, workspace_bytes, st);
+  return kgrad_impl<float, float>(FLK_F32, kernel, a, b, gg, vv, t, out, out_rs, out_cs, sigma_host, sigma_len,
+                                  workspace, workspace_bytes, st);
 }
 
 int flk_set_timing(int enable) {

@@ -15,7 +15,7 @@ from .. import _lib
 from ..options import BaseOptions
 from .utils import check_contiguity, create_output_mat
 
-__all__ = ("fmmv", "fdmmv")
+__all__ = ("fmmv", "fdmmv", "KernelMmvFn")
 
 
 def _kernel_spec(kernel):
@@ -60,32 +60,9 @@ def _to_dev(t, dev):
     return None if t is None else (t if t.device == dev else t.to(dev, non_blocking=True))
 
 
-def fmmv(
-    X1: torch.Tensor,
-    X2: torch.Tensor,
-    v: torch.Tensor,
-    kernel,
-    out: Optional[torch.Tensor] = None,
-    opt: Optional[BaseOptions] = None,
-    kwargs_m1: Optional[Dict[str, torch.Tensor]] = None,
-    kwargs_m2: Optional[Dict[str, torch.Tensor]] = None,
-) -> torch.Tensor:
-    """``k(X1, X2) @ v`` -> (n x t).  Signature of falkon/mmv_ops/fmmv.py:960-969."""
-    if _is_sparse(X1, X2):
-        raise NotImplementedError("Sparse kernel-vector products are not implemented by falkon_b200.")
-    if kwargs_m1 or kwargs_m2:
-        raise NotImplementedError("Distance kernels take no per-row keyword tensors (kwargs_m1 / kwargs_m2).")
+def _fmmv_forward(X1, X2, v, kernel, out, opt):
+    """The product itself (no autograd bookkeeping); ``v`` is 2-D here."""
     kernel_id, sigma = _kernel_spec(kernel)
-    params = list(getattr(kernel, "diff_params", {}).values())
-    if torch.is_grad_enabled() and any(t.requires_grad for t in [X1, X2, v] + params):
-        raise NotImplementedError(
-            "falkon_b200 does not implement the backward pass of the kernel-vector product; "
-            "call it under torch.no_grad() / inference_mode() or detach the inputs."
-        )
-    check_contiguity((X1, "X1"), (X2, "X2"), (v, "v"), (out, "out"))
-    _require_cuda(opt, X1, X2, v)
-    if v.dim() == 1:
-        v = v.reshape(-1, 1)
     data_devs = (X1.device, X2.device, v.device)
     n, t = X1.shape[0], v.shape[1]
     # created outside inference mode, as in the reference (fmmv.py:909-912): the caller may update it in place
@@ -102,6 +79,89 @@ def fmmv(
             if o_dev is not out:
                 out.copy_(o_dev)
     return out
+
+
+def _dense_grad(g: torch.Tensor, dtype) -> torch.Tensor:
+    """Upstream gradients may arrive expanded (stride 0) or in another dtype; the library wants real memory
+    with a unit stride."""
+    g = g.to(dtype)
+    ok = g.dim() == 2 and (g.stride(1) == 1 or g.stride(0) == 1) and all(
+        st >= 1 or sz <= 1 for st, sz in zip(g.stride(), g.shape))
+    return g if ok else g.contiguous()
+
+
+def _grads_to(grads, like):
+    return [None if g is None else g.to(device=t.device) for g, t in zip(grads, like)]
+
+
+class KernelMmvFn(torch.autograd.Function):
+    """``k(X1, X2) @ v`` with a backward pass (the role of KernelMmvFnFull, falkon/mmv_ops/fmmv.py:771-957).
+
+    Forward is the fused product; backward evaluates the pair weights with ``flk_kgrad`` block by block
+    (falkon_b200/mmv_ops/grad.py).  Gradients flow to X1, X2, v and to the kernel's ``sigma``.
+    """
+
+    @staticmethod
+    def forward(ctx, kernel, opt, out, param_names, X1, X2, v, *params):
+        if out is not None:
+            ctx.mark_dirty(out)
+        res = _fmmv_forward(X1.detach(), X2.detach(), v.detach(), kernel, out, opt)
+        ctx.save_for_backward(X1, X2, v, *params)
+        ctx.kernel, ctx.opt, ctx.param_names = kernel, opt, param_names
+        return res
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        from .grad import kernel_backward
+
+        X1, X2, v, *params = ctx.saved_tensors
+        kernel_id, _ = _kernel_spec(ctx.kernel)
+        dev = _pick_device((X1.device, X2.device, v.device, grad_out.device))
+        sigma_idx = ctx.param_names.index("sigma") if "sigma" in ctx.param_names else None
+        needs = list(ctx.needs_input_grad[4:7])
+        needs.append(sigma_idx is not None and ctx.needs_input_grad[7 + sigma_idx])
+        sigma = params[sigma_idx] if sigma_idx is not None else ctx.kernel.sigma
+        with torch.no_grad():
+            g = kernel_backward(
+                kernel_id, sigma, _to_dev(X1, dev), _to_dev(X2, dev),
+                _to_dev(_dense_grad(grad_out, X1.dtype), dev), _to_dev(v, dev), needs, flags=_flags(ctx.opt),
+            )
+        gx1, gx2, gv = _grads_to(g[:3], (X1, X2, v))
+        param_grads = [None] * len(params)
+        if sigma_idx is not None:
+            param_grads[sigma_idx] = g[3]
+        return (None, None, None, None, gx1, gx2, gv, *param_grads)
+
+
+def fmmv(
+    X1: torch.Tensor,
+    X2: torch.Tensor,
+    v: torch.Tensor,
+    kernel,
+    out: Optional[torch.Tensor] = None,
+    opt: Optional[BaseOptions] = None,
+    kwargs_m1: Optional[Dict[str, torch.Tensor]] = None,
+    kwargs_m2: Optional[Dict[str, torch.Tensor]] = None,
+) -> torch.Tensor:
+    """``k(X1, X2) @ v`` -> (n x t).  Signature of falkon/mmv_ops/fmmv.py:960-969.
+
+    Differentiable with respect to X1, X2, v and the kernel's ``sigma`` when any of them requires a
+    gradient (and gradients are enabled), like the reference's ``KernelMmvFnFull``.
+    """
+    if _is_sparse(X1, X2):
+        raise NotImplementedError("Sparse kernel-vector products are not implemented by falkon_b200.")
+    if kwargs_m1 or kwargs_m2:
+        raise NotImplementedError("Distance kernels take no per-row keyword tensors (kwargs_m1 / kwargs_m2).")
+    _kernel_spec(kernel)
+    check_contiguity((X1, "X1"), (X2, "X2"), (v, "v"), (out, "out"))
+    _require_cuda(opt, X1, X2, v)
+    if v.dim() == 1:
+        v = v.reshape(-1, 1)
+    diff_params = getattr(kernel, "diff_params", {})
+    if torch.is_grad_enabled() and any(t.requires_grad for t in [X1, X2, v] + list(diff_params.values())):
+        names = tuple(diff_params.keys())
+        return KernelMmvFn.apply(kernel, opt, out, names, X1, X2, v, *diff_params.values())
+    return _fmmv_forward(X1, X2, v, kernel, out, opt)
 
 
 def fdmmv(

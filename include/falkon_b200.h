@@ -54,7 +54,7 @@ typedef enum flk_kernel {
 /* Bits of the `flags` argument. */
 #define FLK_FLAG_FORCE_SIMT 1 /* never use the tensor-core kernel (diagnostics / comparison) */
 #define FLK_FLAG_FORCE_TC 2   /* fail with FLK_ERR_UNSUPPORTED instead of using the SIMT kernel */
-#define FLK_FLAG_FP64_MATH 4  /* flk_fmm only: evaluate fp32 data in fp64, round once on store   */
+#define FLK_FLAG_FP64_MATH 4  /* flk_fmm / flk_kgrad: evaluate fp32 data in fp64, round on store */
 
 /* Library version (major * 10000 + minor * 100 + patch). */
 int flk_version(void);
@@ -207,6 +207,28 @@ int flk_fmm(int dtype, int kernel,
             void* out, int64_t out_rs, int64_t out_cs,
             const double* sigma_host, int64_t sigma_len,
             void* workspace, int64_t workspace_bytes, int flags, void* stream);
+
+/*
+ * Pair weights of the backward pass (device pointers; workspace as for flk_fmm):
+ *     out[i][j] = 2 k'(D2_ij) * s_ij ,   k' = dk / dD2 at the squared distance of the sigma-scaled rows,
+ *     s_ij = sum_c G[i][c] v[j][c]  (t > 0: G is n x t, v is m x t -- the backward pass of k(X1, X2) v)
+ *     s_ij = G[i][j]                (t == 0, v == NULL: G is n x m -- the backward pass of k(X1, X2)).
+ * Every gradient that the reference obtains by re-running its block product under autograd
+ * (mmv_diff_run_thread, falkon/mmv_ops/fmmv.py:405-485; KernelMmFnFull.backward in falkon/mmv_ops/fmm.py)
+ * is a matrix product with this n x m block: with W = out, a = W 1, b = W^T 1 and X~ = X / sigma,
+ *     dL/dX1~ = a o X1~ - W X2~ ,  dL/dX2~ = b o X2~ - W^T X1~ ,
+ *     dL/dsigma_k = -(1 / sigma_k) sum_ij W_ij (x~_ik - c~_jk)^2 .
+ * Entries whose squared distance the forward pass clamps at 1e-20 get weight zero.  The caller splits
+ * rows into blocks of at most 64 * 65535.
+ */
+int flk_kgrad(int dtype, int kernel,
+              const void* X1, int64_t n, int64_t x1_rs, int64_t x1_cs,
+              const void* X2, int64_t m, int64_t x2_rs, int64_t x2_cs, int64_t d,
+              const void* G, int64_t g_rs, int64_t g_cs,
+              const void* v, int64_t t, int64_t v_rs, int64_t v_cs,
+              void* out, int64_t out_rs, int64_t out_cs,
+              const double* sigma_host, int64_t sigma_len,
+              void* workspace, int64_t workspace_bytes, int flags, void* stream);
 
 /*
  * Counters for the calling process: number of kernels this library has launched and the status

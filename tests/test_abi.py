@@ -103,6 +103,30 @@ def test_kernel_matrix_entry_point_checks_arguments(lib):
     assert st == _lib.FLK_ERR_BAD_ARG  # unknown kernel id
 
 
+def test_kgrad_argument_checks(lib):
+    """flk_kgrad validates before touching the device: the checks run without a GPU."""
+    dummy = ctypes.c_void_p(4096)
+    sig = (ctypes.c_double * 1)(1.0)
+    big = 1 << 30
+
+    def call(X1=dummy, n=10, G=dummy, g_rs=2, g_cs=1, v=dummy, t=2, out_rs=5, out_cs=1, ws=dummy, ws_bytes=big,
+             kernel=0):
+        return lib.flk_kgrad(0, kernel, X1, n, 4, 1, dummy, 5, 4, 1, 4, G, g_rs, g_cs, v, t, 2, 1, dummy, out_rs,
+                             out_cs, sig, 1, ws, ws_bytes, 0, None)
+
+    assert call(X1=None) == _lib.FLK_ERR_BAD_ARG
+    assert call(G=None) == _lib.FLK_ERR_BAD_ARG
+    assert call(v=None) == _lib.FLK_ERR_BAD_ARG           # t > 0 needs the second factor
+    assert call(t=0) == _lib.FLK_ERR_BAD_ARG              # t == 0 means "G is n x m": v must be NULL
+    assert call(t=-1) == _lib.FLK_ERR_BAD_ARG
+    assert call(g_rs=3, g_cs=2) == _lib.FLK_ERR_LAYOUT
+    assert call(out_rs=7, out_cs=3) == _lib.FLK_ERR_LAYOUT
+    assert call(ws_bytes=16) == _lib.FLK_ERR_WORKSPACE
+    assert call(kernel=4) == _lib.FLK_ERR_BAD_ARG
+    assert call(n=64 * 65535 + 1) == _lib.FLK_ERR_UNSUPPORTED
+    assert b"split the rows" in lib.flk_last_error()
+
+
 def test_plain_c_client(lib, tmp_path):
     """The boundary is usable from C with nothing but the header and the shared library."""
     import shutil
