@@ -469,7 +469,8 @@ def main():
     launches = _lib.launch_count() - launches0
     clocks = sampler.stop() if rank == 0 else None
     _lib.set_timing(False)
-    dev_ms = sum(s.elapsed_time(e) for s, e in zip(starts, stops))
+    step_ms = [s.elapsed_time(e) for s, e in zip(starts, stops)]
+    dev_ms = sum(step_ms)
     tmax = torch.tensor([dev_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
@@ -478,6 +479,20 @@ def main():
     pairs_per_step = float(n) * world * M * T
     value = pairs_per_step / (ms_per_step * 1e-3)
     tc_status = _lib.tc_status(dev)
+
+    # ---------------- the single product K v of the same configuration (a data point beside the headline) ----
+    fmmv_out = torch.empty(n, T, dtype=torch.float32, device=dev)
+    fmmv_steps = max(3, min(args.steps, 10))
+    kernel.mmv(X, C, v, out=fmmv_out)
+    fe0, fe1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    fmmv_ms = []
+    for i in range(fmmv_steps):
+        flush.fill_(i & 0xFF)
+        fe0.record()
+        kernel.mmv(X, C, v, out=fmmv_out)
+        fe1.record()
+        fe1.synchronize()
+        fmmv_ms.append(fe0.elapsed_time(fe1))
 
     # ---------------- end-to-end through the host-buffer entry point (rank-local, N=1 semantics per rank) ----
     Xh = X.cpu().pin_memory()
@@ -575,6 +590,11 @@ def main():
         "cpu_baseline": cpu_baseline,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "steps": e2e_steps, "rel_l2_vs_device_path": parity},
+        "step_ms": {"min": float(min(step_ms)), "median": float(np.median(step_ms)), "max": float(max(step_ms)),
+                    "note": "per-step CUDA-event times of rank 0"},
+        "fmmv": {"value": float(n) * M * T / (float(np.median(fmmv_ms)) * 1e-3), "unit": "pair-evals/s per GPU",
+                 "ms_median": float(np.median(fmmv_ms)), "ms_min": float(min(fmmv_ms)), "steps": fmmv_steps,
+                 "note": "K v alone (one sweep), same inputs, L2 flushed between steps"},
         "gpu_launches": int(launches),
         "clocks": clocks,
         "wall_s_timed_region": wall,

@@ -22,9 +22,12 @@ namespace flk {
 namespace dmma {
 
 constexpr int BR = 128, BC = 64, DK = 16, LD = 20, TW = 32, KLD = 68, VLD = 36;
+// Operand chunks, the vector tile and the column norms go through three-deep rings: the copy of step s + 2 is
+// issued after the barrier of step s into the buffer that step s - 1 read, so one barrier per step suffices.
+constexpr int NST = 3;
 
 constexpr size_t smem_bytes() {
-  return sizeof(double) * (size_t)(2 * BR * LD + 2 * BC * LD + 2 * BC * VLD + 2 * BC + BR * KLD);
+  return sizeof(double) * (size_t)(NST * BR * LD + NST * BC * LD + NST * BC * VLD + NST * BC + BR * KLD);
 }
 
 __device__ __forceinline__ void mma884(double (&c)[2], double a, double b) {
@@ -37,11 +40,11 @@ template <int KT>
 __global__ void __launch_bounds__(256, 1) kmv_dmma_kernel(SimtArgs<double> p) {
   if (!gate_open(p.gate)) return;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  double* As = reinterpret_cast<double*>(smem_raw);  // [2][BR][LD]
-  double* Bs = As + 2 * BR * LD;                      // [2][BC][LD]
-  double* Vs = Bs + 2 * BC * LD;                      // [2][BC][VLD]
-  double* bns = Vs + 2 * BC * VLD;                    // [2][BC]
-  double* Ks = bns + 2 * BC;                          // [BR][KLD] kernel values of the current tile, row-major
+  double* As = reinterpret_cast<double*>(smem_raw);  // [NST][BR][LD]
+  double* Bs = As + NST * BR * LD;                    // [NST][BC][LD]
+  double* Vs = Bs + NST * BC * LD;                    // [NST][BC][VLD]
+  double* bns = Vs + NST * BC * VLD;                  // [NST][BC]
+  double* Ks = bns + NST * BC;                        // [BR][KLD] kernel values of the current tile, row-major
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
@@ -74,7 +77,7 @@ __global__ void __launch_bounds__(256, 1) kmv_dmma_kernel(SimtArgs<double> p) {
 
   auto issue = [&](int s) {
     const int tl = s / nk, kc = s - tl * nk;
-    const int buf = s & 1;
+    const int buf = s % NST;
     const int k0 = kc * DK;
     const int kw = min(DK, ld - k0);   // even (ld is a multiple of 2)
     const int kw4 = (kw + 3) & ~3;     // the MMA consumes features in groups of four
@@ -98,7 +101,7 @@ __global__ void __launch_bounds__(256, 1) kmv_dmma_kernel(SimtArgs<double> p) {
     if (kw4 != kw)
       for (int r = tid; r < BC; r += 256) dstb[r * LD + kw] = dstb[r * LD + kw + 1] = 0.0;
     if (kc == 0) {
-      const int vb = tl & 1;
+      const int vb = tl % NST;
       const double* vg = p.vec + ((int64_t)blockIdx.y * p.s_pad + col0) * TW;  // BC rows of TW values, contiguous
       double* vd = Vs + vb * BC * VLD;
       for (int x = tid; x < BC * (TW / 2); x += 256) {
@@ -111,18 +114,20 @@ __global__ void __launch_bounds__(256, 1) kmv_dmma_kernel(SimtArgs<double> p) {
 
   issue(0);
   cp_async_commit();
+  if (steps > 1) issue(1);
+  cp_async_commit();
 
   int tl = 0, kc = 0;
   for (int s = 0; s < steps; ++s) {
-    if (s + 1 < steps) issue(s + 1);
+    cp_async_wait<1>();   // chunk s has landed (chunk s + 1 may still be in flight)
+    __syncthreads();      // ... for every thread, and every warp is done with step s - 1
+    if (s + 2 < steps) issue(s + 2);
     cp_async_commit();
-    cp_async_wait<1>();
-    __syncthreads();
 
-    const double* a_s = As + (nk > 1 ? (s & 1) : 0) * BR * LD + (wr * 32 + g) * LD + q;
-    const double* b_s = Bs + (s & 1) * BC * LD + (wc * 32 + g) * LD + q;
+    const double* a_s = As + (nk > 1 ? (s % NST) : 0) * BR * LD + (wr * 32 + g) * LD + q;
+    const double* b_s = Bs + (s % NST) * BC * LD + (wc * 32 + g) * LD + q;
     const int kw4 = (min(DK, ld - kc * DK) + 3) & ~3;
-    for (int k = 0; k < kw4; k += 4) {
+    auto k_group = [&](int k) {
       double a[4], b[4];
 #pragma unroll
       for (int mt = 0; mt < 4; ++mt) a[mt] = a_s[mt * 8 * LD + k];
@@ -132,11 +137,17 @@ __global__ void __launch_bounds__(256, 1) kmv_dmma_kernel(SimtArgs<double> p) {
       for (int mt = 0; mt < 4; ++mt)
 #pragma unroll
         for (int nt = 0; nt < 4; ++nt) mma884(acc[mt][nt], a[mt], b[nt]);
+    };
+    if (kw4 == DK) {  // full chunk: unrolled, so the fragment loads of the next group overlap the MMAs of this one
+#pragma unroll
+      for (int k = 0; k < DK; k += 4) k_group(k);
+    } else {
+      for (int k = 0; k < kw4; k += 4) k_group(k);
     }
 
     if (kc == nk - 1) {
       // 1. kernel values of this tile -> shared memory
-      const double* bn_s = bns + (tl & 1) * BC;
+      const double* bn_s = bns + (tl % NST) * BC;
 #pragma unroll
       for (int nt = 0; nt < 4; ++nt) {
         const int c = wc * 32 + nt * 8 + 2 * q;
@@ -157,7 +168,7 @@ __global__ void __launch_bounds__(256, 1) kmv_dmma_kernel(SimtArgs<double> p) {
       __syncthreads();
       // 2. out[rows warp*16.., 32 columns] += K[rows, 0..63] vec[0..63, :]
       const double* k_s = Ks + (warp * 16 + g) * KLD + q;
-      const double* v_s = Vs + (tl & 1) * BC * VLD + q * VLD + g;
+      const double* v_s = Vs + (tl % NST) * BC * VLD + q * VLD + g;
 #pragma unroll 4
       for (int k = 0; k < BC; k += 4) {
         const double a0 = k_s[k], a1 = k_s[8 * KLD + k];
@@ -175,7 +186,6 @@ __global__ void __launch_bounds__(256, 1) kmv_dmma_kernel(SimtArgs<double> p) {
     } else {
       ++kc;
     }
-    __syncthreads();
   }
 
 #pragma unroll
