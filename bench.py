@@ -283,6 +283,8 @@ def run_config(args):
     """The other benchmark configurations as measured data points (not the default line):
     --config 4: fdmmv Gaussian sigma = 1, d = 9 Uniform[0,1), M = 100,000, w = 0, N = 10^8 sharded over the
                 GPUs (12.5e6 rows per GPU at any GPU count), fp32 or fp64 (--dtype);
+                with --d D (> 9) the same shape at another feature count: the fp32 path then runs the K-loop
+                tensor-core kernel (30 < d <= 1024), an off-headline data point;
     --config 5: fdmmv Matern 2.5 sigma = 10, fp64, N = 2e6 x d = 128 N(0,1), M = 30,000, T = 32, w ~ N(0,1), one GPU."""
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -303,11 +305,14 @@ def run_config(args):
     dtype = torch.float64 if (args.dtype == "f64" or args.config == 5) else torch.float32
     g = torch.Generator(device=dev).manual_seed(1000 + args.config * 10 + rank)
     if args.config == 4:
-        n, m, d, t, sigma, kind = (args.rows if args.rows != N_PER_GPU else 12_500_000), 100_000, 9, 1, 1.0, "gaussian"
+        n, m, d, t, kind = (args.rows if args.rows != N_PER_GPU else 12_500_000), 100_000, args.d or 9, 1, "gaussian"
+        sigma = 1.0 if d == 9 else round(float(d) ** 0.5 / 3.0, 3)  # same typical exponent at any d
         X = torch.rand(n, d, generator=g, device=dev, dtype=dtype)
         w = None
         kernel = GaussianKernel(sigma)
-        what = f"config4: fdmmv Gaussian sigma=1 {args.dtype}, N={n} per GPU x d=9 U[0,1), M=100000, T=1, w=0"
+        what = f"config4: fdmmv Gaussian sigma={sigma:g} {args.dtype}, N={n} per GPU x d={d} U[0,1), M=100000, T=1, w=0"
+        if d != 9:
+            what = "off-headline variant of " + what
     else:
         n, m, d, t, sigma, kind = (args.rows if args.rows != N_PER_GPU else 2_000_000), 30_000, 128, 32, 10.0, "matern25"
         X = torch.randn(n, d, generator=g, device=dev, dtype=dtype)
@@ -387,6 +392,7 @@ def main():
     ap.add_argument("--config", type=int, default=2, choices=[2, 4, 5],
                     help="2 = the benchmark line (default); 4 / 5 = the other fdmmv configurations as data points")
     ap.add_argument("--dtype", default="f32", choices=["f32", "f64"], help="--config 4 only")
+    ap.add_argument("--d", type=int, default=0, help="--config 4 only: feature count of an off-headline data point")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
     if args.impl == "reference":
