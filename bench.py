@@ -438,6 +438,7 @@ def main():
     kernel = GaussianKernel(SIGMA, opt=opt)
     flags = _lib.FLAG_FORCE_SIMT if args.simt else 0
     kernel.params.flk_flags = flags
+    kernel.params.flk_devices = [local_rank]  # host-operand calls stay on this rank's GPU (n_gpus is the claim)
     ops = ShardedKernelOps(kernel)
     out = torch.empty(M, T, dtype=torch.float32, device=dev)
     flush = torch.empty(256 * 2**20, dtype=torch.uint8, device=dev)  # > L2 (126 MB)

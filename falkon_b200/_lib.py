@@ -41,19 +41,40 @@ def sources():
     ]
 
 
+def _up_to_date() -> bool:
+    if not os.path.exists(LIB_PATH):
+        return False
+    return os.path.getmtime(LIB_PATH) >= max(os.path.getmtime(s) for s in sources())
+
+
 def build(force: bool = False, verbose: bool = False) -> str:
-    """Compiles csrc/flk_api.cu into libfalkon_b200.so (nvcc cross-compiles without a GPU)."""
-    if not force and os.path.exists(LIB_PATH):
-        newest = max(os.path.getmtime(s) for s in sources())
-        if os.path.getmtime(LIB_PATH) >= newest:
-            return LIB_PATH
-    nvcc = os.environ.get("NVCC", "nvcc")
-    cmd = [nvcc] + NVCC_FLAGS + ["-o", LIB_PATH, os.path.join(_CSRC, "flk_api.cu")]
-    if verbose:
-        print(" ".join(cmd))
-    res = subprocess.run(cmd, capture_output=True, text=True)
-    if res.returncode != 0:
-        raise RuntimeError(f"nvcc failed:\n{res.stdout}\n{res.stderr}")
+    """Compiles csrc/flk_api.cu into libfalkon_b200.so (nvcc cross-compiles without a GPU).
+
+    Safe when several processes (one per GPU) start at once: the build runs under an exclusive file lock,
+    writes to a temporary name and is moved into place atomically, and a process that waited for the lock
+    finds the library up to date and does not build again."""
+    if not force and _up_to_date():
+        return LIB_PATH
+    import fcntl
+
+    with open(LIB_PATH + ".lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and _up_to_date():
+                return LIB_PATH
+            tmp = f"{LIB_PATH}.{os.getpid()}.tmp"
+            nvcc = os.environ.get("NVCC", "nvcc")
+            cmd = [nvcc] + NVCC_FLAGS + ["-o", tmp, os.path.join(_CSRC, "flk_api.cu")]
+            if verbose:
+                print(" ".join(cmd))
+            res = subprocess.run(cmd, capture_output=True, text=True)
+            if res.returncode != 0:
+                if os.path.exists(tmp):
+                    os.remove(tmp)
+                raise RuntimeError(f"nvcc failed:\n{res.stdout}\n{res.stderr}")
+            os.replace(tmp, LIB_PATH)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
     return LIB_PATH
 
 

@@ -157,7 +157,7 @@ static SweepPlan plan_sweep(bool tc, int dtype, int64_t r, int64_t s, int64_t t,
   }
   p.row_tiles = (int)ceil_div(std::max<int64_t>(r, 1), p.br);
   p.n_col_tiles = (int)ceil_div(std::max<int64_t>(s, 1), p.bc);
-  const int64_t resident = tc ? 1 : ((dtype == FLK_F32 && p.tt == 1) ? 2 : 1);  // CTAs per SM
+  const int64_t resident = tc ? 1 : (p.tt == 1 ? 2 : 1);  // CTAs per SM (launch bounds of kmv_simt_kernel)
   const int64_t slots = kNumSMs * resident;
   if (!tc) {
     // SIMT kernels (small CTAs): split the reduction side into chunks so that the grid fills whole waves

@@ -25,6 +25,13 @@ constexpr int BR = 128, BC = 64, DK = 16, LD = 20, TW = 32, KLD = 68, VLD = 36;
 // Operand chunks, the vector tile and the column norms go through three-deep rings: the copy of step s + 2 is
 // issued after the barrier of step s into the buffer that step s - 1 read, so one barrier per step suffices.
 constexpr int NST = 3;
+// Warps per CTA.  First product: NW / 2 row groups x 2 column groups of 32; second product: NW row groups.
+#ifndef FLK_DMMA_WARPS
+#define FLK_DMMA_WARPS 16
+#endif
+constexpr int NW = FLK_DMMA_WARPS, NT = 32 * NW;
+constexpr int MT1 = BR / (NW / 2) / 8;  // 8-row MMA tiles per warp, first product
+constexpr int MT2 = BR / NW / 8;        // ... second product
 
 constexpr size_t smem_bytes() {
   return sizeof(double) * (size_t)(NST * BR * LD + NST * BC * LD + NST * BC * VLD + NST * BC + BR * KLD);
@@ -37,7 +44,7 @@ __device__ __forceinline__ void mma884(double (&c)[2], double a, double b) {
 }
 
 template <int KT>
-__global__ void __launch_bounds__(256, 1) kmv_dmma_kernel(SimtArgs<double> p) {
+__global__ void __launch_bounds__(NT, 1) kmv_dmma_kernel(SimtArgs<double> p) {
   if (!gate_open(p.gate)) return;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   double* As = reinterpret_cast<double*>(smem_raw);  // [NST][BR][LD]
@@ -49,7 +56,7 @@ __global__ void __launch_bounds__(256, 1) kmv_dmma_kernel(SimtArgs<double> p) {
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, q = lane & 3;
-  const int wr = warp & 3, wc = warp >> 2;  // first product: warp tile = rows wr*32.., columns wc*32..
+  const int wr = warp % (NW / 2), wc = warp / (NW / 2);  // first product: rows wr * 8 MT1.., columns wc * 32..
   const int row_tile = blockIdx.x % p.row_tiles;
   const int chunk = blockIdx.x / p.row_tiles;
   const int tile_begin = chunk * p.tiles_per_chunk;
@@ -60,18 +67,18 @@ __global__ void __launch_bounds__(256, 1) kmv_dmma_kernel(SimtArgs<double> p) {
   const int steps = ntiles * nk;
   const double* Ag = p.A + (int64_t)row_tile * BR * ld;
 
-  double an[4];
+  double an[MT1];
 #pragma unroll
-  for (int mt = 0; mt < 4; ++mt) an[mt] = p.an[(int64_t)row_tile * BR + wr * 32 + mt * 8 + g];
+  for (int mt = 0; mt < MT1; ++mt) an[mt] = p.an[(int64_t)row_tile * BR + wr * 8 * MT1 + mt * 8 + g];
 
-  double acc[4][4][2];
-  double oacc[2][4][2];  // second product: rows warp*16 + mt*8 + g, vector columns nt*8 + 2q + {0,1}
+  double acc[MT1][4][2];
+  double oacc[MT2][4][2];  // second product: rows warp * 8 MT2 + mt * 8 + g, vector columns nt * 8 + 2q + {0, 1}
 #pragma unroll
-  for (int mt = 0; mt < 4; ++mt)
+  for (int mt = 0; mt < MT1; ++mt)
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) acc[mt][nt][0] = acc[mt][nt][1] = 0.0;
 #pragma unroll
-  for (int mt = 0; mt < 2; ++mt)
+  for (int mt = 0; mt < MT2; ++mt)
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) oacc[mt][nt][0] = oacc[mt][nt][1] = 0.0;
 
@@ -84,27 +91,27 @@ __global__ void __launch_bounds__(256, 1) kmv_dmma_kernel(SimtArgs<double> p) {
     const int pieces = kw / 2;         // 16-byte pieces per row
     if (nk > 1 || s == 0) {
       double* dst = As + (nk > 1 ? buf : 0) * BR * LD;
-      for (int x = tid; x < BR * pieces; x += 256) {
+      for (int x = tid; x < BR * pieces; x += NT) {
         int r = x / pieces, pc = x - r * pieces;
         cp_async16(dst + r * LD + pc * 2, Ag + (int64_t)r * ld + k0 + pc * 2);
       }
       if (kw4 != kw)  // zero the features the last group of four reads beyond kw
-        for (int r = tid; r < BR; r += 256) dst[r * LD + kw] = dst[r * LD + kw + 1] = 0.0;
+        for (int r = tid; r < BR; r += NT) dst[r * LD + kw] = dst[r * LD + kw + 1] = 0.0;
     }
     const int64_t col0 = (int64_t)(tile_begin + tl) * BC;
     double* dstb = Bs + buf * BC * LD;
     const double* Bg = p.B + col0 * ld + k0;
-    for (int x = tid; x < BC * pieces; x += 256) {
+    for (int x = tid; x < BC * pieces; x += NT) {
       int r = x / pieces, pc = x - r * pieces;
       cp_async16(dstb + r * LD + pc * 2, Bg + (int64_t)r * ld + pc * 2);
     }
     if (kw4 != kw)
-      for (int r = tid; r < BC; r += 256) dstb[r * LD + kw] = dstb[r * LD + kw + 1] = 0.0;
+      for (int r = tid; r < BC; r += NT) dstb[r * LD + kw] = dstb[r * LD + kw + 1] = 0.0;
     if (kc == 0) {
       const int vb = tl % NST;
       const double* vg = p.vec + ((int64_t)blockIdx.y * p.s_pad + col0) * TW;  // BC rows of TW values, contiguous
       double* vd = Vs + vb * BC * VLD;
-      for (int x = tid; x < BC * (TW / 2); x += 256) {
+      for (int x = tid; x < BC * (TW / 2); x += NT) {
         int r = x / (TW / 2), pc = x - r * (TW / 2);
         cp_async16(vd + r * VLD + pc * 2, vg + r * TW + pc * 2);
       }
@@ -124,17 +131,17 @@ __global__ void __launch_bounds__(256, 1) kmv_dmma_kernel(SimtArgs<double> p) {
     if (s + 2 < steps) issue(s + 2);
     cp_async_commit();
 
-    const double* a_s = As + (nk > 1 ? (s % NST) : 0) * BR * LD + (wr * 32 + g) * LD + q;
+    const double* a_s = As + (nk > 1 ? (s % NST) : 0) * BR * LD + (wr * 8 * MT1 + g) * LD + q;
     const double* b_s = Bs + (s % NST) * BC * LD + (wc * 32 + g) * LD + q;
     const int kw4 = (min(DK, ld - kc * DK) + 3) & ~3;
     auto k_group = [&](int k) {
-      double a[4], b[4];
+      double a[MT1], b[4];
 #pragma unroll
-      for (int mt = 0; mt < 4; ++mt) a[mt] = a_s[mt * 8 * LD + k];
+      for (int mt = 0; mt < MT1; ++mt) a[mt] = a_s[mt * 8 * LD + k];
 #pragma unroll
       for (int nt = 0; nt < 4; ++nt) b[nt] = b_s[nt * 8 * LD + k];
 #pragma unroll
-      for (int mt = 0; mt < 4; ++mt)
+      for (int mt = 0; mt < MT1; ++mt)
 #pragma unroll
         for (int nt = 0; nt < 4; ++nt) mma884(acc[mt][nt], a[mt], b[nt]);
     };
@@ -153,7 +160,7 @@ __global__ void __launch_bounds__(256, 1) kmv_dmma_kernel(SimtArgs<double> p) {
         const int c = wc * 32 + nt * 8 + 2 * q;
         const double bn0 = bn_s[c], bn1 = bn_s[c + 1];
 #pragma unroll
-        for (int mt = 0; mt < 4; ++mt) {
+        for (int mt = 0; mt < MT1; ++mt) {
           double d0 = (an[mt] - 2.0 * acc[mt][nt][0]) + bn0;
           double d1 = (an[mt] - 2.0 * acc[mt][nt][1]) + bn1;
           d0 = d0 < 1e-20 ? 1e-20 : d0;
@@ -161,25 +168,25 @@ __global__ void __launch_bounds__(256, 1) kmv_dmma_kernel(SimtArgs<double> p) {
           double2 kv;
           kv.x = kernel_eval<KT>(d0);
           kv.y = kernel_eval<KT>(d1);
-          *reinterpret_cast<double2*>(Ks + (wr * 32 + mt * 8 + g) * KLD + c) = kv;
+          *reinterpret_cast<double2*>(Ks + (wr * 8 * MT1 + mt * 8 + g) * KLD + c) = kv;
           acc[mt][nt][0] = acc[mt][nt][1] = 0.0;
         }
       }
       __syncthreads();
-      // 2. out[rows warp*16.., 32 columns] += K[rows, 0..63] vec[0..63, :]
-      const double* k_s = Ks + (warp * 16 + g) * KLD + q;
+      // 2. out[rows warp * 8 MT2.., 32 columns] += K[rows, 0..63] vec[0..63, :]
+      const double* k_s = Ks + (warp * 8 * MT2 + g) * KLD + q;
       const double* v_s = Vs + (tl % NST) * BC * VLD + q * VLD + g;
 #pragma unroll 4
       for (int k = 0; k < BC; k += 4) {
-        const double a0 = k_s[k], a1 = k_s[8 * KLD + k];
-        double b[4];
+        double a[MT2], b[4];
+#pragma unroll
+        for (int mt = 0; mt < MT2; ++mt) a[mt] = k_s[mt * 8 * KLD + k];
 #pragma unroll
         for (int nt = 0; nt < 4; ++nt) b[nt] = v_s[k * VLD + nt * 8];
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt) {
-          mma884(oacc[0][nt], a0, b[nt]);
-          mma884(oacc[1][nt], a1, b[nt]);
-        }
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+          for (int mt = 0; mt < MT2; ++mt) mma884(oacc[mt][nt], a[mt], b[nt]);
       }
       kc = 0;
       ++tl;
@@ -189,8 +196,8 @@ __global__ void __launch_bounds__(256, 1) kmv_dmma_kernel(SimtArgs<double> p) {
   }
 
 #pragma unroll
-  for (int mt = 0; mt < 2; ++mt) {
-    const int64_t row = (int64_t)row_tile * BR + warp * 16 + mt * 8 + g;
+  for (int mt = 0; mt < MT2; ++mt) {
+    const int64_t row = (int64_t)row_tile * BR + warp * 8 * MT2 + mt * 8 + g;
     double* dst = p.raw + ((int64_t)chunk * p.r_pad + row) * p.tp + blockIdx.y * TW + 2 * q;
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) {
@@ -214,7 +221,7 @@ int launch_inst(const SimtArgs<double>& args, int n_chunks, int t_chunks, cudaSt
     if (dev < 16) configured[dev] = true;
   }
   dim3 grid((unsigned)(args.row_tiles * n_chunks), (unsigned)t_chunks, 1);
-  kmv_dmma_kernel<KT><<<grid, 256, smem, stream>>>(args);
+  kmv_dmma_kernel<KT><<<grid, NT, smem, stream>>>(args);
   FLK_CUDA_TRY(cudaGetLastError());
   return FLK_OK;
 }

@@ -68,7 +68,7 @@ constexpr size_t simt_smem_bytes() {
 }
 
 template <typename T, int KT, int TT>
-__global__ void __launch_bounds__(256, ((sizeof(T) == 4 && TT == 1) ? 2 : 1)) kmv_simt_kernel(SimtArgs<T> p) {
+__global__ void __launch_bounds__(256, (TT == 1 ? 2 : 1)) kmv_simt_kernel(SimtArgs<T> p) {
   using C = SimtCfg<T>;
   using Vec = typename C::Vec;
   constexpr int TR = C::TR, TC = C::TC, DK = C::DK, VEC = C::VEC;

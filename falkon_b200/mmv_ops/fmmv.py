@@ -13,6 +13,7 @@ import torch
 
 from .. import _lib
 from ..options import BaseOptions
+from . import multi_device
 from .utils import check_contiguity, create_output_mat
 
 __all__ = ("fmmv", "fdmmv", "KernelMmvFn")
@@ -71,7 +72,11 @@ def _fmmv_forward(X1, X2, v, kernel, out, opt):
         dev = _pick_device(data_devs + (out.device,))
         all_host = all(d.type == "cpu" for d in data_devs) and out.device.type == "cpu"
         if all_host:
-            _lib.call_fmmv(kernel_id, sigma, X1, X2, v, out, flags=_flags(opt), host=True, device=dev)
+            devices = multi_device.host_devices(opt, n, dev)
+            if len(devices) > 1:
+                multi_device.fmmv_host_multi(kernel_id, sigma, X1, X2, v, out, _flags(opt), devices)
+            else:
+                _lib.call_fmmv(kernel_id, sigma, X1, X2, v, out, flags=_flags(opt), host=True, device=devices[0])
         else:
             o_dev = out if out.device == dev else torch.empty(out.shape, dtype=out.dtype, device=dev)
             _lib.call_fmmv(kernel_id, sigma, _to_dev(X1, dev), _to_dev(X2, dev), _to_dev(v, dev), o_dev,
@@ -209,7 +214,12 @@ def fdmmv(
         dev = _pick_device(tuple(data_devs) + (out.device,))
         all_host = all(d.type == "cpu" for d in data_devs) and out.device.type == "cpu"
         if all_host:
-            _lib.call_fdmmv(kernel_id, sigma, X1, X2, v, w, out, flags=_flags(opt), host=True, device=dev)
+            devices = multi_device.host_devices(opt, X1.shape[0], dev)
+            if len(devices) > 1:
+                multi_device.fdmmv_host_multi(kernel_id, sigma, X1, X2, v, w, out, _flags(opt), devices)
+            else:
+                _lib.call_fdmmv(kernel_id, sigma, X1, X2, v, w, out, flags=_flags(opt), host=True,
+                                device=devices[0])
         else:
             o_dev = out if out.device == dev else torch.empty(out.shape, dtype=out.dtype, device=dev)
             _lib.call_fdmmv(kernel_id, sigma, _to_dev(X1, dev), _to_dev(X2, dev), _to_dev(v, dev),

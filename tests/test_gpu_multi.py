@@ -68,3 +68,37 @@ def test_sharded_products_and_fit_two_gpus_nccl():
     for r in range(world):
         assert ret[r][0] <= 1e-12, ret[r]   # fp64 products: only the summation order differs
         assert ret[r][1] <= 1e-6, ret[r]    # alpha of the fit on shards = the reference's
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_host_operands_fan_out_over_gpus_in_one_process():
+    """CPU tensors in, several GPUs used from one process (the reference's default way of using a multi-GPU
+    machine): same result as the one-GPU call, for both products."""
+    sys.path.insert(0, ROOT)
+    from falkon_b200 import _lib
+    from falkon_b200.kernels import GaussianKernel
+    from falkon_b200.mmv_ops import multi_device as md
+    from oracle import falkon_oracle as fo
+
+    n, m, d, t = 2 * md.MIN_ROWS_PER_DEVICE + 77, 1500, 12, 2
+    g = torch.Generator().manual_seed(31)
+    X = torch.randn(n, d, generator=g)
+    C = X[torch.randperm(n, generator=g)[:m]].contiguous()
+    v = torch.randn(m, t, generator=g)
+    w = torch.randn(n, t, generator=g)
+    k_one = GaussianKernel(3.0)
+    k_one.params.flk_devices = [0]
+    k_all = GaussianKernel(3.0)
+    assert len(md.host_devices(k_all.params, n, torch.device("cuda", 0))) >= 2
+    before = _lib.launch_count()
+    got = k_all.dmmv(X, C, v, w)
+    assert _lib.launch_count() > before
+    want = k_one.dmmv(X, C, v, w)
+    assert got.device.type == "cpu"
+    assert fo.rel_l2(got.numpy(), want.numpy()) < 1e-5
+    got = k_all.mmv(X, C, v)
+    want = k_one.mmv(X, C, v)
+    assert fo.rel_l2(got.numpy(), want.numpy()) < 1e-6
+    # and against an fp64 evaluation on the first rows
+    ref = fo.dense_fmmv_fp64(X[:512].numpy(), C.numpy(), v.numpy(), "gaussian", 3.0)
+    assert fo.rel_l2(got[:512].numpy(), ref) < 1e-4
