@@ -163,6 +163,35 @@ def test_ragged_shapes_against_oracle(shape, kernel, nu, dtype):
         assert fo.rel_l2(got, fo.dense_fdmmv_fp64(X, C, None, w, kernel, sigma[0], nu)) <= tol, "dmmv v=None"
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64], ids=["f32", "f64"])
+def test_empty_operands(dtype):
+    """Zero rows on either side: empty or all-zero results of the right shape, no launch failure, and the
+    context stays usable."""
+    from falkon_b200.kernels import GaussianKernel
+
+    k = GaussianKernel(2.0)
+    g = torch.Generator().manual_seed(9)
+    X = torch.randn(50, 4, generator=g, dtype=dtype).cuda()
+    C = torch.randn(7, 4, generator=g, dtype=dtype).cuda()
+    v = torch.randn(7, 2, generator=g, dtype=dtype).cuda()
+    w = torch.randn(50, 2, generator=g, dtype=dtype).cuda()
+    out = k.mmv(X[:0], C, v)
+    assert tuple(out.shape) == (0, 2)
+    out = k.mmv(X, C[:0], v[:0])
+    assert tuple(out.shape) == (50, 2) and float(out.abs().max()) == 0.0
+    out = k.dmmv(X[:0], C, v, w[:0])
+    assert tuple(out.shape) == (7, 2) and float(out.abs().max()) == 0.0
+    out = k.dmmv(X, C[:0], v[:0], w)
+    assert tuple(out.shape) == (0, 2)
+    K = k(X[:0], C)
+    assert tuple(K.shape) == (0, 7)
+    # host operands too
+    out = k.dmmv(X[:0].cpu(), C.cpu(), v.cpu(), w[:0].cpu())
+    assert tuple(out.shape) == (7, 2) and float(out.abs().max()) == 0.0
+    ref = fo.dense_fdmmv_fp64(X.cpu().numpy(), C.cpu().numpy(), v.cpu().numpy(), w.cpu().numpy(), "gaussian", 2.0)
+    assert fo.rel_l2(k.dmmv(X, C, v, w).cpu().numpy(), ref) < (1e-4 if dtype == torch.float32 else 1e-10)
+
+
 def test_duplicate_points_clamp():
     """Centres that are exact copies of data rows (distance 0): the clamp keeps sqrt() finite and
     the diagonal entries equal to 1 (falkon/kernels/distance_kernel.py:100)."""
