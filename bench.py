@@ -304,7 +304,17 @@ def run_config(args):
     _lib.build()
     dtype = torch.float64 if (args.dtype == "f64" or args.config == 5) else torch.float32
     g = torch.Generator(device=dev).manual_seed(1000 + args.config * 10 + rank)
-    if args.config == 4:
+    if args.config == 3:
+        # the product inside the fit of configuration 3: strong scaling, the 1e7 rows are split over the GPUs
+        n_total = args.rows if args.rows != N_PER_GPU else 10_000_000
+        n, m, d, t, kind, sigma = n_total // world, 50_000, D, 1, "gaussian", SIGMA
+        z = (torch.rand(n, 1, generator=g, device=dev) < 0.5).to(dtype)
+        X = torch.randn(n, d, generator=g, device=dev, dtype=dtype) + (2.0 * z - 1.0) * 0.5
+        w = torch.randn(n, t, generator=g, device=dev, dtype=dtype)
+        kernel = GaussianKernel(sigma)
+        what = (f"config3 product: fdmmv Gaussian sigma=5 f32, N={n_total} split over {world} GPU(s) x d=28 mixture, "
+                f"M=50000, T=1, w~N(0,1)")
+    elif args.config == 4:
         n, m, d, t, kind = (args.rows if args.rows != N_PER_GPU else 12_500_000), 100_000, args.d or 9, 1, "gaussian"
         sigma = 1.0 if d == 9 else round(float(d) ** 0.5 / 3.0, 3)  # same typical exponent at any d
         X = torch.rand(n, d, generator=g, device=dev, dtype=dtype)
@@ -357,7 +367,8 @@ def run_config(args):
     if rank == 0:
         sm_mhz = (clocks or {}).get("sm_mhz") or 1965.0
         line = {"metric": METRIC, "value": float(n) * world * m * t / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
-                "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": ms, "scaling": "weak",
+                "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": ms,
+                "scaling": "strong" if args.config == 3 else "weak",
                 "dtype": "f64" if dtype == torch.float64 else "f32", "data": "synthetic",
                 "config": {"workload": what, "rows_per_gpu": n, "centres": m, "d": d, "T": t,
                            "tensor_core_path": bool(_lib.load().flk_uses_tensor_cores(0 if dtype == torch.float32 else 1, 0, d, t, 0))},
@@ -365,6 +376,13 @@ def run_config(args):
                 "kernel_evals_per_s_per_gpu": 2.0 * n * m / (ms * 1e-3),
                 "spot_check_rel_l2_vs_fp64": err, "spot_check_rows": ns, "clocks": clocks,
                 "tc_status": _lib.tc_status(dev), "range_flag": _lib.range_flag(dev)}
+        if dtype == torch.float32 and d <= 30:
+            # resident tensor-core kernel: one exponential per kernel evaluation, bound by the MUFU rate
+            mufu = _lib.measure_mufu_rate(dev)
+            evals = float(n) * m / (0.5 * (sweeps[0] + sweeps[1]) * 1e-3)
+            line["roofline"] = {"bound": "mufu", "achieved": evals / 1e9, "peak": mufu / 1e9, "unit": "Gexp/s",
+                                "frac": evals / mufu, "note": "per GPU (rank 0), sweep launches only; peak = ex2 "
+                                "rate measured live by the probe kernel"}
         if dtype == torch.float64:
             dfma_per_pair = d + (t if t > 4 else 4 + t) + 4
             peak = 148 * 64 * sm_mhz * 1e6
@@ -389,8 +407,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--fit", action="store_true", help="run benchmark configuration 3 (full Falkon.fit) instead")
     ap.add_argument("--centres", type=int, default=50_000, help="number of Nystrom centres for --fit")
-    ap.add_argument("--config", type=int, default=2, choices=[2, 4, 5],
-                    help="2 = the benchmark line (default); 4 / 5 = the other fdmmv configurations as data points")
+    ap.add_argument("--config", type=int, default=2, choices=[2, 3, 4, 5],
+                    help="2 = the benchmark line (default); 3 / 4 / 5 = the other fdmmv configurations as data points "
+                         "(3 = the fdmmv of the fit configuration, N = 1e7 rows split over the GPUs, M = 50,000)")
     ap.add_argument("--dtype", default="f32", choices=["f32", "f64"], help="--config 4 only")
     ap.add_argument("--d", type=int, default=0, help="--config 4 only: feature count of an off-headline data point")
     args = ap.parse_args()
@@ -401,7 +420,7 @@ def main():
         return run_fit(args)
     if args.config != 2:
         if args.steps == 40:
-            args.steps = 3
+            args.steps = 10 if args.config == 3 else 3
         return run_config(args)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))

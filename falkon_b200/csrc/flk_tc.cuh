@@ -511,6 +511,7 @@ struct TcCfg {
 };
 
 constexpr int kWideTT = 32;  // vector columns per pass of the many-column epilogue
+constexpr int kFlushTiles = 32;  // column tiles (of 128) summed in one running fp32 sum before it is folded away
 
 // Ring depths: with 32 vector columns per pass a vector tile is 16 KB, so two of them and one B stage fewer.
 template <int NSLAB, int TT>
@@ -523,7 +524,8 @@ template <int NSLAB, int TT>
 constexpr size_t tc_smem_bytes() {
   using C = TcCfg<NSLAB>;
   return 1024 /* alignment slack */ + (size_t)C::A_BYTES + (size_t)RingOf<NSLAB, TT>::S * C::TILE_BYTES +
-         (size_t)RingOf<NSLAB, TT>::VS * kColsPerTile * TT * 4 + 512 /* barriers + tmem pointer */;
+         (size_t)RingOf<NSLAB, TT>::VS * kColsPerTile * TT * 4 + 512 /* barriers + tmem pointer */ +
+         (TT == kWideTT ? 0 : kRowsPerCta * 16) /* second-level sums, four floats per epilogue thread */;
 }
 
 // error codes written to the status word: role * 16 + which wait
@@ -632,6 +634,8 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
   uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bar_t_empty + kRowBlocks);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
   static_assert((1 + 2 * S + 2 * VS + 2 * kRowBlocks) * 8 + 8 <= 512, "barrier block overflows its 512 bytes");
+  // second-level sums of the epilogue threads (TT <= 4): one float4 each, behind the 512-byte barrier block
+  float4* tot_sm = reinterpret_cast<float4*>(reinterpret_cast<unsigned char*>(bars) + 512);
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
@@ -763,14 +767,47 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
     const int q = warp & 3;    // TMEM lane quarter this warp may access
     const int rb = warp >> 2;  // row block
     constexpr int NSUM = TT == kWideTT ? 16 : 2;  // packed pairs of running sums (see epilogue_32 / epilogue_wide16)
+    // Two-level summation: `osum` collects kFlushTiles column tiles, then is folded into a second-level sum
+    // (shared memory for TT <= 4, so the hot loop keeps its registers; thread-local for the many-column form).
+    // A chunk may span millions of columns; one running fp32 sum over all of them loses about half a digit more
+    // than the reference's blocked GEMV does, enough to unsettle an fp32 conjugate gradient at lambda = 1e-7.
     uint64_t osum[NSUM];
+    uint64_t otot[TT == kWideTT ? NSUM : 1];
 #pragma unroll
     for (int i = 0; i < NSUM; ++i) osum[i] = 0ull;
+    float4* tot = tot_sm + (warp * 32 + lane);
+    if constexpr (TT == kWideTT) {
+#pragma unroll
+      for (int i = 0; i < NSUM; ++i) otot[i] = 0ull;
+    } else {
+      otot[0] = 0ull;
+      *tot = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
     const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(rb * kColsPerTile);
     bool epi_ok = true;
 
     for (int j = 0; j < ntiles; ++j) {
       const int vstage = j % VS;
+      if ((j & (kFlushTiles - 1)) == kFlushTiles - 1) {
+        if constexpr (TT == kWideTT) {
+#pragma unroll
+          for (int i = 0; i < NSUM; ++i) {
+            otot[i] = add2(otot[i], osum[i]);
+            osum[i] = 0ull;
+          }
+        } else {
+          float4 t = *tot;
+          float a0, a1, b0, b1;
+          unpack2(osum[0], a0, a1);
+          unpack2(osum[1], b0, b1);
+          t.x += a0;
+          t.y += a1;
+          t.z += b0;
+          t.w += b1;
+          *tot = t;
+          osum[0] = osum[1] = 0ull;
+        }
+      }
       if (*abort_flag) { epi_ok = false; break; }
       if (!mbar_wait(smem_u32(bar_v_full + vstage), (j / VS) & 1) ||
           !mbar_wait(smem_u32(bar_t_full + rb), j & 1)) {
@@ -824,6 +861,14 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
       if (lane == 0) mbar_arrive(smem_u32(bar_v_empty + vstage));
     }
     if (epi_ok) {
+      if constexpr (TT == kWideTT) {
+#pragma unroll
+        for (int i = 0; i < NSUM; ++i) osum[i] = add2(otot[i], osum[i]);
+      } else {
+        const float4 t = *tot;
+        osum[0] = add2(pack2(t.x, t.y), osum[0]);
+        osum[1] = add2(pack2(t.z, t.w), osum[1]);
+      }
       const int64_t row = (int64_t)row_tile * kRowsPerCta + rb * kTileRows + q * 32 + lane;
       float* dst = p.raw + ((int64_t)chunk * p.r_pad + row) * p.tp + tchunk * TT;
       if constexpr (TT == kWideTT) {

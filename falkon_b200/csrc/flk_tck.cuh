@@ -381,12 +381,20 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
     const int rb = (warp >> 2) & 1;
     const int half = warp >> 3;  // columns half * 64 .. + 63 of every tile
     constexpr int NSUM = TT == kWideTT ? 16 : 2;
-    uint64_t osum[NSUM];
+    // two-level summation, as in the resident kernel: a running sum covers tc::kFlushTiles column tiles
+    uint64_t osum[NSUM], otot[NSUM];
 #pragma unroll
-    for (int i = 0; i < NSUM; ++i) osum[i] = 0ull;
+    for (int i = 0; i < NSUM; ++i) osum[i] = otot[i] = 0ull;
     bool epi_ok = true;
     for (int j = 0; j < ntiles; ++j) {
       const int vstage = j % VS, buf = j & 1;
+      if ((j & (tc::kFlushTiles - 1)) == tc::kFlushTiles - 1) {
+#pragma unroll
+        for (int i = 0; i < NSUM; ++i) {
+          otot[i] = tc::add2(otot[i], osum[i]);
+          osum[i] = 0ull;
+        }
+      }
       if (*abort_flag) { epi_ok = false; break; }
       if (!mbar_wait(smem_u32(bar_v_full + vstage), (j / VS) & 1) ||
           !mbar_wait(smem_u32(bar_t_full + rb * 2 + buf), (j >> 1) & 1)) {
@@ -428,6 +436,8 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
       if (lane == 0) mbar_arrive(smem_u32(bar_v_empty + vstage));
     }
     // per-thread sums of this column half
+#pragma unroll
+    for (int i = 0; i < NSUM; ++i) osum[i] = tc::add2(otot[i], osum[i]);
     float o[TT];
     if constexpr (TT == kWideTT) {
 #pragma unroll

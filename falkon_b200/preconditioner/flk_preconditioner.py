@@ -11,8 +11,9 @@ A, A^T, T, T^T; ``apply(v) = T^-1 A^-1 v`` and ``apply_t(v) = A^-T T^-T v``.
 What differs from the reference is where the work runs.  The reference packs T and A into the two
 triangles of one M x M buffer and drives cuSOLVER / its own out-of-core LAUUM and POTRF from Python
 so that M x M may exceed GPU memory.  A B200 holds several M x M matrices at M = 50 000 (10 GB each
-in fp32), so this class keeps T and A as two separate device tensors and uses the library
-factorisation and triangular solves of torch (cuSOLVER / cuBLAS): these steps are outside the
+in fp32), so this class keeps T and A as two separate device tensors.  Triangular solves are the
+library's (cuBLAS); the factorisations and T T^T are the library's in fp64 and, in fp32, blocked versions
+whose M^3 products run as split-TF32 tensor-core GEMMs (tensor_core_la.py).  These steps are outside the
 kernel-vector-product hot path.  K_MM itself comes from this package's CUDA kernel (``Kernel.__call__``
 -> ``flk_fmm``), evaluated in fp64 for fp32 data when ``no_single_kernel`` is set, as in the reference.
 """
@@ -22,6 +23,7 @@ from typing import Optional
 import torch
 
 from ..options import FalkonOptions
+from .tensor_core_la import cholesky_lower_3xtf32, triu_times_transpose_3xtf32
 
 __all__ = ("Preconditioner", "FalkonPreconditioner")
 
@@ -87,7 +89,9 @@ class FalkonPreconditioner(Preconditioner):
     opt
         ``pc_epsilon_32 / pc_epsilon_64`` (jitter added to K_MM, multiplied by M as in the reference,
         flk_preconditioner.py:117) and ``no_single_kernel`` are honoured.  ``cpu_preconditioner`` /
-        ``use_cpu`` are rejected: there is no CPU path in this package.
+        ``use_cpu`` are rejected: there is no CPU path in this package.  Setting the attribute
+        ``opt.pc_tensor_cores = False`` (not a reference option, hence not a dataclass field) selects the library's
+        fp32 Cholesky and fp32 GEMMs instead of the split-TF32 tensor-core versions.
     """
 
     def __init__(self, penalty: float, kernel, opt: Optional[FalkonOptions] = None):
@@ -126,24 +130,36 @@ class FalkonPreconditioner(Preconditioner):
             C = self.kernel(Xd, Xd, opt=self.params)  # M x M, data dtype
             eps = self.params.pc_epsilon(C.dtype)
             C.diagonal().add_(eps * M)
-            # T^T T = C.  `cholesky_ex` reports failure as a status instead of a device assert.
-            T, info = torch.linalg.cholesky_ex(C, upper=True)
-            if int(info.item()) != 0:
+            # fp32: blocked factorisation / products whose M^3 part runs on the tensor cores (tensor_core_la.py)
+            tensor_cores = C.dtype == torch.float32 and getattr(self.params, "pc_tensor_cores", True)
+            # T^T T = C.  Failure is reported as a status instead of a device assert.
+            if tensor_cores:
+                L, code = cholesky_lower_3xtf32(C)  # in place; T is its transpose, as a view
+                T = L.mT
+            else:
+                T, info = torch.linalg.cholesky_ex(C, upper=True)
+                code = int(info.item())
+            if code != 0:
                 raise RuntimeError(
-                    f"Cholesky factorisation of K_MM failed at leading minor {int(info.item())}: "
+                    f"Cholesky factorisation of K_MM failed at leading minor {code}: "
                     f"K_MM is not positive definite; increase pc_epsilon (now {eps})."
                 )
             del C
-            TTt = _triu_times_transpose(T)
+            TTt = triu_times_transpose_3xtf32(T) if tensor_cores else _triu_times_transpose(T)
             if weight_vec is not None:
                 s = weight_vec.to(dev, TTt.dtype).reshape(-1).sqrt()
                 TTt.mul_(s.reshape(-1, 1)).mul_(s.reshape(1, -1))
             TTt.mul_(1.0 / M)
             TTt.diagonal().add_(self._lambda)
-            A, info = torch.linalg.cholesky_ex(TTt, upper=True)
-            if int(info.item()) != 0:
+            if tensor_cores:
+                L2, code = cholesky_lower_3xtf32(TTt)
+                A = L2.mT
+            else:
+                A, info = torch.linalg.cholesky_ex(TTt, upper=True)
+                code = int(info.item())
+            if code != 0:
                 raise RuntimeError(
-                    f"Cholesky factorisation of 1/M T T^T + lambda I failed at leading minor {int(info.item())}."
+                    f"Cholesky factorisation of 1/M T T^T + lambda I failed at leading minor {code}."
                 )
             del TTt
             self.T, self.A = T, A

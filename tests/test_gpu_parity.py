@@ -192,6 +192,27 @@ def test_empty_operands(dtype):
     assert fo.rel_l2(k.dmmv(X, C, v, w).cpu().numpy(), ref) < (1e-4 if dtype == torch.float32 else 1e-10)
 
 
+@pytest.mark.parametrize("d", [8, 48], ids=["resident", "kloop"])
+def test_long_reductions_keep_fp32_accuracy(d):
+    """Reduction over millions of rows (the K^T u sweep of a large fit): the fp32 result stays within 1e-6 of an
+    fp64 evaluation.  A single running fp32 sum per thread over a whole chunk reaches several 1e-6 here, which is
+    enough to make an fp32 conjugate gradient at lambda = 1e-7 drift; the kernels sum in two levels."""
+    from falkon_b200.kernels import GaussianKernel
+
+    n, m = 4_000_000, 1024
+    g = torch.Generator(device="cuda").manual_seed(12)
+    X = torch.randn(n, d, generator=g, device="cuda")
+    C = X[torch.randperm(n, generator=g, device="cuda")[:m]].contiguous()
+    y = torch.randn(n, 2, generator=g, device="cuda")
+    k = GaussianKernel(float(d) ** 0.5)
+    got = k.mmv(C, X, y)
+    want = k.mmv(C.double(), X.double(), y.double())
+    err = fo.rel_l2(got.cpu().numpy(), want.cpu().numpy())
+    assert err < 1e-6, err
+    got = k.dmmv(X, C, None, y)
+    assert fo.rel_l2(got.cpu().numpy(), want.cpu().numpy()) < 1e-6
+
+
 def test_duplicate_points_clamp():
     """Centres that are exact copies of data rows (distance 0): the clamp keeps sqrt() finite and
     the diagonal entries equal to 1 (falkon/kernels/distance_kernel.py:100)."""
