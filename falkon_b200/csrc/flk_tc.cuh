@@ -768,21 +768,15 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
     const int rb = warp >> 2;  // row block
     constexpr int NSUM = TT == kWideTT ? 16 : 2;  // packed pairs of running sums (see epilogue_32 / epilogue_wide16)
     // Two-level summation: `osum` collects kFlushTiles column tiles, then is folded into a second-level sum
-    // (shared memory for TT <= 4, so the hot loop keeps its registers; thread-local for the many-column form).
+    // that costs the hot loop no registers: a float4 in shared memory for TT <= 4, this thread's own entries of
+    // the partial-result buffer in global memory for the many-column form (32 floats every 32 tiles).
     // A chunk may span millions of columns; one running fp32 sum over all of them loses about half a digit more
     // than the reference's blocked GEMV does, enough to unsettle an fp32 conjugate gradient at lambda = 1e-7.
     uint64_t osum[NSUM];
-    uint64_t otot[TT == kWideTT ? NSUM : 1];
 #pragma unroll
     for (int i = 0; i < NSUM; ++i) osum[i] = 0ull;
     float4* tot = tot_sm + (warp * 32 + lane);
-    if constexpr (TT == kWideTT) {
-#pragma unroll
-      for (int i = 0; i < NSUM; ++i) otot[i] = 0ull;
-    } else {
-      otot[0] = 0ull;
-      *tot = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    }
+    if constexpr (TT != kWideTT) *tot = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(rb * kColsPerTile);
     bool epi_ok = true;
 
@@ -790,9 +784,17 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
       const int vstage = j % VS;
       if ((j & (kFlushTiles - 1)) == kFlushTiles - 1) {
         if constexpr (TT == kWideTT) {
+          const int64_t row = (int64_t)row_tile * kRowsPerCta + rb * kTileRows + q * 32 + lane;
+          float2* dst2 = reinterpret_cast<float2*>(p.raw + ((int64_t)chunk * p.r_pad + row) * p.tp + tchunk * TT);
+          const bool first = j == kFlushTiles - 1;
 #pragma unroll
           for (int i = 0; i < NSUM; ++i) {
-            otot[i] = add2(otot[i], osum[i]);
+            float lo, hi;
+            unpack2(osum[i], lo, hi);
+            float2 t = first ? make_float2(0.0f, 0.0f) : dst2[i];
+            t.x += lo;
+            t.y += hi;
+            dst2[i] = t;
             osum[i] = 0ull;
           }
         } else {
@@ -861,10 +863,7 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
       if (lane == 0) mbar_arrive(smem_u32(bar_v_empty + vstage));
     }
     if (epi_ok) {
-      if constexpr (TT == kWideTT) {
-#pragma unroll
-        for (int i = 0; i < NSUM; ++i) osum[i] = add2(otot[i], osum[i]);
-      } else {
+      if constexpr (TT != kWideTT) {
         const float4 t = *tot;
         osum[0] = add2(pack2(t.x, t.y), osum[0]);
         osum[1] = add2(pack2(t.z, t.w), osum[1]);
@@ -872,12 +871,13 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
       const int64_t row = (int64_t)row_tile * kRowsPerCta + rb * kTileRows + q * 32 + lane;
       float* dst = p.raw + ((int64_t)chunk * p.r_pad + row) * p.tp + tchunk * TT;
       if constexpr (TT == kWideTT) {
+        const bool flushed = ntiles >= kFlushTiles;  // the buffer already holds the second-level sums
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           float lo, hi;
           unpack2(osum[i], lo, hi);
-          dst[2 * i] = lo;
-          dst[2 * i + 1] = hi;
+          dst[2 * i] = flushed ? dst[2 * i] + lo : lo;
+          dst[2 * i + 1] = flushed ? dst[2 * i + 1] + hi : hi;
         }
       } else {
         float a0, a1, b0, b1;
