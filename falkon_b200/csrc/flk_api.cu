@@ -212,10 +212,12 @@ static SweepPlan plan_sweep(bool tc, int dtype, int64_t r, int64_t s, int64_t t,
       p.tiles_per_chunk_tail = (int)(ctas_t > 0 ? tpc_t : tpc_m);
     }
   };
-  for (int64_t c = 1; c <= c_cap; ++c) consider(R, c, c);
+  // the many-column epilogue sums a whole chunk in one running fp32 sum per thread: bound its length
+  const int64_t c_min = p.tt == tc::kWideTT ? ceil_div(Ct, (int64_t)tc::kMaxWideTilesPerChunk) : 1;
+  for (int64_t c = c_min; c <= std::max(c_cap, c_min); ++c) consider(R, c, c);
   if (Y == 1 && !p.kloop) {
     for (int64_t cm : {1, 2, 4}) {  // divisors of 148, so that the first segment ends on a wave boundary
-      if (cm > c_cap || ceil_div(Ct, ceil_div(Ct, cm)) != cm) continue;
+      if (cm < c_min || cm > c_cap || ceil_div(Ct, ceil_div(Ct, cm)) != cm) continue;
       const int64_t main_tiles = (R * cm / slots) * (slots / cm);
       if (main_tiles <= 0 || main_tiles >= R) continue;
       for (int64_t ct = cm + 1; ct <= std::min<int64_t>(c_cap, 64); ++ct) consider(main_tiles, cm, ct);

@@ -273,6 +273,12 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
   asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
   return d;
 }
+__device__ __forceinline__ void ld_shared_f4(uint32_t addr, float& a, float& b, float& c, float& d) {
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(a), "=f"(b), "=f"(c), "=f"(d) : "r"(addr) : "memory");
+}
+__device__ __forceinline__ void st_shared_f4(uint32_t addr, float a, float b, float c, float d) {
+  asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
 __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
   uint64_t d;
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
@@ -512,6 +518,7 @@ struct TcCfg {
 
 constexpr int kWideTT = 32;  // vector columns per pass of the many-column epilogue
 constexpr int kFlushTiles = 32;  // column tiles (of 128) summed in one running fp32 sum before it is folded away
+constexpr int kMaxWideTilesPerChunk = 512;  // many-column epilogue (single-level sums): longest chunk the planner forms
 
 // Ring depths: with 32 vector columns per pass a vector tile is 16 KB, so two of them and one B stage fewer.
 template <int NSLAB, int TT>
@@ -635,7 +642,6 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
   static_assert((1 + 2 * S + 2 * VS + 2 * kRowBlocks) * 8 + 8 <= 512, "barrier block overflows its 512 bytes");
   // second-level sums of the epilogue threads (TT <= 4): one float4 each, behind the 512-byte barrier block
-  float4* tot_sm = reinterpret_cast<float4*>(reinterpret_cast<unsigned char*>(bars) + 512);
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
@@ -767,49 +773,36 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
     const int q = warp & 3;    // TMEM lane quarter this warp may access
     const int rb = warp >> 2;  // row block
     constexpr int NSUM = TT == kWideTT ? 16 : 2;  // packed pairs of running sums (see epilogue_32 / epilogue_wide16)
-    // Two-level summation: `osum` collects kFlushTiles column tiles, then is folded into a second-level sum
-    // that costs the hot loop no registers: a float4 in shared memory for TT <= 4, this thread's own entries of
-    // the partial-result buffer in global memory for the many-column form (32 floats every 32 tiles).
-    // A chunk may span millions of columns; one running fp32 sum over all of them loses about half a digit more
-    // than the reference's blocked GEMV does, enough to unsettle an fp32 conjugate gradient at lambda = 1e-7.
+    // Two-level summation (TT <= 4): `osum` collects kFlushTiles column tiles, then is folded into a float4 of
+    // this thread in shared memory, addressed through a 32-bit shared address formed on the spot, so that the
+    // hot loop keeps its registers: this kernel sits at its 80-register ceiling and must not spill, because
+    // registers that a tcgen05.ld is still filling could be among the spilled ones.  A chunk may span millions of
+    // columns; one running fp32 sum over all of them loses about half a digit more than the reference's blocked
+    // GEMV does, enough to unsettle an fp32 conjugate gradient at lambda = 1e-7.  The many-column form keeps
+    // one level: the planner bounds its chunk length instead (kMaxWideTilesPerChunk).
     uint64_t osum[NSUM];
 #pragma unroll
     for (int i = 0; i < NSUM; ++i) osum[i] = 0ull;
-    float4* tot = tot_sm + (warp * 32 + lane);
-    if constexpr (TT != kWideTT) *tot = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if constexpr (TT != kWideTT) st_shared_f4(smem_u32(bars) + 512u + (uint32_t)(warp * 32 + lane) * 16u, 0.f, 0.f, 0.f, 0.f);
     const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(rb * kColsPerTile);
     bool epi_ok = true;
 
-    for (int j = 0; j < ntiles; ++j) {
-      const int vstage = j % VS;
-      if ((j & (kFlushTiles - 1)) == kFlushTiles - 1) {
-        if constexpr (TT == kWideTT) {
-          const int64_t row = (int64_t)row_tile * kRowsPerCta + rb * kTileRows + q * 32 + lane;
-          float2* dst2 = reinterpret_cast<float2*>(p.raw + ((int64_t)chunk * p.r_pad + row) * p.tp + tchunk * TT);
-          const bool first = j == kFlushTiles - 1;
-#pragma unroll
-          for (int i = 0; i < NSUM; ++i) {
-            float lo, hi;
-            unpack2(osum[i], lo, hi);
-            float2 t = first ? make_float2(0.0f, 0.0f) : dst2[i];
-            t.x += lo;
-            t.y += hi;
-            dst2[i] = t;
-            osum[i] = 0ull;
-          }
-        } else {
-          float4 t = *tot;
-          float a0, a1, b0, b1;
-          unpack2(osum[0], a0, a1);
-          unpack2(osum[1], b0, b1);
-          t.x += a0;
-          t.y += a1;
-          t.z += b0;
-          t.w += b1;
-          *tot = t;
-          osum[0] = osum[1] = 0ull;
-        }
+    // outer loop = blocks of kFlushTiles tiles, with the fold between the blocks and outside the hot inner loop
+    for (int j0 = 0; j0 < ntiles && epi_ok; j0 += kFlushTiles) {
+    if constexpr (TT != kWideTT) {
+      if (j0 > 0) {
+        const uint32_t tot = smem_u32(bars) + 512u + (uint32_t)(warp * 32 + lane) * 16u;
+        float t0, t1, t2, t3, a0, a1, b0, b1;
+        ld_shared_f4(tot, t0, t1, t2, t3);
+        unpack2(osum[0], a0, a1);
+        unpack2(osum[1], b0, b1);
+        st_shared_f4(tot, t0 + a0, t1 + a1, t2 + b0, t3 + b1);
+        osum[0] = osum[1] = 0ull;
       }
+    }
+    const int j1 = min(j0 + kFlushTiles, ntiles);
+    for (int j = j0; j < j1; ++j) {
+      const int vstage = j % VS;
       if (*abort_flag) { epi_ok = false; break; }
       if (!mbar_wait(smem_u32(bar_v_full + vstage), (j / VS) & 1) ||
           !mbar_wait(smem_u32(bar_t_full + rb), j & 1)) {
@@ -862,22 +855,23 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(bar_v_empty + vstage));
     }
+    }
     if (epi_ok) {
       if constexpr (TT != kWideTT) {
-        const float4 t = *tot;
-        osum[0] = add2(pack2(t.x, t.y), osum[0]);
-        osum[1] = add2(pack2(t.z, t.w), osum[1]);
+        float t0, t1, t2, t3;
+        ld_shared_f4(smem_u32(bars) + 512u + (uint32_t)(warp * 32 + lane) * 16u, t0, t1, t2, t3);
+        osum[0] = add2(pack2(t0, t1), osum[0]);
+        osum[1] = add2(pack2(t2, t3), osum[1]);
       }
       const int64_t row = (int64_t)row_tile * kRowsPerCta + rb * kTileRows + q * 32 + lane;
       float* dst = p.raw + ((int64_t)chunk * p.r_pad + row) * p.tp + tchunk * TT;
       if constexpr (TT == kWideTT) {
-        const bool flushed = ntiles >= kFlushTiles;  // the buffer already holds the second-level sums
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           float lo, hi;
           unpack2(osum[i], lo, hi);
-          dst[2 * i] = flushed ? dst[2 * i] + lo : lo;
-          dst[2 * i + 1] = flushed ? dst[2 * i + 1] + hi : hi;
+          dst[2 * i] = lo;
+          dst[2 * i + 1] = hi;
         }
       } else {
         float a0, a1, b0, b1;

@@ -381,20 +381,27 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
     const int rb = (warp >> 2) & 1;
     const int half = warp >> 3;  // columns half * 64 .. + 63 of every tile
     constexpr int NSUM = TT == kWideTT ? 16 : 2;
-    // two-level summation, as in the resident kernel: a running sum covers tc::kFlushTiles column tiles
-    uint64_t osum[NSUM], otot[NSUM];
+    // two-level summation for TT <= 4, as in the resident kernel (here the second level fits in registers);
+    // the many-column form keeps one level and relies on the planner's bound on the chunk length
+    uint64_t osum[NSUM], otot[TT == kWideTT ? 1 : NSUM];
 #pragma unroll
-    for (int i = 0; i < NSUM; ++i) osum[i] = otot[i] = 0ull;
+    for (int i = 0; i < NSUM; ++i) osum[i] = 0ull;
+#pragma unroll
+    for (int i = 0; i < (TT == kWideTT ? 1 : NSUM); ++i) otot[i] = 0ull;
     bool epi_ok = true;
-    for (int j = 0; j < ntiles; ++j) {
-      const int vstage = j % VS, buf = j & 1;
-      if ((j & (tc::kFlushTiles - 1)) == tc::kFlushTiles - 1) {
+    for (int j0 = 0; j0 < ntiles && epi_ok; j0 += tc::kFlushTiles) {
+    if constexpr (TT != kWideTT) {
+      if (j0 > 0) {
 #pragma unroll
         for (int i = 0; i < NSUM; ++i) {
           otot[i] = tc::add2(otot[i], osum[i]);
           osum[i] = 0ull;
         }
       }
+    }
+    const int j1 = min(j0 + tc::kFlushTiles, ntiles);
+    for (int j = j0; j < j1; ++j) {
+      const int vstage = j % VS, buf = j & 1;
       if (*abort_flag) { epi_ok = false; break; }
       if (!mbar_wait(smem_u32(bar_v_full + vstage), (j / VS) & 1) ||
           !mbar_wait(smem_u32(bar_t_full + rb * 2 + buf), (j >> 1) & 1)) {
@@ -435,9 +442,12 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(bar_v_empty + vstage));
     }
+    }
     // per-thread sums of this column half
+    if constexpr (TT != kWideTT) {
 #pragma unroll
-    for (int i = 0; i < NSUM; ++i) osum[i] = tc::add2(otot[i], osum[i]);
+      for (int i = 0; i < NSUM; ++i) osum[i] = tc::add2(otot[i], osum[i]);
+    }
     float o[TT];
     if constexpr (TT == kWideTT) {
 #pragma unroll
