@@ -24,6 +24,10 @@ import torch
 
 from ..options import FalkonOptions
 from .tensor_core_la import cholesky_lower_3xtf32, triu_times_transpose_3xtf32
+from .tri_solve import BlockedTriangular
+
+#: from this many centres on, the per-iteration triangular solves go through BlockedTriangular
+_BLOCKED_SOLVE_MIN_M = 8192
 
 __all__ = ("Preconditioner", "FalkonPreconditioner")
 
@@ -103,6 +107,8 @@ class FalkonPreconditioner(Preconditioner):
         self.kernel = kernel
         self.T: Optional[torch.Tensor] = None
         self.A: Optional[torch.Tensor] = None
+        self._t_solver: Optional[BlockedTriangular] = None
+        self._a_solver: Optional[BlockedTriangular] = None
 
     # the reference exposes the diagonals it has to save because its two factors share a buffer
     @property
@@ -137,7 +143,8 @@ class FalkonPreconditioner(Preconditioner):
                 L, code = cholesky_lower_3xtf32(C)  # in place; T is its transpose, as a view
                 T = L.mT
             else:
-                T, info = torch.linalg.cholesky_ex(C, upper=True)
+                L, info = torch.linalg.cholesky_ex(C, upper=False)
+                T = L.mT
                 code = int(info.item())
             if code != 0:
                 raise RuntimeError(
@@ -155,7 +162,8 @@ class FalkonPreconditioner(Preconditioner):
                 L2, code = cholesky_lower_3xtf32(TTt)
                 A = L2.mT
             else:
-                A, info = torch.linalg.cholesky_ex(TTt, upper=True)
+                L2, info = torch.linalg.cholesky_ex(TTt, upper=False)
+                A = L2.mT
                 code = int(info.item())
             if code != 0:
                 raise RuntimeError(
@@ -163,6 +171,11 @@ class FalkonPreconditioner(Preconditioner):
                 )
             del TTt
             self.T, self.A = T, A
+            # T = L^T and A = L2^T are kept as transposed views of the row-major lower factors
+            self._t_solver = self._a_solver = None
+            if M >= _BLOCKED_SOLVE_MIN_M:
+                self._t_solver = BlockedTriangular(L)
+                self._a_solver = BlockedTriangular(L2)
         return self
 
     def to(self, device):
@@ -170,6 +183,10 @@ class FalkonPreconditioner(Preconditioner):
             self.T = self.T.to(device)
         if self.A is not None:
             self.A = self.A.to(device)
+        if self._t_solver is not None:  # the solvers hold the lower factors the views above are taken from
+            self._t_solver.to(device)
+            self._a_solver.to(device)
+            self.T, self.A = self._t_solver.L.mT, self._a_solver.L.mT
         return self
 
     @staticmethod
@@ -183,24 +200,33 @@ class FalkonPreconditioner(Preconditioner):
             out = torch.linalg.solve_triangular(tri, rhs, upper=True)
         return out.reshape(-1) if vec else out
 
+    # With the block solvers: A = L2^T, so A x = v is the transposed solve with L2 and A^T x = v the plain one.
     @_require_init
     def invA(self, v: torch.Tensor) -> torch.Tensor:
         """Solves A x = v."""
+        if self._a_solver is not None:
+            return self._a_solver.solve_t(v)
         return self._solve(self.A, v, transpose=False)
 
     @_require_init
     def invAt(self, v: torch.Tensor) -> torch.Tensor:
         """Solves A^T x = v."""
+        if self._a_solver is not None:
+            return self._a_solver.solve(v)
         return self._solve(self.A, v, transpose=True)
 
     @_require_init
     def invT(self, v: torch.Tensor) -> torch.Tensor:
         """Solves T x = v."""
+        if self._t_solver is not None:
+            return self._t_solver.solve_t(v)
         return self._solve(self.T, v, transpose=False)
 
     @_require_init
     def invTt(self, v: torch.Tensor) -> torch.Tensor:
         """Solves T^T x = v."""
+        if self._t_solver is not None:
+            return self._t_solver.solve(v)
         return self._solve(self.T, v, transpose=True)
 
     @_require_init

@@ -64,3 +64,26 @@ def test_blocked_cholesky(m, panel, trailing):
     assert info == m // 2 + 1  # order of the first leading minor that is not positive definite
     with pytest.raises(ValueError):
         cholesky_lower_3xtf32(K.double())
+
+
+@pytest.mark.parametrize("m,block", [(700, 128), (512, 128), (100, 128), (1, 4)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+def test_blocked_triangular_solves(m, block, dtype):
+    from falkon_b200.preconditioner.tri_solve import BlockedTriangular
+
+    g = torch.Generator().manual_seed(4)
+    L = torch.tril(torch.randn(m, m, generator=g, dtype=torch.float64)) + 20.0 * torch.eye(m, dtype=torch.float64)
+    L = L.to(dtype).contiguous()
+    bt = BlockedTriangular(L, block=block)
+    tol = 1e-4 if dtype == torch.float32 else 1e-12
+    for shape in ((m,), (m, 3)):
+        b = torch.randn(*shape, generator=g, dtype=torch.float64).to(dtype)
+        x = bt.solve(b)
+        assert x.shape == b.shape
+        assert float((L.double() @ x.double() - b.double()).abs().max()) < tol * 20
+        x = bt.solve_t(b)
+        assert float((L.double().T @ x.double() - b.double()).abs().max()) < tol * 20
+    with pytest.raises(ValueError):
+        bt.solve(torch.zeros(m + 1, dtype=dtype))
+    with pytest.raises(ValueError):
+        BlockedTriangular(L.t() if m > 1 else torch.zeros(2, 3, dtype=dtype))
