@@ -3,6 +3,8 @@ epilogues, one- and two-segment grids, chunked reductions) against the library's
 no code with them beyond the operand preparation.  Tolerance: rel-L2 <= 1e-4 (the fp32 bar), and the two
 products of an fdmmv must agree with each other (K^T u computed by fdmmv and by fmmv on swapped operands).
 """
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -13,9 +15,10 @@ pytestmark = pytest.mark.gpu
 
 
 def _cases():
-    rng = np.random.default_rng(20240607)
+    # FLK_FUZZ_SEED / FLK_FUZZ_CASES widen the sweep for a longer soak run
+    rng = np.random.default_rng(int(os.environ.get("FLK_FUZZ_SEED", "20240607")))
     out = []
-    for i in range(36):
+    for i in range(int(os.environ.get("FLK_FUZZ_CASES", "36"))):
         d = int(rng.choice([1, 2, 5, 9, 10, 19, 20, 28, 30, 31, 33, 64, 100, 200]))
         t = int(rng.choice([1, 1, 1, 2, 3, 4, 5, 8, 20, 33, 40]))
         n = int(rng.integers(1, 300_000)) if i % 3 else int(rng.integers(1, 3000))
@@ -62,3 +65,40 @@ def test_random_shape_against_fp64_kernels(case):
     o_w = k.dmmv(X, C, None, w)
     assert fo.rel_l2(o_w.cpu().numpy(), kt.cpu().numpy()) < 2e-5
     assert _lib.tc_status(X.device) == 0 and _lib.range_flag(X.device) == 0
+
+
+def _host_cases():
+    rng = np.random.default_rng(77)
+    out = []
+    for i in range(8):
+        n = int(rng.choice([1000, 262_144, 262_145, 300_001, 524_288, 700_000]))
+        m = int(rng.integers(1, 3000))
+        d = int(rng.choice([3, 9, 28, 40]))
+        t = int(rng.choice([1, 2, 5]))
+        out.append((i, n, m, d, t, ["gaussian", "laplacian", "matern15", "matern25"][i % 4], ["C", "F"][i % 2]))
+    return out
+
+
+HOST_CASES = _host_cases()
+
+
+@pytest.mark.parametrize("case", HOST_CASES, ids=[f"{c[5]}_n{c[1]}_m{c[2]}_d{c[3]}_t{c[4]}_{c[6]}" for c in HOST_CASES])
+def test_host_operands_match_device_operands(case):
+    """Host tensors (staged, from 262,144 rows on in row chunks through the copy stream) give the result of the
+    same call on device tensors, in either memory order."""
+    seed, n, m, d, t, name, order = case
+    g = torch.Generator().manual_seed(500 + seed)
+    X = torch.randn(n, d, generator=g)
+    C = torch.randn(m, d, generator=g)
+    v = torch.randn(m, t, generator=g)
+    w = torch.randn(n, t, generator=g)
+    if order == "F":
+        X, w = X.t().contiguous().t(), w.t().contiguous().t()
+    k = _kernel(name, 1.5 * float(d) ** 0.5)
+    k.params.flk_devices = [torch.cuda.current_device()]
+    dev = [a.cuda() for a in (X, C, v, w)]
+    got, want = k.dmmv(X, C, v, w), k.dmmv(*dev)
+    assert got.device.type == "cpu"
+    assert fo.rel_l2(got.numpy(), want.cpu().numpy()) < 1e-5
+    got, want = k.mmv(X, C, v), k.mmv(*dev[:3])
+    assert fo.rel_l2(got.numpy(), want.cpu().numpy()) < 1e-5
