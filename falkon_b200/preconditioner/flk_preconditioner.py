@@ -26,7 +26,7 @@ from ..options import FalkonOptions
 from .tensor_core_la import cholesky_lower_3xtf32, triu_times_transpose_3xtf32
 from .tri_solve import BlockedTriangular
 
-#: from this many centres on, the per-iteration triangular solves go through BlockedTriangular
+#: from this many centres on, the per-iteration triangular solves of an fp32 preconditioner go through BlockedTriangular
 _BLOCKED_SOLVE_MIN_M = 8192
 
 __all__ = ("Preconditioner", "FalkonPreconditioner")
@@ -173,7 +173,9 @@ class FalkonPreconditioner(Preconditioner):
             self.T, self.A = T, A
             # T = L^T and A = L2^T are kept as transposed views of the row-major lower factors
             self._t_solver = self._a_solver = None
-            if M >= _BLOCKED_SOLVE_MIN_M:
+            # fp32 only: multiplying with inverted diagonal blocks is not backward stable, and the fp64 factors of a
+            # kernel matrix with a 1e-13 jitter are ill-conditioned enough for that to show
+            if M >= _BLOCKED_SOLVE_MIN_M and L.dtype == torch.float32:
                 self._t_solver = BlockedTriangular(L)
                 self._a_solver = BlockedTriangular(L2)
         return self
