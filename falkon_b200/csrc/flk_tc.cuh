@@ -61,9 +61,11 @@ constexpr int kVecStages = 4;                       // ring of vector tiles
 constexpr uint64_t kWaitTimeoutNs = 1000000000ull;  // every device-side wait gives up after 1 s
 constexpr float kNormLimit = 60000.0f;              // largest half squared norm an image may carry
 #ifndef FLK_TC_POLY_PAIRS
-#define FLK_TC_POLY_PAIRS 6
+#define FLK_TC_POLY_PAIRS 4
 #endif
-// of the 16 column pairs of every 32-column accumulator piece, how many take the FMA-pipe exponential
+// of the 16 column pairs of every 32-column accumulator piece, how many take the FMA-pipe exponential (Gaussian;
+// measured on config 2 in 30-step runs under the board's power cap: 2 -> 9.89 ms per fdmmv, 3 -> 9.50, 4 -> 9.37 - 9.47,
+// 5 -> 9.59 - 9.64, 6 -> 9.79 - 9.87, 7 -> 10.10)
 constexpr int kPolyPairs = FLK_TC_POLY_PAIRS;
 
 // words of the 256-byte status block at the front of the workspace
