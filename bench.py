@@ -577,9 +577,9 @@ def main():
     tensor_tflops = evals_per_s * 2 * k_used / 1e12
     fp32_peak_tflops = 148 * 128 * 2 * sm_mhz * 1e6 / 1e12
     alg_flops_pair = 2 * D + 2 * T + 4 + 1
-    # DRAM traffic of one sweep launch: 217 bytes per row of X, from the ncu capture at 400,000 rows
-    # (80.9 MB read + 6.1 MB written; algorithmic 84 MB), scaled by rows (traffic is proportional to rows)
-    traffic = 217.0 * n if uses_tc else None
+    # DRAM traffic of one sweep launch: 210 bytes per row of X, from the ncu capture at 400,000 rows
+    # (80.9 MB read + 3.1 MB written; algorithmic 84 MB), scaled by rows (traffic is proportional to rows)
+    traffic = 210.0 * n if uses_tc else None
     alg_bytes = (n * (3 * D + 6 + 6) * 2.0 + M * 96 * 2.0 + n * 4.0 + M * 4.0) if uses_tc else None
     roofline = {
         "bound": "mufu" if uses_tc else "fp32",

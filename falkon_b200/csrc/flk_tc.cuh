@@ -545,7 +545,13 @@ enum { kErrProducer = 0x10, kErrMma = 0x20, kErrEpilogue = 0x30 };
 // FMA work per value), spread evenly over the piece so both pipes have work throughout.
 template <int KT>
 __host__ __device__ constexpr int poly_pairs_of() {
-  return KT == FLK_GAUSSIAN ? kPolyPairs : (KT == FLK_MATERN25 ? 5 : 8);
+#ifndef FLK_TC_POLY_PAIRS_LM
+#define FLK_TC_POLY_PAIRS_LM 8
+#endif
+#ifndef FLK_TC_POLY_PAIRS_M25
+#define FLK_TC_POLY_PAIRS_M25 5
+#endif
+  return KT == FLK_GAUSSIAN ? kPolyPairs : (KT == FLK_MATERN25 ? FLK_TC_POLY_PAIRS_M25 : FLK_TC_POLY_PAIRS_LM);
 }
 template <int KT>
 __host__ __device__ constexpr bool poly_pair(int pr) {
