@@ -210,13 +210,42 @@ def _sigma_args(sigma: np.ndarray):
     return sigma, sigma.ctypes.data_as(_dp), sigma.shape[0]
 
 
+def _check_operands(host: bool, **named):
+    """Last line of defence before raw pointers cross the C ABI: every operand is a 2-D tensor of the expected
+    shape, all share one dtype, and all live where the entry point will look for them (one CUDA device, or host
+    memory for the host-buffer entry points).  A mismatch here would otherwise become an out-of-bounds access
+    on the device; the reference raises a torch error for the same mistake."""
+    tensors = {k: v for k, v in named.items() if v[0] is not None}
+    dtype = device = None
+    for name, (t, shape) in tensors.items():
+        if not isinstance(t, torch.Tensor):
+            raise TypeError(f"{name} must be a torch.Tensor, not {type(t).__name__}")
+        if t.dim() != 2:
+            raise ValueError(f"{name} must be 2-D, found {t.dim()}-D")
+        if tuple(t.shape) != tuple(shape):
+            raise ValueError(f"{name} has shape {tuple(t.shape)}, expected {tuple(shape)}")
+        if dtype is None:
+            dtype, device = t.dtype, t.device
+        if t.dtype != dtype:
+            raise TypeError(f"Data types of input matrices must be equal ({name} is {t.dtype}, expected {dtype}).")
+        if host:
+            if t.device.type != "cpu":
+                raise ValueError(f"{name} must be in host memory for the host-buffer entry points (found {t.device})")
+        else:
+            if t.device.type != "cuda":
+                raise ValueError(f"{name} must be on a CUDA device (found {t.device})")
+            if t.device != device:
+                raise ValueError(f"All operands must be on the same device ({name} is on {t.device}, expected {device})")
+
+
 def call_fmmv(kernel_id, sigma, X1, X2, v, out, flags=0, host=False, device=None):
     """out[n, t] = k(X1, X2) v through the C ABI (device pointers, or host pointers with host=True)."""
     lib = load()
     dt = dtype_code(X1.dtype)
     n, d = X1.shape
     m = X2.shape[0]
-    t = v.shape[1]
+    t = v.shape[1] if v.dim() == 2 else -1
+    _check_operands(host, X1=(X1, (n, d)), X2=(X2, (m, d)), v=(v, (m, t)), out=(out, (n, t)))
     dev = device if host else X1.device
     query = lib.flk_fmmv_host_workspace_bytes if host else lib.flk_fmmv_workspace_bytes
     need = query(dt, kernel_id, n, m, d, t, flags)
@@ -242,7 +271,11 @@ def call_fdmmv(kernel_id, sigma, X1, X2, v, w, out, flags=0, host=False, device=
     dt = dtype_code(X1.dtype)
     n, d = X1.shape
     m = X2.shape[0]
-    t = v.shape[1] if v is not None else w.shape[1]
+    if v is None and w is None:
+        raise ValueError("One of v and w must be specified to run fdMMV.")
+    lead = v if v is not None else w
+    t = lead.shape[1] if lead.dim() == 2 else -1
+    _check_operands(host, X1=(X1, (n, d)), X2=(X2, (m, d)), v=(v, (m, t)), w=(w, (n, t)), out=(out, (m, t)))
     dev = device if host else X1.device
     query = lib.flk_fdmmv_host_workspace_bytes if host else lib.flk_fdmmv_workspace_bytes
     need = query(dt, kernel_id, n, m, d, t, flags)
@@ -269,6 +302,7 @@ def call_fmm(kernel_id, sigma, X1, X2, out, flags=0):
     n, d = X1.shape
     m = X2.shape[0]
     dev = X1.device
+    _check_operands(False, X1=(X1, (n, d)), X2=(X2, (m, d)), out=(out, (n, m)))
     need = lib.flk_fmm_workspace_bytes(dt, n, m, d, flags)
     if need < 0:
         raise_for_status(int(need))
@@ -290,6 +324,11 @@ def call_kgrad(kernel_id, sigma, X1, X2, G, v, out, flags=0):
     n, d = X1.shape
     m = X2.shape[0]
     dev = X1.device
+    if v is None:
+        _check_operands(False, X1=(X1, (n, d)), X2=(X2, (m, d)), G=(G, (n, m)), out=(out, (n, m)))
+    else:
+        tg = G.shape[1] if G.dim() == 2 else -1
+        _check_operands(False, X1=(X1, (n, d)), X2=(X2, (m, d)), G=(G, (n, tg)), v=(v, (m, tg)), out=(out, (n, m)))
     need = lib.flk_fmm_workspace_bytes(dt, n, m, d, flags)
     if need < 0:
         raise_for_status(int(need))
@@ -305,6 +344,32 @@ def call_kgrad(kernel_id, sigma, X1, X2, G, v, out, flags=0):
                                ctypes.c_void_p(G.data_ptr()), G.stride(0), G.stride(1), *v_args,
                                *_mat_args(out, with_rows=False), sig_ptr, sig_len,
                                ctypes.c_void_p(ws.data_ptr()), ws.numel(), flags, stream)
+    del keep
+    raise_for_status(status)
+    return out
+
+
+def call_square_norm(X, sigma=None, out=None):
+    """out[n] = sum_k (X[i, k] / sigma)^2 through the C ABI (device pointers; ``sigma`` a scalar or None)."""
+    lib = load()
+    dt = dtype_code(X.dtype)
+    if X.dim() != 2:
+        raise ValueError(f"X must be 2-D, found {X.dim()}-D")
+    if X.device.type != "cuda":
+        raise ValueError(f"X must be on a CUDA device (found {X.device})")
+    n, d = X.shape
+    if out is None:
+        out = torch.empty(n, dtype=X.dtype, device=X.device)
+    if out.shape != (n,) or out.dtype != X.dtype or out.device != X.device or (n > 1 and out.stride(0) != 1):
+        raise ValueError("out must be a dense vector of n entries with the dtype and device of X")
+    if sigma is None:
+        keep, sig_ptr, sig_len = None, None, 0
+    else:
+        keep, sig_ptr, sig_len = _sigma_args(np.atleast_1d(np.asarray(sigma, dtype=np.float64)))
+    with torch.cuda.device(X.device):
+        stream = ctypes.c_void_p(torch.cuda.current_stream(X.device).cuda_stream)
+        status = lib.flk_square_norm(dt, ctypes.c_void_p(X.data_ptr()), n, d, X.stride(0), X.stride(1), sig_ptr,
+                                     sig_len, ctypes.c_void_p(out.data_ptr()), stream)
     del keep
     raise_for_status(status)
     return out

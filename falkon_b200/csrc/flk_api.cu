@@ -394,12 +394,13 @@ static int run_prep_vec(const Mat& v, void* vbuf, int64_t s_pad, int tp, int tt,
 
 template <typename T>
 static int run_finalize(const SweepPlan& sp, const void* raw, const Mat* add, void* out, int64_t out_rs,
-                        int64_t out_cs, int64_t t, bool padded, Gate gate, cudaStream_t stream) {
+                        int64_t out_cs, int64_t t, bool padded, Gate gate, cudaStream_t stream,
+                        const int* timeout_word = nullptr) {
   finalize_kernel<T><<<grid_for(sp.r_pad * sp.tp), 256, 0, stream>>>(
       reinterpret_cast<const T*>(raw), sp.n_chunks, sp.r_pad, sp.tp, sp.r, (int)t,
       add ? reinterpret_cast<const T*>(add->ptr) : nullptr, add ? add->rs : 0, add ? add->cs : 0,
       reinterpret_cast<T*>(out), out_rs, out_cs, padded ? 1 : 0, sp.tt, (int64_t)sp.main_tiles * sp.br,
-      sp.n_chunks_tail, gate);
+      sp.n_chunks_tail, gate, timeout_word);
   count_launch();
   FLK_CUDA_TRY(cudaGetLastError());
   return FLK_OK;
@@ -515,7 +516,8 @@ static int sweep_and_finalize(const Layout& L, int kernel, int dtype, int64_t d,
   const int ld = ld_for(dtype, d);
   if (L.tc) {
     FLK_TRY(run_sweep_tc(kernel, tcp, a.img_a, b.img_b, d, vec, raw, L.status, stream, sweep_idx));
-    FLK_TRY(run_finalize<T>(tcp, raw, add, out, out_rs, out_cs, t, padded, gate_tc(L), stream));
+    FLK_TRY(run_finalize<T>(tcp, raw, add, out, out_rs, out_cs, t, padded, gate_tc(L), stream,
+                            reinterpret_cast<const int*>(L.status) + tc::kStatusTimeout));
     FLK_TRY(run_sweep_simt<T>(kernel, fp, a, b, ld, vec, fraw, gate_simt(L), stream, sweep_idx));
     FLK_TRY(run_finalize<T>(fp, fraw, add, out, out_rs, out_cs, t, padded, gate_simt(L), stream));
   } else {

@@ -152,6 +152,9 @@ __global__ void __launch_bounds__(256) prep_vec_kernel(const T* __restrict__ v, 
 //   mode 0: out[r x t] with the caller's strides,
 //   mode 1: a padded buffer in the column-chunked layout out[t_chunks][r_pad][tt] whose rows >= r
 //           and columns >= t are zero (it becomes the vector operand of the second sweep of fdmmv).
+// `timeout_word` (tensor-core sweeps only, else null): when a bounded wait of the sweep gave up, CTAs of that
+// launch left their partials unwritten; every live result is then stored as NaN, so that a caller who never
+// reads the status word cannot mistake the garbage for a product.
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(256) finalize_kernel(const T* __restrict__ raw, int n_chunks,
@@ -159,8 +162,10 @@ __global__ void __launch_bounds__(256) finalize_kernel(const T* __restrict__ raw
                                                        const T* __restrict__ add, int64_t add_rs,
                                                        int64_t add_cs, T* __restrict__ out,
                                                        int64_t out_rs, int64_t out_cs, int padded_out,
-                                                       int tt, int64_t main_rows, int n_chunks_tail, Gate gate) {
+                                                       int tt, int64_t main_rows, int n_chunks_tail, Gate gate,
+                                                       const int* __restrict__ timeout_word) {
   if (!gate_open(gate)) return;
+  const bool poisoned = timeout_word != nullptr && *reinterpret_cast<const volatile int*>(timeout_word) != 0;
   int64_t total = r_pad * tp;
   for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (int64_t)gridDim.x * blockDim.x) {
@@ -172,6 +177,7 @@ __global__ void __launch_bounds__(256) finalize_kernel(const T* __restrict__ raw
       const int nch = i < main_rows ? n_chunks : n_chunks_tail;
       for (int ch = 0; ch < nch; ++ch) acc += raw[(int64_t)ch * total + idx];
       if (add != nullptr) acc += add[i * add_rs + (int64_t)c * add_cs];
+      if (poisoned) acc = (T)NAN;
     }
     if (padded_out) {
       out[chunked_index(i, c, r_pad, tt)] = acc;

@@ -53,9 +53,16 @@ class DiffKernel(Kernel):
         return self._other_params
 
     def compute(self, X1, X2, out, diag, **kwargs):
-        raise NotImplementedError(
-            "falkon_b200 never forms kernel blocks in memory; dense blocks are available from the reference package."
-        )
+        """Dense kernel block ``k(X1, X2)`` written into ``out`` (n x m, or (n,) with ``diag=True``) and returned:
+        the extension point of falkon/kernels/diff_kernel.py:90-91 (``core_fn(X1, X2, out=out, diag=diag,
+        **params)``).  The block is evaluated by ``flk_fmm`` in the dtype of the data, as the reference's core
+        functions do (the fp64 upcast of ``no_single_kernel`` belongs to ``fmm``, not to ``compute``).  The
+        products ``mmv`` / ``dmmv`` never call this: they do not form the block."""
+        from ..mmv_ops.fmm import compute_block
+
+        if kwargs:
+            raise NotImplementedError("Distance kernels take no per-row keyword tensors.")
+        return compute_block(self, X1, X2, out, diag)
 
     def dmmv(self, X1, X2, v, w, out=None, opt=None):
         """Same entry as falkon/kernels/diff_kernel.py:127-145: validates, then calls the chosen

@@ -6,7 +6,6 @@ merging (:283-285), and the implementation-choice hooks ``_decide_mmv_impl`` /
 ``_decide_dmmv_impl`` (:298-334, :419-459) through which a backend is plugged in.  The hooks here
 return the CUDA-backed :func:`falkon_b200.mmv_ops.fmmv` / :func:`fdmmv`.
 """
-import dataclasses
 from abc import ABC, abstractmethod
 from typing import Dict, Optional
 
@@ -14,7 +13,7 @@ import torch
 
 from ..mmv_ops.fmm import fmm
 from ..mmv_ops.fmmv import fdmmv, fmmv
-from ..options import FalkonOptions
+from ..options import FalkonOptions, merge_options
 
 
 def _same_dtype(*tensors) -> bool:
@@ -96,9 +95,7 @@ class Kernel(torch.nn.Module, ABC):
             raise RuntimeError(f"All input arguments to {fn_name} must be on the same device")
 
     def _merged(self, opt: Optional[FalkonOptions]) -> FalkonOptions:
-        if opt is None:
-            return self.params
-        return dataclasses.replace(self.params, **dataclasses.asdict(opt))
+        return merge_options(self.params, opt)
 
     # ---- the kernel matrix itself (falkon/kernels/kernel.py:135-193) ----
     @staticmethod

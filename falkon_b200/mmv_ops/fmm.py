@@ -15,7 +15,7 @@ from ..options import BaseOptions
 from .fmmv import _dense_grad, _is_sparse, _kernel_spec, _pick_device, _require_cuda, _to_dev
 from .utils import check_contiguity, create_same_stride
 
-__all__ = ("fmm", "KernelMmFn")
+__all__ = ("fmm", "KernelMmFn", "compute_block")
 
 
 def _diag_kernel(X1, X2, kernel_id, sigma, out):
@@ -146,3 +146,19 @@ def fmm(
         names = tuple(diff_params.keys())
         return KernelMmFn.apply(kernel, opt, out, names, X1, X2, *diff_params.values())
     return _fmm_forward(kernel, opt, out, diag, X1, X2)
+
+
+class _PlainMath:
+    """Options stand-in for ``compute_block``: evaluate in the dtype of the data."""
+
+    no_single_kernel = False
+    use_cpu = False
+
+
+def compute_block(kernel, X1: torch.Tensor, X2: torch.Tensor, out: Optional[torch.Tensor], diag: bool) -> torch.Tensor:
+    """``Kernel.compute``: the dense block (or its diagonal) into ``out``, in the data's own precision.
+    Validates like ``Kernel.__call__``; differentiable like ``fmm``."""
+    from ..kernels.kernel import Kernel
+
+    X1, X2, out = Kernel._check_mm_dimensions(X1, X2, diag, out)
+    return fmm(kernel, _PlainMath, out, diag, X1, X2)

@@ -21,6 +21,8 @@ __all__ = (
     "PreconditionerOptions",
     "CholeskyOptions",
     "FalkonOptions",
+    "EXTRA_ATTRS",
+    "merge_options",
 )
 
 
@@ -109,3 +111,29 @@ class FalkonOptions(BaseOptions, ConjugateGradientOptions, PreconditionerOptions
     """Global options; the union of all option groups (falkon/options.py:293-303)."""
 
     pass
+
+
+# Attributes of this package that are not fields of the reference's option classes (so that the field list
+# stays the reference's): plain attributes set on an option object.
+#   flk_flags        FLK_FLAG_* bits handed to the C ABI (force the SIMT or the tensor-core kernels)
+#   flk_devices      list of CUDA ordinals a host-operand product may spread over
+#   pc_tensor_cores  False selects the library factorisations in the fp32 preconditioner
+EXTRA_ATTRS = ("flk_flags", "flk_devices", "pc_tensor_cores")
+
+
+def merge_options(base, override):
+    """Options of one call: ``override``'s fields on top of ``base`` (falkon/kernels/kernel.py:283-285).
+
+    ``dataclasses.replace`` rebuilds the object from its fields and so drops the extra attributes above;
+    they are carried over here: ``base``'s first, then ``override``'s where it sets them."""
+    import dataclasses
+
+    if override is None:
+        return base
+    fields = {f.name for f in dataclasses.fields(base)}
+    merged = dataclasses.replace(base, **{k: v for k, v in dataclasses.asdict(override).items() if k in fields})
+    for src in (base, override):
+        for name in EXTRA_ATTRS:
+            if name in getattr(src, "__dict__", {}):
+                setattr(merged, name, getattr(src, name))
+    return merged

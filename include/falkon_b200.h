@@ -73,10 +73,15 @@ int flk_check_device(void);
 int flk_uses_tensor_cores(int dtype, int kernel, int64_t d, int64_t t, int flags);
 
 /*
- * Row-wise squared norms of X / sigma:  out[i] = sum_k (X[i,k] / sigma[k])^2 , out has n entries.
+ * Row-wise squared norms of X / sigma:  out[i] = sum_k (X[i,k] / sigma)^2 , out has n entries, summed in
+ * column order in the data's own precision (as the reference accumulates).
  * Replaces falkon::square_norm as the distance kernels call it
- * (falkon/c_ext/ops/square_norm.cpp:23-26; call sites falkon/kernels/distance_kernel.py:153-154).
- * sigma may be NULL (no scaling).  Needs no workspace.
+ * (falkon/c_ext/ops/square_norm.cpp:23-26, CUDA falkon/c_ext/ops/cuda/cuda_square_norm.cu:48-61; call
+ * sites falkon/kernels/distance_kernel.py:153-154).  X is a DEVICE pointer in either memory order.
+ * sigma_host may be NULL (no scaling) or point at ONE length-scale (sigma_len = 1): the reference's
+ * routine takes no scaling at all, the scalar is a convenience.  A per-dimension vector (sigma_len = d
+ * > 1) is refused with FLK_ERR_UNSUPPORTED: the call has no workspace to stage it in; scale the data
+ * first, or use the products, which take the vector.  Needs no workspace.
  */
 int flk_square_norm(int dtype, const void* X, int64_t n, int64_t d, int64_t x_rs, int64_t x_cs,
                     const double* sigma_host, int64_t sigma_len, void* out, void* stream);

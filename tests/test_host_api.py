@@ -143,3 +143,71 @@ def test_falkon_constructor_validation():
         model.predict(torch.randn(4, 3))
     with pytest.raises(ValueError, match="same number of samples"):
         model.fit(torch.randn(20, 3), torch.randn(19, 1))
+
+
+def test_option_merge_keeps_the_extra_attributes():
+    """``dataclasses.replace`` drops attributes that are not dataclass fields; the per-call merge must carry
+    flk_flags / flk_devices / pc_tensor_cores from the kernel's own options and let the call's options override."""
+    from falkon_b200.options import merge_options
+
+    base = FalkonOptions(debug=True)
+    base.flk_flags = _lib.FLAG_FORCE_SIMT
+    base.flk_devices = [1]
+    k = GaussianKernel(1.0, opt=base)
+    assert k._merged(None) is base
+    call = FalkonOptions(max_gpu_mem=5.0)
+    m = k._merged(call)
+    assert m.max_gpu_mem == 5.0 and m.debug is False  # fields: the call's options win, as in the reference
+    assert m.flk_flags == _lib.FLAG_FORCE_SIMT and m.flk_devices == [1]  # extras survive the merge
+    call.flk_flags = _lib.FLAG_FORCE_TC
+    m = k._merged(call)
+    assert m.flk_flags == _lib.FLAG_FORCE_TC and m.flk_devices == [1]
+    assert not hasattr(merge_options(FalkonOptions(), FalkonOptions()), "flk_flags")
+    # a narrower option object (the reference passes BaseOptions subsets around) merges field by field
+    from falkon_b200.options import BaseOptions
+
+    assert merge_options(base, BaseOptions(max_cpu_mem=7.0)).max_cpu_mem == 7.0
+
+
+def test_c_abi_guard_rejects_mismatched_operands():
+    """The ctypes layer refuses operands whose shape, dtype or placement disagree before any pointer reaches the
+    library (the kernels trust the sizes they are given)."""
+    X, C, v, w = torch.randn(10, 3), torch.randn(4, 3), torch.randn(4, 2), torch.randn(10, 2)
+    out_m, out_n = torch.empty(4, 2), torch.empty(10, 2)
+    sig = np.array([1.0])
+    with pytest.raises(ValueError, match="v has shape"):
+        _lib.call_fmmv(0, sig, X, C, torch.randn(5, 2), out_n, host=True)
+    with pytest.raises(ValueError, match="out has shape"):
+        _lib.call_fmmv(0, sig, X, C, v, torch.empty(9, 2), host=True)
+    with pytest.raises(TypeError, match="Data types"):
+        _lib.call_fmmv(0, sig, X, C, v.double(), out_n, host=True)
+    with pytest.raises(ValueError, match="X2 has shape"):
+        _lib.call_fmmv(0, sig, X, torch.randn(4, 5), v, out_n, host=True)
+    with pytest.raises(ValueError, match="w has shape"):
+        _lib.call_fdmmv(0, sig, X, C, v, torch.randn(9, 2), out_m, host=True)
+    with pytest.raises(ValueError, match="out has shape"):
+        _lib.call_fdmmv(0, sig, X, C, v, w, torch.empty(4, 3), host=True)
+    with pytest.raises(TypeError, match="Data types"):
+        _lib.call_fdmmv(0, sig, X, C, v, w.double(), out_m, host=True)
+    with pytest.raises(ValueError, match="One of v and w"):
+        _lib.call_fdmmv(0, sig, X, C, None, None, out_m, host=True)
+    with pytest.raises(ValueError, match="must be 2-D"):
+        _lib.call_fmmv(0, sig, X, C, v[:, 0], out_n, host=True)
+    with pytest.raises(ValueError, match="CUDA device"):
+        _lib.call_fmmv(0, sig, X, C, v, out_n)  # device entry point given host tensors
+    with pytest.raises(ValueError, match="CUDA device"):
+        _lib.call_fmm(0, sig, X, C, torch.empty(10, 4))
+    with pytest.raises(ValueError, match="CUDA device"):
+        _lib.call_kgrad(0, sig, X, C, torch.randn(10, 2), v, torch.empty(10, 4))
+
+
+def test_falkon_passes_extra_attributes_down():
+    """The estimator hands its options to every product as ``opt=``; a forced tensor-core path on fp64 data must
+    therefore surface as NotImplementedError from inside fit, not be silently dropped.  Checked here through the
+    merge alone (no GPU): the options the products see carry the flag."""
+    from falkon_b200 import Falkon
+
+    o = FalkonOptions()
+    o.flk_flags = _lib.FLAG_FORCE_TC
+    model = Falkon(kernel=GaussianKernel(1.0), penalty=1e-3, M=5, options=o)
+    assert model.kernel._merged(model.options).flk_flags == _lib.FLAG_FORCE_TC
