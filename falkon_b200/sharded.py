@@ -39,6 +39,9 @@ class ShardedKernelOps:
         self.group = group
         self._mmv = local_mmv if local_mmv is not None else kernel.mmv
         self._dmmv = local_dmmv if local_dmmv is not None else kernel.dmmv
+        # measurement hook: when set to a list, every all-reduce of a CUDA tensor appends a (start, end) pair of
+        # CUDA events recorded on the current stream around the collective
+        self.collective_events = None
 
     @property
     def world(self) -> int:
@@ -47,6 +50,16 @@ class ShardedKernelOps:
     def _all_reduce(self, t: torch.Tensor) -> torch.Tensor:
         if self.world == 1:
             return t
+        if self.collective_events is not None and t.device.type == "cuda":
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            self._all_reduce_untimed(t)
+            e1.record()
+            self.collective_events.append((e0, e1))
+            return t
+        return self._all_reduce_untimed(t)
+
+    def _all_reduce_untimed(self, t: torch.Tensor) -> torch.Tensor:
         backend = dist.get_backend(self.group)
         if backend == "nccl" and t.device.type != "cuda":
             tmp = t.to(torch.device("cuda", torch.cuda.current_device()))

@@ -9,6 +9,13 @@ for p in (ROOT, os.path.join(ROOT, "tests", "golden")):
         sys.path.insert(0, p)
 
 
+# The reference package, when oracle/build_ref.py has built it (test infrastructure; used by the drop-in tests).
+# Appended, so that a reference the user put on PYTHONPATH wins.
+_REF_SITE = os.path.join(ROOT, "oracle", "_ref", "site")
+if os.path.isdir(os.path.join(_REF_SITE, "falkon")) and _REF_SITE not in sys.path:
+    sys.path.append(_REF_SITE)
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: test needs a CUDA device (run on the B200 box)")
 
