@@ -20,7 +20,7 @@ LIB_PATH = os.environ.get("FALKON_B200_LIB") or os.path.join(_HERE, "libfalkon_b
 
 FLK_F32, FLK_F64 = 0, 1
 FLK_GAUSSIAN, FLK_LAPLACIAN, FLK_MATERN15, FLK_MATERN25 = 0, 1, 2, 3
-FLAG_FORCE_SIMT, FLAG_FORCE_TC, FLAG_FP64_MATH = 1, 2, 4
+FLAG_FORCE_SIMT, FLAG_FORCE_TC, FLAG_FP64_MATH, FLAG_NO_FOLD, FLAG_ACCUMULATE = 1, 2, 4, 8, 16
 STATIC_SCRATCH_BYTES = 64 << 20
 
 FLK_ERR_BAD_ARG, FLK_ERR_LAYOUT, FLK_ERR_WORKSPACE = -1, -2, -3
@@ -28,8 +28,16 @@ FLK_ERR_CUDA, FLK_ERR_UNSUPPORTED, FLK_ERR_DEVICE, FLK_ERR_TIMEOUT = -4, -5, -6,
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-    "-Xcompiler", "-fPIC", "-shared",
+    "-Xcompiler", "-fPIC", "-shared", "-Xptxas", "-v",
 ]
+PTXAS_REPORT = LIB_PATH + ".ptxas.txt"
+# The tensor-core sweeps read their accumulators with asynchronous tcgen05.ld: a register that such a load is still
+# to fill must never be spilled, so the resident kernel has to compile without any spill.  It re-partitions
+# registers between its warp roles and relies on being launched with exactly this many per thread:
+TC_LAUNCH_REGISTERS = 80
+# The K-loop kernel still spills a few bytes outside its hot loop in some instantiations; the build tolerates up
+# to this many bytes there and fails beyond (a regression guard, not an endorsement).
+TCK_SPILL_ALLOWANCE = 64
 
 _lock = threading.Lock()
 _lib: Optional[ctypes.CDLL] = None
@@ -64,7 +72,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
                 return LIB_PATH
             tmp = f"{LIB_PATH}.{os.getpid()}.tmp"
             nvcc = os.environ.get("NVCC", "nvcc")
-            cmd = [nvcc] + NVCC_FLAGS + ["-o", tmp, os.path.join(_CSRC, "flk_api.cu")]
+            extra = os.environ.get("FALKON_B200_NVCC_EXTRA", "").split()  # e.g. -D tuning macros of the kernels
+            cmd = [nvcc] + NVCC_FLAGS + extra + ["-o", tmp, os.path.join(_CSRC, "flk_api.cu")]
             if verbose:
                 print(" ".join(cmd))
             res = subprocess.run(cmd, capture_output=True, text=True)
@@ -72,10 +81,65 @@ def build(force: bool = False, verbose: bool = False) -> str:
                 if os.path.exists(tmp):
                     os.remove(tmp)
                 raise RuntimeError(f"nvcc failed:\n{res.stdout}\n{res.stderr}")
+            table = parse_ptxas(res.stderr)
+            problems = check_ptxas(table)
+            with open(PTXAS_REPORT, "w") as f:
+                f.write(format_ptxas(table))
+            if problems:
+                os.remove(tmp)
+                raise RuntimeError("register check of the tensor-core kernels failed:\n" + "\n".join(problems))
             os.replace(tmp, LIB_PATH)
         finally:
             fcntl.flock(lock, fcntl.LOCK_UN)
     return LIB_PATH
+
+
+def parse_ptxas(text: str):
+    """[(kernel name, registers, stack bytes, spill-store bytes, spill-load bytes)] from `ptxas -v` output."""
+    import re
+
+    pat = re.compile(
+        r"Compiling entry function '(\S+)' for 'sm_100a'\s*\n.*?Function properties for \S+\s*\n"
+        r"\s*(\d+) bytes stack frame, (\d+) bytes spill stores, (\d+) bytes spill loads\s*\n"
+        r".*?Used (\d+) registers", re.S)
+    rows = pat.findall(text)
+    if not rows:
+        return []
+    try:
+        names = subprocess.run(["c++filt"], input="\n".join(r[0] for r in rows), capture_output=True,
+                               text=True).stdout.split("\n")
+    except OSError:
+        names = [r[0] for r in rows]
+    out = []
+    for (mangled, stack, st, ld, regs), name in zip(rows, names):
+        name = re.sub(r"\(.*$", "", name).replace("void ", "").strip() or mangled
+        out.append((name, int(regs), int(stack), int(st), int(ld)))
+    return sorted(out)
+
+
+def check_ptxas(table):
+    """Problems (strings) that make the build fail: any spill in the resident tensor-core kernel, a launch register
+    count other than the one its register re-partitioning assumes, more than the allowance in the K-loop kernel."""
+    problems = []
+    seen_tc = False
+    for name, regs, stack, st, ld in table:
+        if "tc::kmv_tc_kernel" in name:
+            seen_tc = True
+            if st or ld:
+                problems.append(f"{name}: {st} bytes of spill stores, {ld} of spill loads (must be 0)")
+            if regs != TC_LAUNCH_REGISTERS:
+                problems.append(f"{name}: launched with {regs} registers per thread, {TC_LAUNCH_REGISTERS} assumed")
+        elif "tck::kmv_tck_kernel" in name and max(st, ld) > TCK_SPILL_ALLOWANCE:
+            problems.append(f"{name}: {st} / {ld} bytes of spill stores / loads exceed the allowance")
+    if table and not seen_tc:
+        problems.append("no tc::kmv_tc_kernel instantiation found in the ptxas output")
+    return problems
+
+
+def format_ptxas(table) -> str:
+    lines = ["kernel | registers | stack bytes | spill stores | spill loads", "---|---|---|---|---"]
+    lines += [f"{n} | {r} | {k} | {a} | {b}" for n, r, k, a, b in table]
+    return "\n".join(lines) + "\n"
 
 
 _i64, _int, _vp = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p

@@ -6,6 +6,7 @@
 #include "flk_common.cuh"
 #include "flk_dmma.cuh"
 #include "flk_fmm.cuh"
+#include "flk_fold.cuh"
 #include "flk_grad.cuh"
 #include "flk_prep.cuh"
 #include "flk_simt.cuh"
@@ -91,6 +92,7 @@ static int check_mat(const char* name, const Mat& m, bool nullable) {
 struct SweepPlan {
   bool tc;            // tensor-core kernel?
   bool kloop;         // ... its K-loop variant for many features (flk_tck.cuh: 256-row CTAs, operands streamed)
+  bool fold;          // ... with the vector folded into the reduction-side image (flk_fold.cuh; one tile more)
   int64_t r, s;       // live rows on the output / reduction side
   int64_t r_pad, s_pad;
   int tt, tp, t_chunks;
@@ -138,10 +140,11 @@ static bool wide_pays_off(bool tc, int dtype, int kernel, int64_t d, int64_t t) 
 // `allow_wide`: the plan may group 32 vector columns per pass.  The SIMT alternative of a tensor-core plan shares
 // its vector buffers and therefore must be planned with the same column grouping.
 static SweepPlan plan_sweep(bool tc, int dtype, int64_t r, int64_t s, int64_t t, bool allow_wide = false,
-                            bool kloop = false) {
+                            bool kloop = false, bool fold = false) {
   SweepPlan p;
   p.tc = tc;
   p.kloop = tc && kloop;
+  p.fold = tc && fold;
   p.r = r;
   p.s = s;
   p.r_pad = round_up(std::max<int64_t>(r, 1), kRowPad);
@@ -156,7 +159,7 @@ static SweepPlan plan_sweep(bool tc, int dtype, int64_t r, int64_t s, int64_t t,
     p.bc = (dtype == FLK_F32) ? 128 : 64;
   }
   p.row_tiles = (int)ceil_div(std::max<int64_t>(r, 1), p.br);
-  p.n_col_tiles = (int)ceil_div(std::max<int64_t>(s, 1), p.bc);
+  p.n_col_tiles = p.fold ? tc::fold_tiles(s) : (int)ceil_div(std::max<int64_t>(s, 1), p.bc);
   const int64_t resident = tc ? 1 : (p.tt == 1 ? 2 : 1);  // CTAs per SM (launch bounds of kmv_simt_kernel)
   const int64_t slots = kNumSMs * resident;
   if (!tc) {
@@ -261,6 +264,8 @@ struct Operand {
 
 struct Layout {
   bool tc;
+  bool fold = false;       // Gaussian, t = 1, resident tensor-core kernel: vector folded into the B images
+  int* blk_pos = nullptr;  // fold: scratch of the sign partition (one int per 128 rows of the larger operand)
   int64_t total = 0;
   void* status = nullptr;  // 256 bytes: device status word of the tensor-core kernel
   void* sigma = nullptr;   // d entries of T (per-dimension length-scales)
@@ -276,6 +281,9 @@ struct Layout {
   void* fraw2 = nullptr;
   SweepPlan f1, f2;
   int* range_flag() const { return reinterpret_cast<int*>(status) + tc::kStatusRange; }
+  int* fold_block(int sweep_idx) const {
+    return reinterpret_cast<int*>(status) + (sweep_idx == 0 ? tc::kFoldWordsSweep1 : tc::kFoldWordsSweep2);
+  }
 };
 
 // need_x1_as_b / need_x2_as_a: which tensor-core images each operand needs.
@@ -289,18 +297,22 @@ static Layout make_layout(void* ws, bool dmmv, bool has_v, int dtype, int kernel
   L.sigma = c.take(std::max<int64_t>(d, 1) * es);
   const bool kloop = L.tc && tck::supports_d(d);
   const bool wide_ok = wide_pays_off(L.tc, dtype, kernel, d, t);  // every path has a 32-columns-per-pass kernel
-  L.s1 = plan_sweep(L.tc, dtype, n, m, t, wide_ok, kloop);  // rows = X1, reduction over X2
-  L.s2 = plan_sweep(L.tc, dtype, m, n, t, wide_ok, kloop);  // rows = X2, reduction over X1 (fdmmv only)
+  L.fold = L.tc && !kloop && kernel == FLK_GAUSSIAN && t == 1 && !(flags & FLK_FLAG_NO_FOLD);
+  L.s1 = plan_sweep(L.tc, dtype, n, m, t, wide_ok, kloop, L.fold);  // rows = X1, reduction over X2
+  L.s2 = plan_sweep(L.tc, dtype, m, n, t, wide_ok, kloop, L.fold);  // rows = X2, reduction over X1 (fdmmv only)
   const int64_t n_pad = L.s1.r_pad, m_pad = L.s1.s_pad;
   const bool first = !dmmv || has_v;  // is the first sweep executed?
   if (L.tc) {
     const int64_t kp = kloop ? tck::padded_k(d) : tc::padded_k(d);
+    // a folded reduction-side image has one tile more than the operand has (see flk_fold.cuh)
+    const int64_t n_rows_b = L.fold ? tc::fold_image_rows(n) : n_pad, m_rows_b = L.fold ? tc::fold_image_rows(m) : m_pad;
     if (first) L.x1.img_a = c.take(n_pad * kp * 2);
-    if (first) L.x2.img_b = c.take(m_pad * kp * 2);
+    if (first) L.x2.img_b = c.take(m_rows_b * kp * 2);
     if (dmmv) {
       L.x2.img_a = c.take(m_pad * kp * 2);
-      L.x1.img_b = c.take(n_pad * kp * 2);
+      L.x1.img_b = c.take(n_rows_b * kp * 2);
     }
+    if (L.fold) L.blk_pos = reinterpret_cast<int*>(c.take(((int64_t)tc::fold_blocks(std::max(n, m)) + 2) * 4));
     L.f1 = plan_sweep(false, dtype, n, m, t, wide_ok);
     L.f2 = plan_sweep(false, dtype, m, n, t, wide_ok);
   }
@@ -441,7 +453,8 @@ static int run_sweep_simt(int kernel, const SweepPlan& sp, const Operand& a, con
 }
 
 static int run_sweep_tc(int kernel, const SweepPlan& sp, const void* img_a, const void* img_b, int64_t d,
-                        const void* vec, void* raw, void* status, cudaStream_t stream, int sweep_idx) {
+                        const void* vec, void* raw, void* status, const int* fold, cudaStream_t stream,
+                        int sweep_idx) {
   FLK_TRY(timer_mark(2 * sweep_idx, stream));
   if (sp.kloop) {
     tck::SweepArgsL args;
@@ -464,6 +477,7 @@ static int run_sweep_tc(int kernel, const SweepPlan& sp, const void* img_a, cons
     args.vec = reinterpret_cast<const float*>(vec);
     args.raw = reinterpret_cast<float*>(raw);
     args.status = reinterpret_cast<int*>(status);
+    args.fold = sp.fold ? fold : nullptr;
     args.tp = sp.tp;
     args.r_pad = sp.r_pad;
     args.s_pad = sp.s_pad;
@@ -493,12 +507,22 @@ static int prepare_operands(const Layout& L, int kernel, const Mat& X1, const Ma
                             T sig_scalar, int sigma_len, int dtype, bool reset_status, cudaStream_t stream) {
   if (L.tc) {
     if (reset_status) FLK_CUDA_TRY(cudaMemsetAsync(L.status, 0, 256, stream));
+    else if (L.fold)  // the fold blocks start from zero in every call (the two leading status words are kept)
+      FLK_CUDA_TRY(cudaMemsetAsync(L.fold_block(0), 0, 2 * tc::kFoldWords * sizeof(int), stream));
     auto prep = L.s1.kloop ? tck::prep_images_large : tc::prep_images;
-    FLK_TRY(prep(kernel, X1.ptr, X1.rows, X1.rs, X1.cs, (int)d, (const float*)sig_dev, (float)sig_scalar, sigma_len,
-                 L.s1.r_pad, L.x1.img_a, L.x1.img_b, reinterpret_cast<int*>(L.status), stream));
-    FLK_TRY(prep(kernel, X2.ptr, X2.rows, X2.rs, X2.cs, (int)d, (const float*)sig_dev, (float)sig_scalar, sigma_len,
-                 L.s1.s_pad, L.x2.img_a, L.x2.img_b, reinterpret_cast<int*>(L.status), stream));
-    count_launch(2);
+    // folded sweeps build their reduction-side images per sweep, with the vector (fold_operand)
+    void* x1_b = L.fold ? nullptr : L.x1.img_b;
+    void* x2_b = L.fold ? nullptr : L.x2.img_b;
+    if (L.x1.img_a != nullptr || x1_b != nullptr) {
+      FLK_TRY(prep(kernel, X1.ptr, X1.rows, X1.rs, X1.cs, (int)d, (const float*)sig_dev, (float)sig_scalar, sigma_len,
+                   L.s1.r_pad, L.x1.img_a, x1_b, reinterpret_cast<int*>(L.status), stream));
+      count_launch();
+    }
+    if (L.x2.img_a != nullptr || x2_b != nullptr) {
+      FLK_TRY(prep(kernel, X2.ptr, X2.rows, X2.rs, X2.cs, (int)d, (const float*)sig_dev, (float)sig_scalar, sigma_len,
+                   L.s1.s_pad, L.x2.img_a, x2_b, reinterpret_cast<int*>(L.status), stream));
+      count_launch();
+    }
   }
   const int ld = ld_for(dtype, d);
   FLK_TRY(run_prep_rows<T>(X1, sig_dev, sig_scalar, sigma_len, L.x1.xs, ld, L.s1.r_pad, L.x1.norms, gate_simt(L), stream));
@@ -508,14 +532,32 @@ static int prepare_operands(const Layout& L, int kernel, const Mat& X1, const Ma
 
 // One sweep + its finalisation, on whichever path(s) the layout holds.  `a`/`b` = output-side and
 // reduction-side operands, `tcp`/`fp` = the tensor-core (or sole SIMT) plan and the SIMT alternative.
+// What a folded sweep needs beside the plan: the reduction-side operand as the caller gave it, and sigma.
+struct FoldSigma {
+  const float* dev = nullptr;
+  float scalar = 1.0f;
+  int len = 1;
+};
+
 template <typename T>
 static int sweep_and_finalize(const Layout& L, int kernel, int dtype, int64_t d, int64_t t, const SweepPlan& tcp,
                               const SweepPlan& fp, const Operand& a, const Operand& b, const void* vec, void* raw,
                               void* fraw, const Mat* add, void* out, int64_t out_rs, int64_t out_cs, bool padded,
-                              cudaStream_t stream, int sweep_idx) {
+                              cudaStream_t stream, int sweep_idx, const Mat& bX = Mat{nullptr, 0, 0, 0, 0},
+                              const FoldSigma& fold_sig = FoldSigma{}) {
   const int ld = ld_for(dtype, d);
   if (L.tc) {
-    FLK_TRY(run_sweep_tc(kernel, tcp, a.img_a, b.img_b, d, vec, raw, L.status, stream, sweep_idx));
+    if (L.fold) {
+      if constexpr (sizeof(T) == 4) {
+        // reduction-side image of this sweep with the vector folded in (vec is dense: one column, tt = 1)
+        FLK_TRY(tc::build_folded_image(kernel, bX.ptr, bX.rows, bX.rs, bX.cs, (int)d, fold_sig.dev, fold_sig.scalar,
+                                       fold_sig.len, reinterpret_cast<const float*>(vec), L.blk_pos,
+                                       L.fold_block(sweep_idx), b.img_b, reinterpret_cast<int*>(L.status), stream));
+        count_launch(3);
+      }
+    }
+    FLK_TRY(run_sweep_tc(kernel, tcp, a.img_a, b.img_b, d, vec, raw, L.status, L.fold_block(sweep_idx), stream,
+                         sweep_idx));
     FLK_TRY(run_finalize<T>(tcp, raw, add, out, out_rs, out_cs, t, padded, gate_tc(L), stream,
                             reinterpret_cast<const int*>(L.status) + tc::kStatusTimeout));
     FLK_TRY(run_sweep_simt<T>(kernel, fp, a, b, ld, vec, fraw, gate_simt(L), stream, sweep_idx));
@@ -545,8 +587,10 @@ static int fmmv_impl(int dtype, int kernel, const Mat& X1, const Mat& X2, const 
   FLK_TRY(upload_sigma<T>(sigma, sigma_len, L.sigma, &sig_scalar, &sig_dev, stream));
   FLK_TRY(prepare_operands<T>(L, kernel, X1, X2, d, sig_dev, sig_scalar, (int)sigma_len, dtype, reset_status, stream));
   FLK_TRY(run_prep_vec<T>(v, L.vbuf, L.s1.s_pad, L.s1.tp, L.s1.tt, stream));
+  FoldSigma fs;
+  if constexpr (sizeof(T) == 4) fs = FoldSigma{sig_dev, sig_scalar, (int)sigma_len};
   FLK_TRY(sweep_and_finalize<T>(L, kernel, dtype, d, t, L.s1, L.f1, L.x1, L.x2, L.vbuf, L.raw1, L.fraw1, nullptr,
-                                out, out_rs, out_cs, false, stream, 0));
+                                out, out_rs, out_cs, false, stream, 0, X2, fs));
   return FLK_OK;
 }
 
@@ -569,18 +613,20 @@ static int fdmmv_impl(int dtype, int kernel, const Mat& X1, const Mat& X2, const
   const T* sig_dev;
   FLK_TRY(upload_sigma<T>(sigma, sigma_len, L.sigma, &sig_scalar, &sig_dev, stream));
   FLK_TRY(prepare_operands<T>(L, kernel, X1, X2, d, sig_dev, sig_scalar, (int)sigma_len, dtype, reset_status, stream));
+  FoldSigma fs;
+  if constexpr (sizeof(T) == 4) fs = FoldSigma{sig_dev, sig_scalar, (int)sigma_len};
   if (has_v) {
     // sweep 1: u = K v (+ w), kept as a padded vector operand
     FLK_TRY(run_prep_vec<T>(v, L.vbuf, L.s1.s_pad, L.s1.tp, L.s1.tt, stream));
     FLK_TRY(sweep_and_finalize<T>(L, kernel, dtype, d, t, L.s1, L.f1, L.x1, L.x2, L.vbuf, L.raw1, L.fraw1,
-                                  has_w ? &w : nullptr, L.ubuf, 0, 0, true, stream, 0));
+                                  has_w ? &w : nullptr, L.ubuf, 0, 0, true, stream, 0, X2, fs));
   } else {
     FLK_TRY(run_prep_vec<T>(w, L.ubuf, L.s1.r_pad, L.s1.tp, L.s1.tt, stream));
   }
   // sweep 2: out = K^T u  (rows = X2, reduction over X1)
   const Mat prev{out, m, t, out_rs, out_cs};
   FLK_TRY(sweep_and_finalize<T>(L, kernel, dtype, d, t, L.s2, L.f2, L.x2, L.x1, L.ubuf, L.raw2, L.fraw2,
-                                accumulate ? &prev : nullptr, out, out_rs, out_cs, false, stream, 1));
+                                accumulate ? &prev : nullptr, out, out_rs, out_cs, false, stream, 1, X1, fs));
   return FLK_OK;
 }
 
@@ -889,8 +935,8 @@ int flk_square_norm(int dtype, const void* X, int64_t n, int64_t d, int64_t x_rs
                     const double* sigma_host, int64_t sigma_len, void* out, void* stream) {
   FLK_TRY(check_common(dtype, FLK_GAUSSIAN, n, 0, d, 0));
   Mat mx{X, n, d, x_rs, x_cs};
-  FLK_TRY(check_mat("X", mx, false));
-  if (out == nullptr) return fail(FLK_ERR_BAD_ARG, "out: null pointer");
+  FLK_TRY(check_mat("X", mx, n == 0));
+  if (out == nullptr && n > 0) return fail(FLK_ERR_BAD_ARG, "out: null pointer");
   if (sigma_host != nullptr && sigma_len != 1 && sigma_len != d)
     return fail(FLK_ERR_BAD_ARG, "sigma must have 1 or d entries");
   if (sigma_host != nullptr && sigma_len != 1)
@@ -957,11 +1003,12 @@ int flk_fdmmv(int dtype, int kernel, const void* X1, int64_t n, int64_t x1_rs, i
   FLK_TRY(check_mat("out", oo, m == 0 || t == 0));
   FLK_TRY(check_sigma(sigma_host, sigma_len, d));
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const bool acc = (flags & FLK_FLAG_ACCUMULATE) != 0;
   if (dtype == FLK_F32)
     return fdmmv_impl<float>(dtype, kernel, a, b, vv, ww, t, out, out_rs, out_cs, sigma_host, sigma_len, workspace,
-                             workspace_bytes, flags, st);
+                             workspace_bytes, flags, st, acc);
   return fdmmv_impl<double>(dtype, kernel, a, b, vv, ww, t, out, out_rs, out_cs, sigma_host, sigma_len, workspace,
-                            workspace_bytes, flags, st);
+                            workspace_bytes, flags, st, acc);
 }
 
 

@@ -56,7 +56,29 @@ constexpr int kMaxD = 30;
 constexpr int kEpilogueWarps = 4 * kRowBlocks;
 constexpr int kMmaWarp0 = kEpilogueWarps;                // warps 16..19: MMA issuer of row block (warp - 16)
 constexpr int kProducerWarp = kMmaWarp0 + kRowBlocks;    // warp 20
-constexpr int kThreads = (kEpilogueWarps + kRowBlocks + 1) * 32;
+// Warps 21-23 do no work: they fill up the producer's warpgroup, because registers are handed back and
+// claimed (setmaxnreg) by whole warpgroups of four consecutive warps.
+constexpr int kThreads = (kEpilogueWarps + kRowBlocks + 4) * 32;
+// Register budget per thread.  A CTA of 24 warps puts six warps on each SM sub-partition (16384 registers
+// each), so the kernel starts with 80 registers per thread (6 x 32 x 80 = 15360 per sub-partition).  The MMA
+// issuers and the producer need few: both warpgroups hand registers back at once and the four epilogue
+// warpgroups (one warp per sub-partition each) claim them.  The pool that setmaxnreg redistributes is what the
+// CTA was launched with (24 warps x 80), so the new counts must add up to no more than that, or the claim
+// would wait for ever.  With 80 the epilogue spilled a register or two in most instantiations, and a spilled
+// register may be one that a tcgen05.ld in flight is still to fill.
+// The split (104, 32, 32) compiles every instantiation without spills except the plain (unfolded) Gaussian
+// single-column sweep, which needs the milder split (96, 56, 40): both sum to the launch-time pool of
+// 24 warps x 80 registers.  The build fails when any tensor-core instantiation reports spills.
+template <int KT, int TT, bool FOLD>
+struct RegBudget {
+  static constexpr bool kMild = KT == FLK_GAUSSIAN && TT == 1 && !FOLD;
+  static constexpr int kEpilogue = kMild ? 96 : 104;
+  static constexpr int kMma = kMild ? 56 : 32;
+  static constexpr int kProducer = kMild ? 40 : 32;
+  static_assert(kEpilogueWarps * kEpilogue + 4 * kMma + 4 * kProducer <= (kThreads / 32) * 80,
+                "register re-partitioning exceeds the pool the CTA is launched with");
+  static_assert(kEpilogue % 8 == 0 && kMma % 8 == 0 && kProducer % 8 == 0, "setmaxnreg takes multiples of 8");
+};
 constexpr int kVecStages = 4;                       // ring of vector tiles
 constexpr uint64_t kWaitTimeoutNs = 1000000000ull;  // every device-side wait gives up after 1 s
 constexpr float kNormLimit = 60000.0f;              // largest half squared norm an image may carry
@@ -127,30 +149,30 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-__device__ __forceinline__ uint64_t global_timer_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+// Low 32 bits of the nanosecond timer (wraps every 4.29 s; differences of two readings stay valid below that).
+__device__ __forceinline__ uint32_t timer_lo_ns() {
+  uint32_t t;
+  asm volatile("mov.u32 %0, %%globaltimer_lo;" : "=r"(t));
   return t;
 }
-// Bounded wait: false when the phase did not complete within kWaitTimeoutNs.  A waiting warp backs
-// off with a short nanosleep between probes: a warp that spins on a barrier competes for issue
-// slots with the epilogue warps of its SM sub-partition (measured: the sub-partition hosting the
-// spinning MMA warp ran its epilogue warps almost 2x slower and set the pace of the whole CTA).
+// Bounded wait: false when the phase did not complete within about a second (kWaitTimeoutNs), or after 2^26
+// probes, whichever comes first.  A waiting warp backs off with a short nanosleep between probes: a warp that
+// spins on a barrier competes for issue slots with the epilogue warps of its SM sub-partition (measured: the
+// sub-partition hosting the spinning MMA warp ran its epilogue warps almost 2x slower and set the pace of the
+// whole CTA).  Inlined and kept to two registers (start time, probe count): the kernels that use it re-partition
+// their registers between warp roles (setmaxnreg), which rules out out-of-line calls.
 #ifndef FLK_TC_BACKOFF_NS
 #define FLK_TC_BACKOFF_NS 20
 #endif
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity) {
-  const uint64_t t0 = global_timer_ns();
-  for (uint32_t it = 0; it < (1u << 28); ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (FLK_TC_BACKOFF_NS > 0) __nanosleep(FLK_TC_BACKOFF_NS);
-    if ((it & 63u) == 63u && global_timer_ns() - t0 > kWaitTimeoutNs) return false;
-  }
-  return false;
-}
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   if (mbar_try_wait(bar, parity)) return true;
-  return mbar_wait_slow(bar, parity);
+  const uint32_t t0 = timer_lo_ns();
+  for (uint32_t it = 0; it < (1u << 26); ++it) {
+    if (FLK_TC_BACKOFF_NS > 0) __nanosleep(FLK_TC_BACKOFF_NS);
+    if (mbar_try_wait(bar, parity)) return true;
+    if (timer_lo_ns() - t0 > (uint32_t)kWaitTimeoutNs) return false;
+  }
+  return false;
 }
 __device__ __forceinline__ void fence_barrier_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -159,6 +181,16 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uin
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
                "l"(src), "r"(bytes), "r"(bar)
                : "memory");
+}
+
+// Register re-partitioning between warp roles; both are executed by all four warps of a warpgroup.
+template <int N>
+__device__ __forceinline__ void reg_release() {  // lower this warpgroup's register count to N
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void reg_claim() {  // raise it to N (waits until the pool holds enough)
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
 }
 
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
@@ -492,15 +524,17 @@ inline int prep_images(int kernel, const void* X, int64_t n, int64_t rs, int64_t
 // ---------------------------------------------------------------------------------------------
 struct SweepArgs {
   const __half* img_a;  // [r_pad / 128] tile images (output side)
-  const __half* img_b;  // [s_pad / 128] tile images (reduction side)
-  const float* vec;     // [t_chunks][s_pad][TT]
+  const __half* img_b;  // [n_col_tiles] tile images (reduction side; with the vector folded in when `fold` is set)
+  const float* vec;     // [t_chunks][s_pad][TT]  (unused with `fold`)
   float* raw;           // [n_chunks][r_pad][tp]
   int* status;          // device status block (word kStatusTimeout, word kStatusRange)
+  const int* fold;      // folded sweeps: [kFoldNegTile] first tile of negative vector entries, [kFoldExp] power of
+                        // two the stored vector magnitudes were divided by; null for ordinary sweeps
   int tp;
   int64_t r_pad;
   int64_t s_pad;
   int row_tiles;        // ceil(r / 512)
-  int n_col_tiles;      // ceil(s / 128)
+  int n_col_tiles;      // column tiles of the reduction side
   int tiles_per_chunk;
   // two-segment grid: CTAs [0, main_ctas) cover row tiles [0, main_tiles) with `tiles_per_chunk` column
   // tiles each; the remaining CTAs cover the remaining row tiles with `tiles_per_chunk_tail` each
@@ -509,6 +543,9 @@ struct SweepArgs {
   int tiles_per_chunk_tail;
   int ksteps;           // MMA K-steps (16 fp16 each) actually carrying data
 };
+
+// words of the fold block (inside the 256-byte status block, one block per sweep)
+enum { kFoldNegTile = 0, kFoldExp = 1, kFoldPositives = 2, kFoldMaxBits = 3, kFoldWords = 8 };
 
 template <int NSLAB>
 struct TcCfg {
@@ -523,17 +560,20 @@ constexpr int kFlushTiles = 32;  // column tiles (of 128) summed in one running 
 constexpr int kMaxWideTilesPerChunk = 512;  // many-column epilogue (single-level sums): longest chunk the planner forms
 
 // Ring depths: with 32 vector columns per pass a vector tile is 16 KB, so two of them and one B stage fewer.
-template <int NSLAB, int TT>
+// A folded sweep has no vector ring at all.
+template <int NSLAB, int TT, bool FOLD>
 struct RingOf {
   static constexpr int S = TT == kWideTT ? (NSLAB == 3 ? 3 : (NSLAB == 2 ? 5 : 10)) : TcCfg<NSLAB>::STAGES;
-  static constexpr int VS = TT == kWideTT ? 2 : kVecStages;
+  static constexpr int VS = FOLD ? 0 : (TT == kWideTT ? 2 : kVecStages);
+  static constexpr int V_BYTES = VS * kColsPerTile * TT * 4;
 };
 
-template <int NSLAB, int TT>
+template <int NSLAB, int TT, bool FOLD>
 constexpr size_t tc_smem_bytes() {
   using C = TcCfg<NSLAB>;
-  return 1024 /* alignment slack */ + (size_t)C::A_BYTES + (size_t)RingOf<NSLAB, TT>::S * C::TILE_BYTES +
-         (size_t)RingOf<NSLAB, TT>::VS * kColsPerTile * TT * 4 + 512 /* barriers + tmem pointer */ +
+  using R = RingOf<NSLAB, TT, FOLD>;
+  return 1024 /* alignment slack */ + (size_t)C::A_BYTES + (size_t)R::S * C::TILE_BYTES + (size_t)R::V_BYTES +
+         512 /* barriers + tmem pointer */ +
          (TT == kWideTT ? 0 : kRowsPerCta * 16) /* second-level sums, four floats per epilogue thread */;
 }
 
@@ -542,8 +582,11 @@ enum { kErrProducer = 0x10, kErrMma = 0x20, kErrEpilogue = 0x30 };
 
 // Which column pairs (0..15 within a 32-column piece) take the FMA-pipe exponential: a per-kernel-function
 // count (measured optima on config-2 data; the Laplacian / Matern epilogues carry a MUFU square root and more
-// FMA work per value), spread evenly over the piece so both pipes have work throughout.
-template <int KT>
+// FMA work per value; a folded sweep has no shared-memory vector reads competing with the MUFU instructions for
+// the same issue queue, so its balance point lies elsewhere: measured ms per fdmmv at N = 1e7, M = 50,000 times
+// the sampled SM clock in GHz, 3 -> 429, 4 -> 407, 5 -> 392, 6 -> 382, 7 -> 403, 8 -> 422), spread evenly over the
+// piece so both pipes have work throughout.
+template <int KT, bool FOLD = false>
 __host__ __device__ constexpr int poly_pairs_of() {
 #ifndef FLK_TC_POLY_PAIRS_LM
 #define FLK_TC_POLY_PAIRS_LM 8
@@ -551,11 +594,15 @@ __host__ __device__ constexpr int poly_pairs_of() {
 #ifndef FLK_TC_POLY_PAIRS_M25
 #define FLK_TC_POLY_PAIRS_M25 5
 #endif
-  return KT == FLK_GAUSSIAN ? kPolyPairs : (KT == FLK_MATERN25 ? FLK_TC_POLY_PAIRS_M25 : FLK_TC_POLY_PAIRS_LM);
+#ifndef FLK_TC_POLY_PAIRS_FOLD
+#define FLK_TC_POLY_PAIRS_FOLD 6
+#endif
+  return KT == FLK_GAUSSIAN ? (FOLD ? FLK_TC_POLY_PAIRS_FOLD : kPolyPairs)
+                            : (KT == FLK_MATERN25 ? FLK_TC_POLY_PAIRS_M25 : FLK_TC_POLY_PAIRS_LM);
 }
-template <int KT>
+template <int KT, bool FOLD = false>
 __host__ __device__ constexpr bool poly_pair(int pr) {
-  constexpr int np = poly_pairs_of<KT>();
+  constexpr int np = poly_pairs_of<KT, FOLD>();
   return np > 0 && ((pr + 1) * np / 16 != pr * np / 16);
 }
 
@@ -596,6 +643,22 @@ __device__ __forceinline__ void epilogue_32(const uint32_t (&r)[32], const float
   }
 }
 
+// Folded sweep (Gaussian, one vector column): log2 |vec_j| already sits in the exponent, so a kernel value times
+// |vec_j| is ONE exponential and the contraction is a signed sum -- no vector tile, no shared-memory reads.  All
+// 128 columns of a tile carry the same sign (the image builder sorts the reduction side by sign), `sgn2` is that
+// sign as a packed pair (+1, +1) or (-1, -1).
+template <int KT, int C0 = 0>
+__device__ __forceinline__ void epilogue_32_fold(const uint32_t (&r)[32], uint64_t sgn2, uint64_t (&osum)[2]) {
+  if constexpr (C0 < 32) {
+    float k0, k1, k2, k3;
+    eval_pair<KT, poly_pair<KT, true>(C0 / 2)>(r[C0], r[C0 + 1], k0, k1);
+    eval_pair<KT, poly_pair<KT, true>(C0 / 2 + 1)>(r[C0 + 2], r[C0 + 3], k2, k3);
+    osum[0] = fma2(pack2(k0, k1), sgn2, osum[0]);
+    osum[1] = fma2(pack2(k2, k3), sgn2, osum[1]);
+    epilogue_32_fold<KT, C0 + 4>(r, sgn2, osum);
+  }
+}
+
 // Many-column epilogue: kernel function + contraction with 32 vector columns for 16 accumulator columns held in
 // registers: per kernel value one exponential, then 16 packed multiply-adds against the 32 vector entries of that
 // column (eight 16-byte broadcasts from shared memory).  PR0 = index of the first column pair within its 32-column
@@ -621,35 +684,56 @@ __device__ __forceinline__ void epilogue_wide16(const uint32_t (&r)[16], const f
   }
 }
 
+// Shared-memory map of the sweep kernel, as 32-bit shared addresses computed from one base (generic 64-bit
+// pointers to every ring and barrier would be live across all three warp roles and cost a dozen registers).
+// barrier block: a_full | b_full[S] | b_empty[S] | v_full[VS] | v_empty[VS] | t_full[4] | t_empty[4] | tmem pointer |
+// abort flag; then the second-level sums (one float4 per epilogue thread).
+template <int NSLAB, int TT, bool FOLD>
+struct SmemMap {
+  using C = TcCfg<NSLAB>;
+  using R = RingOf<NSLAB, TT, FOLD>;
+  static constexpr uint32_t A = 0;
+  static constexpr uint32_t B = C::A_BYTES;
+  static constexpr uint32_t V = B + R::S * C::TILE_BYTES;
+  static constexpr uint32_t BARS = V + R::V_BYTES;
+  static constexpr uint32_t A_FULL = BARS;
+  static constexpr uint32_t B_FULL = BARS + 8;
+  static constexpr uint32_t B_EMPTY = B_FULL + 8 * R::S;
+  static constexpr uint32_t V_FULL = B_EMPTY + 8 * R::S;
+  static constexpr uint32_t V_EMPTY = V_FULL + 8 * R::VS;
+  static constexpr uint32_t T_FULL = V_EMPTY + 8 * R::VS;
+  static constexpr uint32_t T_EMPTY = T_FULL + 8 * kRowBlocks;
+  static constexpr uint32_t TMEM_PTR = T_EMPTY + 8 * kRowBlocks;
+  static constexpr uint32_t ABORT = TMEM_PTR + 4;
+  static constexpr uint32_t SUMS = BARS + 512;
+  static_assert(ABORT + 4 <= SUMS, "barrier block overflows its 512 bytes");
+};
+
+__device__ __forceinline__ int ld_shared_i32_volatile(uint32_t addr) {
+  int v;
+  asm volatile("ld.volatile.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_shared_i32_volatile(uint32_t addr, int v) {
+  asm volatile("st.volatile.shared.b32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+
 // Epilogue warp w: TMEM lane quarter q = w % 4 (hardware rule: a warp may only touch lanes
 // 32 (w % 4) .. +31; warps with the same w % 4 also share an SM sub-partition, so each row block
 // has one warp on every sub-partition), row block rb = w / 4.
-template <int KT, int NSLAB, int TT>
+template <int KT, int NSLAB, int TT, bool FOLD>
 __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) {
+  static_assert(!FOLD || (KT == FLK_GAUSSIAN && TT == 1), "only the Gaussian single-column sweep folds its vector");
   using C = TcCfg<NSLAB>;
-  constexpr int S = RingOf<NSLAB, TT>::S;
-  constexpr int VS = RingOf<NSLAB, TT>::VS;
+  using M = SmemMap<NSLAB, TT, FOLD>;
+  using RB = RegBudget<KT, TT, FOLD>;
+  constexpr int S = RingOf<NSLAB, TT, FOLD>::S;
+  constexpr int VS = RingOf<NSLAB, TT, FOLD>::VS;
   extern __shared__ unsigned char tc_smem_raw[];
   // the swizzle atoms want a 512-byte aligned base; 1024 keeps every tile image on a round address
   const uint32_t raw_addr = smem_u32(tc_smem_raw);
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
-  unsigned char* smem = tc_smem_raw + pad;
-  unsigned char* a_smem = smem;
-  unsigned char* b_smem = smem + C::A_BYTES;
-  float* vs = reinterpret_cast<float*>(b_smem + S * C::TILE_BYTES);  // [VS][128][TT]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(vs) + VS * kColsPerTile * TT * 4);
-  // barrier map: a_full | b_full[S] | b_empty[S] | v_full[VS] | v_empty[VS] | t_full[4] | t_empty[4]
-  uint64_t* bar_a_full = bars;
-  uint64_t* bar_b_full = bars + 1;
-  uint64_t* bar_b_empty = bar_b_full + S;
-  uint64_t* bar_v_full = bar_b_empty + S;
-  uint64_t* bar_v_empty = bar_v_full + VS;
-  uint64_t* bar_t_full = bar_v_empty + VS;
-  uint64_t* bar_t_empty = bar_t_full + kRowBlocks;
-  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bar_t_empty + kRowBlocks);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
-  static_assert((1 + 2 * S + 2 * VS + 2 * kRowBlocks) * 8 + 8 <= 512, "barrier block overflows its 512 bytes");
-  // second-level sums of the epilogue threads (TT <= 4): one float4 each, behind the 512-byte barrier block
+  const uint32_t sm = raw_addr + pad;  // shared address of the map's origin
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
@@ -666,8 +750,7 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
   }
   const int tchunk = blockIdx.y;
   const int tile_begin = chunk * tiles_per_chunk;
-  const int tile_end = min(tile_begin + tiles_per_chunk, p.n_col_tiles);
-  const int ntiles = tile_end - tile_begin;
+  const int ntiles = min(tile_begin + tiles_per_chunk, p.n_col_tiles) - tile_begin;
 
   // Do not start when a CTA of this launch already gave up (keeps a failed launch short) or when
   // the image builder found rows fp16 cannot carry (the SIMT kernels take over).
@@ -680,62 +763,70 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
   if (skip_launch) return;
 
   if (tid == 0) {
-    mbar_init(smem_u32(bar_a_full), 1);
+    mbar_init(sm + M::A_FULL, 1);
+#pragma unroll 1
     for (int s = 0; s < S; ++s) {
-      mbar_init(smem_u32(bar_b_full + s), 1);
-      mbar_init(smem_u32(bar_b_empty + s), kRowBlocks);  // one MMA commit per row-block issuer
+      mbar_init(sm + M::B_FULL + 8 * s, 1);
+      mbar_init(sm + M::B_EMPTY + 8 * s, kRowBlocks);  // one MMA commit per row-block issuer
     }
+#pragma unroll 1
     for (int s = 0; s < VS; ++s) {
-      mbar_init(smem_u32(bar_v_full + s), 1);
-      mbar_init(smem_u32(bar_v_empty + s), kEpilogueWarps);  // one arrive per epilogue warp
+      mbar_init(sm + M::V_FULL + 8 * s, 1);
+      mbar_init(sm + M::V_EMPTY + 8 * s, kEpilogueWarps);  // one arrive per epilogue warp
     }
+#pragma unroll 1
     for (int i = 0; i < kRowBlocks; ++i) {
-      mbar_init(smem_u32(bar_t_full + i), 1);
-      mbar_init(smem_u32(bar_t_empty + i), 4);  // the four warps of that row block
+      mbar_init(sm + M::T_FULL + 8 * i, 1);
+      mbar_init(sm + M::T_EMPTY + 8 * i, 4);  // the four warps of that row block
     }
-    *abort_flag = 0;
+    st_shared_i32_volatile(sm + M::ABORT, 0);
     fence_barrier_init();
   }
   if (warp == kMmaWarp0) {
-    tmem_alloc(smem_u32(tmem_ptr), 512);
+    tmem_alloc(sm + M::TMEM_PTR, 512);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_base = *tmem_ptr;
+  const uint32_t tmem_base = (uint32_t)ld_shared_i32_volatile(sm + M::TMEM_PTR);
 
-  if (warp == kProducerWarp) {
+  if (warp > kProducerWarp) {
+    reg_release<RB::kProducer>();  // filler warps of the producer's warpgroup
+  } else if (warp == kProducerWarp) {
     // ------------------------------ bulk-copy producer ------------------------------
     // The whole warp walks the loop (converged); one elected lane issues the copies.
+    reg_release<RB::kProducer>();
     if (elect_one()) {
       const __half* a_src = p.img_a + (int64_t)row_tile * kRowBlocks * (kTileRows * C::KP);
-      mbar_expect_tx(smem_u32(bar_a_full), C::A_BYTES);
+      mbar_expect_tx(sm + M::A_FULL, C::A_BYTES);
       for (int rb = 0; rb < kRowBlocks; ++rb)
-        bulk_copy_g2s(smem_u32(a_smem) + rb * C::TILE_BYTES, a_src + rb * (kTileRows * C::KP), C::TILE_BYTES,
-                      smem_u32(bar_a_full));
+        bulk_copy_g2s(sm + M::A + rb * C::TILE_BYTES, a_src + rb * (kTileRows * C::KP), C::TILE_BYTES, sm + M::A_FULL);
     }
     __syncwarp();
-    const float* vec_base = p.vec + (int64_t)tchunk * p.s_pad * TT;
+    const __half* b_src = p.img_b + (int64_t)tile_begin * (kTileRows * C::KP);
+    const float* v_src = FOLD ? nullptr : p.vec + ((int64_t)tchunk * p.s_pad + (int64_t)tile_begin * kColsPerTile) * TT;
     for (int j = 0; j < ntiles; ++j) {
-      const int stage = j % S, vstage = j % VS;
-      if (*abort_flag) break;
-      if (!mbar_wait(smem_u32(bar_b_empty + stage), ((j / S) & 1) ^ 1) ||
-          !mbar_wait(smem_u32(bar_v_empty + vstage), ((j / VS) & 1) ^ 1)) {
+      const int stage = j % S;
+      if (ld_shared_i32_volatile(sm + M::ABORT)) break;
+      bool ok = mbar_wait(sm + M::B_EMPTY + 8 * stage, ((j / S) & 1) ^ 1);
+      if constexpr (!FOLD) ok = ok && mbar_wait(sm + M::V_EMPTY + 8 * (j % VS), ((j / VS) & 1) ^ 1);
+      if (!ok) {
         if (lane == 0) atomicExch(p.status + kStatusTimeout, kErrProducer | 1);
-        *abort_flag = 1;
+        st_shared_i32_volatile(sm + M::ABORT, 1);
         break;
       }
       if (elect_one()) {
-        const int64_t ct = tile_begin + j;
-        const uint32_t bar = smem_u32(bar_b_full + stage);
+        const uint32_t bar = sm + M::B_FULL + 8 * stage;
         mbar_expect_tx(bar, C::TILE_BYTES);
-        bulk_copy_g2s(smem_u32(b_smem) + stage * C::TILE_BYTES, p.img_b + ct * (kTileRows * C::KP), C::TILE_BYTES,
-                      bar);
-        const uint32_t vbar = smem_u32(bar_v_full + vstage);
-        mbar_expect_tx(vbar, kColsPerTile * TT * 4);
-        bulk_copy_g2s(smem_u32(vs) + vstage * kColsPerTile * TT * 4, vec_base + ct * kColsPerTile * TT,
-                      kColsPerTile * TT * 4, vbar);
+        bulk_copy_g2s(sm + M::B + stage * C::TILE_BYTES, b_src + (int64_t)j * (kTileRows * C::KP), C::TILE_BYTES, bar);
+        if constexpr (!FOLD) {
+          const int vstage = j % VS;
+          const uint32_t vbar = sm + M::V_FULL + 8 * vstage;
+          mbar_expect_tx(vbar, kColsPerTile * TT * 4);
+          bulk_copy_g2s(sm + M::V + vstage * kColsPerTile * TT * 4, v_src + (int64_t)j * kColsPerTile * TT,
+                        kColsPerTile * TT * 4, vbar);
+        }
       }
       __syncwarp();
     }
@@ -744,130 +835,151 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
     // One issuer warp per row block, each on its own SM sub-partition: a queued tcgen05.mma holds
     // up the other warps of its sub-partition, so the issue work is spread evenly over the four.
     // All lanes wait on the barriers together; one elected lane issues the MMAs and commits.
+    reg_release<RB::kMma>();
     const int rb = warp - kMmaWarp0;
-    bool ok = mbar_wait(smem_u32(bar_a_full), 0);
+    bool ok = mbar_wait(sm + M::A_FULL, 0);
     if (!ok) {
       if (lane == 0) atomicExch(p.status + kStatusTimeout, kErrMma | 1);
-      *abort_flag = 1;
+      st_shared_i32_volatile(sm + M::ABORT, 1);
     }
-    const uint64_t a_desc0 = make_smem_desc(smem_u32(a_smem) + rb * C::TILE_BYTES);
+    const uint64_t a_desc0 = make_smem_desc(sm + M::A + rb * C::TILE_BYTES);
     const uint32_t d_tmem = tmem_base + (uint32_t)(rb * kColsPerTile);
     for (int j = 0; ok && j < ntiles; ++j) {
       const int stage = j % S;
-      if (*abort_flag) break;
+      if (ld_shared_i32_volatile(sm + M::ABORT)) break;
       // B tile j has landed, and this row block's accumulator is free (its warps pulled tile j-1
       // into registers)
-      if (!mbar_wait(smem_u32(bar_b_full + stage), (j / S) & 1) ||
-          !mbar_wait(smem_u32(bar_t_empty + rb), (j & 1) ^ 1)) {
+      if (!mbar_wait(sm + M::B_FULL + 8 * stage, (j / S) & 1) || !mbar_wait(sm + M::T_EMPTY + 8 * rb, (j & 1) ^ 1)) {
         if (lane == 0) atomicExch(p.status + kStatusTimeout, kErrMma | 2);
-        *abort_flag = 1;
+        st_shared_i32_volatile(sm + M::ABORT, 1);
         break;
       }
       tc_fence_after();
       if (elect_one()) {
-        const uint64_t b_desc0 = make_smem_desc(smem_u32(b_smem) + stage * C::TILE_BYTES);
+        const uint64_t b_desc0 = make_smem_desc(sm + M::B + stage * C::TILE_BYTES);
         for (int ks = 0; ks < p.ksteps; ++ks) {
           // 32 bytes (16 fp16) per K-step, two K-steps per 64-byte swizzle row, 8 KiB per slab
           const uint64_t koff = (uint64_t)((ks >> 1) * ((kTileRows * 64) >> 4) + (ks & 1) * 2);
           mma_f16(d_tmem, a_desc0 + koff, b_desc0 + koff, kInstrDesc, ks > 0 ? 1u : 0u);
         }
-        mma_commit(smem_u32(bar_t_full + rb));
-        mma_commit(smem_u32(bar_b_empty + stage));
+        mma_commit(sm + M::T_FULL + 8 * rb);
+        mma_commit(sm + M::B_EMPTY + 8 * stage);
       }
       __syncwarp();
     }
   } else {
     // ------------------------------ epilogue warps ------------------------------
+    reg_claim<RB::kEpilogue>();
     const int q = warp & 3;    // TMEM lane quarter this warp may access
     const int rb = warp >> 2;  // row block
     constexpr int NSUM = TT == kWideTT ? 16 : 2;  // packed pairs of running sums (see epilogue_32 / epilogue_wide16)
     // Two-level summation (TT <= 4): `osum` collects kFlushTiles column tiles, then is folded into a float4 of
-    // this thread in shared memory, addressed through a 32-bit shared address formed on the spot, so that the
-    // hot loop keeps its registers: this kernel sits at its 80-register ceiling and must not spill, because
-    // registers that a tcgen05.ld is still filling could be among the spilled ones.  A chunk may span millions of
-    // columns; one running fp32 sum over all of them loses about half a digit more than the reference's blocked
-    // GEMV does, enough to unsettle an fp32 conjugate gradient at lambda = 1e-7.  The many-column form keeps
-    // one level: the planner bounds its chunk length instead (kMaxWideTilesPerChunk).
+    // this thread in shared memory.  A chunk may span millions of columns; one running fp32 sum over all of them
+    // loses about half a digit more than the reference's blocked GEMV does, enough to unsettle an fp32 conjugate
+    // gradient at lambda = 1e-7.  The many-column form keeps one level: the planner bounds its chunk length
+    // instead (kMaxWideTilesPerChunk).
     uint64_t osum[NSUM];
 #pragma unroll
     for (int i = 0; i < NSUM; ++i) osum[i] = 0ull;
-    if constexpr (TT != kWideTT) st_shared_f4(smem_u32(bars) + 512u + (uint32_t)(warp * 32 + lane) * 16u, 0.f, 0.f, 0.f, 0.f);
+    const uint32_t tot = sm + M::SUMS + (uint32_t)(warp * 32 + lane) * 16u;
+    if constexpr (TT != kWideTT) st_shared_f4(tot, 0.f, 0.f, 0.f, 0.f);
     const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(rb * kColsPerTile);
+    int neg_first = 0;
+    if constexpr (FOLD) neg_first = __ldg(p.fold + kFoldNegTile) - tile_begin;  // first tile of this chunk that is negative
     bool epi_ok = true;
 
     // outer loop = blocks of kFlushTiles tiles, with the fold between the blocks and outside the hot inner loop
     for (int j0 = 0; j0 < ntiles && epi_ok; j0 += kFlushTiles) {
-    if constexpr (TT != kWideTT) {
-      if (j0 > 0) {
-        const uint32_t tot = smem_u32(bars) + 512u + (uint32_t)(warp * 32 + lane) * 16u;
-        float t0, t1, t2, t3, a0, a1, b0, b1;
-        ld_shared_f4(tot, t0, t1, t2, t3);
-        unpack2(osum[0], a0, a1);
-        unpack2(osum[1], b0, b1);
-        st_shared_f4(tot, t0 + a0, t1 + a1, t2 + b0, t3 + b1);
-        osum[0] = osum[1] = 0ull;
+      if constexpr (TT != kWideTT) {
+        if (j0 > 0) {
+          float t0, t1, t2, t3, a0, a1, b0, b1;
+          ld_shared_f4(tot, t0, t1, t2, t3);
+          unpack2(osum[0], a0, a1);
+          unpack2(osum[1], b0, b1);
+          st_shared_f4(tot, t0 + a0, t1 + a1, t2 + b0, t3 + b1);
+          osum[0] = osum[1] = 0ull;
+        }
       }
-    }
-    const int j1 = min(j0 + kFlushTiles, ntiles);
-    for (int j = j0; j < j1; ++j) {
-      const int vstage = j % VS;
-      if (*abort_flag) { epi_ok = false; break; }
-      if (!mbar_wait(smem_u32(bar_v_full + vstage), (j / VS) & 1) ||
-          !mbar_wait(smem_u32(bar_t_full + rb), j & 1)) {
-        atomicExch(p.status + kStatusTimeout, kErrEpilogue | 1);
-        *abort_flag = 1;
-        epi_ok = false;
-        break;
-      }
-      tc_fence_after();
-      const float* vsm = vs + vstage * kColsPerTile * TT;
-      if constexpr (TT == kWideTT) {
-        // eight 16-column pieces; the accumulator goes back to its issuer once the last one is in registers
-        uint32_t rw[16];
+      const int j1 = min(j0 + kFlushTiles, ntiles);
+      for (int j = j0; j < j1; ++j) {
+        if (ld_shared_i32_volatile(sm + M::ABORT)) { epi_ok = false; break; }
+        bool ok = true;
+        if constexpr (!FOLD) ok = mbar_wait(sm + M::V_FULL + 8 * (j % VS), (j / VS) & 1);
+        if (!ok || !mbar_wait(sm + M::T_FULL + 8 * rb, j & 1)) {
+          atomicExch(p.status + kStatusTimeout, kErrEpilogue | 1);
+          st_shared_i32_volatile(sm + M::ABORT, 1);
+          epi_ok = false;
+          break;
+        }
+        tc_fence_after();
+        if constexpr (FOLD) {
+          const uint64_t sgn2 = j >= neg_first ? 0xBF800000BF800000ull : 0x3F8000003F800000ull;
+          uint32_t ra[32], rc[32];
+          tmem_ld32(taddr, ra);
+          tmem_ld_wait_on(ra);
+          tmem_ld32(taddr + 32, rc, ra);
+          epilogue_32_fold<KT>(ra, sgn2, osum);
+          tmem_ld_wait_on(rc, osum);
+          tmem_ld32(taddr + 64, ra, rc);
+          epilogue_32_fold<KT>(rc, sgn2, osum);
+          tmem_ld_wait_on(ra, osum);
+          tmem_ld32(taddr + 96, rc, ra);
+          tmem_ld_wait_on(rc);
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(sm + M::T_EMPTY + 8 * rb);
+          epilogue_32_fold<KT>(ra, sgn2, osum);
+          epilogue_32_fold<KT>(rc, sgn2, osum);
+        } else {
+          const float* vsm = reinterpret_cast<const float*>(tc_smem_raw + pad + M::V) + (j % VS) * kColsPerTile * TT;
+          if constexpr (TT == kWideTT) {
+            // eight 16-column pieces; the accumulator goes back to its issuer once the last one is in registers
+            uint32_t rw[16];
 #pragma unroll
-        for (int pc = 0; pc < 8; ++pc) {
-          tmem_ld16(taddr + pc * 16, rw);
-          tmem_ld_wait_on(rw);
-          if (pc == 7) {
+            for (int pc = 0; pc < 8; ++pc) {
+              tmem_ld16(taddr + pc * 16, rw);
+              tmem_ld_wait_on(rw);
+              if (pc == 7) {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(sm + M::T_EMPTY + 8 * rb);
+              }
+              if (pc & 1)
+                epilogue_wide16<KT, 8>(rw, vsm + pc * 16 * TT, osum);
+              else
+                epilogue_wide16<KT, 0>(rw, vsm + pc * 16 * TT, osum);
+            }
+          } else {
+            uint32_t ra[32], rc[32];
+            // pieces 0 and 2 travel in `ra`, 1 and 3 in `rc`; the next piece loads while this one is evaluated
+            tmem_ld32(taddr, ra);
+            tmem_ld_wait_on(ra);
+            tmem_ld32(taddr + 32, rc, ra);
+            epilogue_32<KT, TT>(ra, vsm, osum);
+            tmem_ld_wait_on(rc, osum);
+            tmem_ld32(taddr + 64, ra, rc);
+            epilogue_32<KT, TT>(rc, vsm + 32 * TT, osum);
+            tmem_ld_wait_on(ra, osum);
+            tmem_ld32(taddr + 96, rc, ra);
+            tmem_ld_wait_on(rc);
+            // The second half of the accumulator is in registers: hand the accumulator back now, so the
+            // MMA of the next tile (and the barrier round trips either side of it) runs under the
+            // evaluation of these two pieces.
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(bar_t_empty + rb));
+            if (lane == 0) mbar_arrive(sm + M::T_EMPTY + 8 * rb);
+            epilogue_32<KT, TT>(ra, vsm + 64 * TT, osum);
+            epilogue_32<KT, TT>(rc, vsm + 96 * TT, osum);
           }
-          if (pc & 1)
-            epilogue_wide16<KT, 8>(rw, vsm + pc * 16 * TT, osum);
-          else
-            epilogue_wide16<KT, 0>(rw, vsm + pc * 16 * TT, osum);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(sm + M::V_EMPTY + 8 * (j % VS));
         }
-      } else {
-        uint32_t ra[32], rc[32];
-        // pieces 0 and 2 travel in `ra`, 1 and 3 in `rc`; the next piece loads while this one is evaluated
-        tmem_ld32(taddr, ra);
-        tmem_ld_wait_on(ra);
-        tmem_ld32(taddr + 32, rc, ra);
-        epilogue_32<KT, TT>(ra, vsm, osum);
-        tmem_ld_wait_on(rc, osum);
-        tmem_ld32(taddr + 64, ra, rc);
-        epilogue_32<KT, TT>(rc, vsm + 32 * TT, osum);
-        tmem_ld_wait_on(ra, osum);
-        tmem_ld32(taddr + 96, rc, ra);
-        tmem_ld_wait_on(rc);
-        // The second half of the accumulator is in registers: hand the accumulator back now, so the
-        // MMA of the next tile (and the barrier round trips either side of it) runs under the
-        // evaluation of these two pieces.
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(bar_t_empty + rb));
-        epilogue_32<KT, TT>(ra, vsm + 64 * TT, osum);
-        epilogue_32<KT, TT>(rc, vsm + 96 * TT, osum);
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(bar_v_empty + vstage));
-    }
     }
     if (epi_ok) {
       if constexpr (TT != kWideTT) {
         float t0, t1, t2, t3;
-        ld_shared_f4(smem_u32(bars) + 512u + (uint32_t)(warp * 32 + lane) * 16u, t0, t1, t2, t3);
+        ld_shared_f4(tot, t0, t1, t2, t3);
         osum[0] = add2(pack2(t0, t1), osum[0]);
         osum[1] = add2(pack2(t2, t3), osum[1]);
       }
@@ -886,7 +998,10 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
         unpack2(osum[0], a0, a1);
         unpack2(osum[1], b0, b1);
         if constexpr (TT == 1) {
-          dst[0] = (a0 + a1) + (b0 + b1);
+          float sum = (a0 + a1) + (b0 + b1);
+          // folded: the vector magnitudes were stored divided by 2^e; the factor goes back on here (exact)
+          if constexpr (FOLD) sum *= __int_as_float((__ldg(p.fold + kFoldExp) + 127) << 23);
+          dst[0] = sum;
         } else if constexpr (TT == 2) {
           dst[0] = a0 + b0;
           dst[1] = a1 + b1;
@@ -903,19 +1018,18 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
   // ------------------------------ teardown ------------------------------
   tc_fence_before();
   __syncthreads();
-  const bool aborted = (*abort_flag != 0);
+  const bool aborted = ld_shared_i32_volatile(sm + M::ABORT) != 0;
   if (aborted && warp == kProducerWarp && lane == 0) {
     // give this CTA's own bulk copies a bounded chance to land before the shared memory is released
-    mbar_wait(smem_u32(bar_a_full), 0);
-    for (int s = 0; s < S; ++s) {
-      for (int par = 0; par < 2; ++par) {
-        if (mbar_try_wait(smem_u32(bar_b_full + s), par)) break;
-      }
+    // (the B and vector "full" barriers lie next to each other in the map: one rolled loop over all of them)
+    mbar_wait(sm + M::A_FULL, 0);
+#pragma unroll 1
+    for (uint32_t bar = sm + M::B_FULL; bar < sm + M::B_FULL + 8 * S; bar += 8) {
+      if (!mbar_try_wait(bar, 0)) mbar_try_wait(bar, 1);
     }
-    for (int s = 0; s < VS; ++s) {
-      for (int par = 0; par < 2; ++par) {
-        if (mbar_try_wait(smem_u32(bar_v_full + s), par)) break;
-      }
+#pragma unroll 1
+    for (uint32_t bar = sm + M::V_FULL; bar < sm + M::V_FULL + 8 * VS; bar += 8) {
+      if (!mbar_try_wait(bar, 0)) mbar_try_wait(bar, 1);
     }
   }
   __syncthreads();
@@ -926,32 +1040,40 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
   }
 }
 
-template <int KT, int NSLAB, int TT>
+template <int KT, int NSLAB, int TT, bool FOLD>
 int launch_sweep_inst(const SweepArgs& args, int grid_x, int t_chunks, cudaStream_t stream) {
-  constexpr size_t smem = tc_smem_bytes<NSLAB, TT>();
+  constexpr size_t smem = tc_smem_bytes<NSLAB, TT, FOLD>();
   static_assert(smem > 116 * 1024, "one CTA per SM is assumed (each CTA takes all 512 TMEM columns)");
   static_assert(smem <= 227 * 1024, "shared memory budget exceeded");
   static bool configured[16] = {false};
   int dev = 0;
   FLK_CUDA_TRY(cudaGetDevice(&dev));
   if (dev >= 16 || !configured[dev]) {
-    FLK_CUDA_TRY(cudaFuncSetAttribute(kmv_tc_kernel<KT, NSLAB, TT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    FLK_CUDA_TRY(cudaFuncSetAttribute(kmv_tc_kernel<KT, NSLAB, TT, FOLD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)smem));
     if (dev < 16) configured[dev] = true;
   }
   dim3 grid((unsigned)grid_x, (unsigned)t_chunks, 1);
-  kmv_tc_kernel<KT, NSLAB, TT><<<grid, kThreads, smem, stream>>>(args);
+  kmv_tc_kernel<KT, NSLAB, TT, FOLD><<<grid, kThreads, smem, stream>>>(args);
   FLK_CUDA_TRY(cudaGetLastError());
   return FLK_OK;
 }
 
 template <int KT, int NSLAB>
 int launch_sweep_tt(const SweepArgs& args, int tt, int grid_x, int t_chunks, cudaStream_t stream) {
+  if constexpr (KT == FLK_GAUSSIAN) {
+    if (args.fold != nullptr) {
+      if (tt != 1) return fail(FLK_ERR_BAD_ARG, "internal: a folded sweep has one vector column, not %d", tt);
+      return launch_sweep_inst<KT, NSLAB, 1, true>(args, grid_x, t_chunks, stream);
+    }
+  } else if (args.fold != nullptr) {
+    return fail(FLK_ERR_BAD_ARG, "internal: only the Gaussian sweep folds its vector");
+  }
   switch (tt) {
-    case 1: return launch_sweep_inst<KT, NSLAB, 1>(args, grid_x, t_chunks, stream);
-    case 2: return launch_sweep_inst<KT, NSLAB, 2>(args, grid_x, t_chunks, stream);
-    case 4: return launch_sweep_inst<KT, NSLAB, 4>(args, grid_x, t_chunks, stream);
-    case kWideTT: return launch_sweep_inst<KT, NSLAB, kWideTT>(args, grid_x, t_chunks, stream);
+    case 1: return launch_sweep_inst<KT, NSLAB, 1, false>(args, grid_x, t_chunks, stream);
+    case 2: return launch_sweep_inst<KT, NSLAB, 2, false>(args, grid_x, t_chunks, stream);
+    case 4: return launch_sweep_inst<KT, NSLAB, 4, false>(args, grid_x, t_chunks, stream);
+    case kWideTT: return launch_sweep_inst<KT, NSLAB, kWideTT, false>(args, grid_x, t_chunks, stream);
   }
   return fail(FLK_ERR_BAD_ARG, "internal: unsupported TT=%d", tt);
 }

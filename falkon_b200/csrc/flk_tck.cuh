@@ -35,7 +35,14 @@ constexpr int kColSplitL = 2;                           // epilogue warps per (r
 constexpr int kEpiWarpsL = 4 * kRowBlocksL * kColSplitL;
 constexpr int kMmaWarpL = kEpiWarpsL;                   // warps 16, 17: MMA issuer of row block (warp - 16)
 constexpr int kProducerWarpL = kEpiWarpsL + kRowBlocksL;
-constexpr int kThreadsL = (kEpiWarpsL + kRowBlocksL + 1) * 32;
+// warp 19 does no work: it completes the warpgroup of the two issuers and the producer, so that this group can
+// hand registers to the four epilogue warpgroups (setmaxnreg works on whole warpgroups, see flk_tc.cuh).  20 warps
+// = 5 per SM sub-partition = 96 registers per thread at launch; afterwards 16 x 104 + 4 x 64 = 20 x 96.
+constexpr int kThreadsL = (kEpiWarpsL + kRowBlocksL + 2) * 32;
+constexpr int kRegsEpilogueL = 104;
+constexpr int kRegsOthersL = 64;
+static_assert(kEpiWarpsL * kRegsEpilogueL + 4 * kRegsOthersL <= (kThreadsL / 32) * 96,
+              "register re-partitioning exceeds the pool the CTA is launched with");
 
 inline bool supports_d(int64_t d) { return d > tc::kMaxD && d <= kMaxDL; }
 inline int used_k(int64_t d) { return (int)(3 * d + 6); }  // always three norm pieces
@@ -208,6 +215,8 @@ __device__ __forceinline__ void epilogue_wide32(const uint32_t (&r)[32], const f
   }
 }
 
+__device__ __forceinline__ void report_timeout(int* status, int code) { atomicExch(status + kStatusTimeout, code); }
+
 template <int KT, int TT, bool ARES>
 __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL p) {
   constexpr int S = RingCfg<TT>::S, VS = RingCfg<TT>::VS;
@@ -216,23 +225,18 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
   extern __shared__ unsigned char tck_smem_raw[];
   const uint32_t raw_addr = smem_u32(tck_smem_raw);
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
-  unsigned char* smem = tck_smem_raw + pad;
-  unsigned char* a_res = smem;                                          // ARES: [2 row blocks][nslab] slabs
-  unsigned char* ring = smem + kAResBytes;                              // [S][A0 | A1 | B] or [S][B] slabs
-  float* vs = reinterpret_cast<float*>(ring + S * kStageBytes);         // [VS][128][TT]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(vs) + VS * kColsPerTile * TT * 4);
-  // barrier map: s_full[S] | s_empty[S] | v_full[VS] | v_empty[VS] | t_full[4] | t_empty[4] (index rb * 2 + buf) | a_full
-  uint64_t* bar_s_full = bars;
-  uint64_t* bar_s_empty = bar_s_full + S;
-  uint64_t* bar_v_full = bar_s_empty + S;
-  uint64_t* bar_v_empty = bar_v_full + VS;
-  uint64_t* bar_t_full = bar_v_empty + VS;
-  uint64_t* bar_t_empty = bar_t_full + 4;
-  uint64_t* bar_a_full = bar_t_empty + 4;
-  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bar_a_full + 1);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
-  static_assert((2 * S + 2 * VS + 9) * 8 + 8 <= 512, "barrier block overflows its 512 bytes");
-  float* combine = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(bars) + 512);  // [256 rows][TT]
+  // Shared-memory map as 32-bit shared addresses from one base (generic pointers to every ring and barrier would
+  // stay live across all warp roles): [A blocks, ARES only] | operand ring | vector ring | barrier block | combine.
+  // barrier block: s_full[S] | s_empty[S] | v_full[VS] | v_empty[VS] | t_full[4] | t_empty[4] (index rb * 2 + buf) |
+  // a_full | tmem pointer | abort flag
+  const uint32_t sm = raw_addr + pad;
+  constexpr uint32_t kRingOff = kAResBytes;
+  constexpr uint32_t kVecOff = kRingOff + S * kStageBytes;
+  constexpr uint32_t kBarsOff = kVecOff + VS * kColsPerTile * TT * 4;
+  constexpr uint32_t kSFull = kBarsOff, kSEmpty = kSFull + 8 * S, kVFull = kSEmpty + 8 * S, kVEmpty = kVFull + 8 * VS;
+  constexpr uint32_t kTFull = kVEmpty + 8 * VS, kTEmpty = kTFull + 32, kAFull = kTEmpty + 32;
+  constexpr uint32_t kTmemPtr = kAFull + 8, kAbort = kTmemPtr + 4, kCombineOff = kBarsOff + 512;
+  static_assert(kAbort + 4 <= kCombineOff, "barrier block overflows its 512 bytes");
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
@@ -253,74 +257,78 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
   if (skip_launch) return;
 
   if (tid == 0) {
+#pragma unroll 1
     for (int s = 0; s < S; ++s) {
-      mbar_init(smem_u32(bar_s_full + s), 1);
-      mbar_init(smem_u32(bar_s_empty + s), kRowBlocksL);  // one MMA commit per issuer
+      mbar_init(sm + kSFull + 8 * s, 1);
+      mbar_init(sm + kSEmpty + 8 * s, kRowBlocksL);  // one MMA commit per issuer
     }
     for (int s = 0; s < VS; ++s) {
-      mbar_init(smem_u32(bar_v_full + s), 1);
-      mbar_init(smem_u32(bar_v_empty + s), kEpiWarpsL);
+      mbar_init(sm + kVFull + 8 * s, 1);
+      mbar_init(sm + kVEmpty + 8 * s, kEpiWarpsL);
     }
     for (int i = 0; i < 4; ++i) {
-      mbar_init(smem_u32(bar_t_full + i), 1);
-      mbar_init(smem_u32(bar_t_empty + i), 4 * kColSplitL);  // the eight warps of that row block
+      mbar_init(sm + kTFull + 8 * i, 1);
+      mbar_init(sm + kTEmpty + 8 * i, 4 * kColSplitL);  // the eight warps of that row block
     }
-    mbar_init(smem_u32(bar_a_full), 1);
-    *abort_flag = 0;
+    mbar_init(sm + kAFull, 1);
+    st_shared_i32_volatile(sm + kAbort, 0);
     fence_barrier_init();
   }
   if (warp == kMmaWarpL) {
-    tmem_alloc(smem_u32(tmem_ptr), 512);
+    tmem_alloc(sm + kTmemPtr, 512);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_base = *tmem_ptr;
+  const uint32_t tmem_base = (uint32_t)ld_shared_i32_volatile(sm + kTmemPtr);
 
-  if (warp == kProducerWarpL) {
+  if (warp > kProducerWarpL) {
+    reg_release<kRegsOthersL>();  // filler warp of the issuers' and the producer's warpgroup
+  } else if (warp == kProducerWarpL) {
     // ------------------------------ bulk-copy producer ------------------------------
+    reg_release<kRegsOthersL>();
     const __half* a_base = p.img_a + (int64_t)row_tile * kRowBlocksL * nslab * (kTileRows * kSlabK);
     const float* vec_base = p.vec + (int64_t)tchunk * p.s_pad * TT;
     if (ARES && elect_one()) {
       // the CTA's two A blocks are contiguous in the image: [row block][slab]
       const uint32_t bytes = (uint32_t)(kRowBlocksL * nslab * kSlabBytes);
-      mbar_expect_tx(smem_u32(bar_a_full), bytes);
+      mbar_expect_tx(sm + kAFull, bytes);
       for (int i = 0; i < kRowBlocksL * nslab; ++i)
-        bulk_copy_g2s(smem_u32(a_res) + i * kSlabBytes, a_base + (int64_t)i * (kTileRows * kSlabK), kSlabBytes,
-                      smem_u32(bar_a_full));
+        bulk_copy_g2s(sm + i * kSlabBytes, a_base + (int64_t)i * (kTileRows * kSlabK), kSlabBytes,
+                      sm + kAFull);
     }
     __syncwarp();
-    int64_t gs = 0;  // running slab counter
+    uint32_t gs = 0;  // running slab counter
     bool ok = true;
     for (int j = 0; ok && j < ntiles; ++j) {
       const int64_t ct = tile_begin + j;
       const int vstage = j % VS;
-      if (!mbar_wait(smem_u32(bar_v_empty + vstage), ((j / VS) & 1) ^ 1)) {
-        if (lane == 0) atomicExch(p.status + kStatusTimeout, kErrProducer | 2);
-        *abort_flag = 1;
+      if (!mbar_wait(sm + kVEmpty + 8 * vstage, ((j / VS) & 1) ^ 1)) {
+        if (lane == 0) report_timeout(p.status, kErrProducer | 2);
+        st_shared_i32_volatile(sm + kAbort, 1);
         break;
       }
       if (elect_one()) {
-        const uint32_t vbar = smem_u32(bar_v_full + vstage);
+        const uint32_t vbar = sm + kVFull + 8 * vstage;
         mbar_expect_tx(vbar, kColsPerTile * TT * 4);
-        bulk_copy_g2s(smem_u32(vs) + vstage * kColsPerTile * TT * 4, vec_base + ct * kColsPerTile * TT,
+        bulk_copy_g2s(sm + kVecOff + vstage * kColsPerTile * TT * 4, vec_base + ct * kColsPerTile * TT,
                       kColsPerTile * TT * 4, vbar);
       }
       __syncwarp();
       const __half* b_base = p.img_b + ct * nslab * (kTileRows * kSlabK);
       for (int s = 0; s < nslab; ++s, ++gs) {
-        const int stage = (int)(gs % S);
-        if (*abort_flag) { ok = false; break; }
-        if (!mbar_wait(smem_u32(bar_s_empty + stage), (uint32_t)(((gs / S) & 1) ^ 1))) {
-          if (lane == 0) atomicExch(p.status + kStatusTimeout, kErrProducer | 1);
-          *abort_flag = 1;
+        const int stage = (int)(gs % (uint32_t)S);
+        if (ld_shared_i32_volatile(sm + kAbort)) { ok = false; break; }
+        if (!mbar_wait(sm + kSEmpty + 8 * stage, ((gs / (uint32_t)S) & 1u) ^ 1u)) {
+          if (lane == 0) report_timeout(p.status, kErrProducer | 1);
+          st_shared_i32_volatile(sm + kAbort, 1);
           ok = false;
           break;
         }
         if (elect_one()) {
-          const uint32_t bar = smem_u32(bar_s_full + stage);
-          const uint32_t dst = smem_u32(ring) + stage * kStageBytes;
+          const uint32_t bar = sm + kSFull + 8 * stage;
+          const uint32_t dst = sm + kRingOff + stage * kStageBytes;
           mbar_expect_tx(bar, kStageBytes);
           if (!ARES) {
             bulk_copy_g2s(dst, a_base + (int64_t)s * (kTileRows * kSlabK), kSlabBytes, bar);
@@ -333,50 +341,52 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
     }
   } else if (warp >= kMmaWarpL) {
     // ------------------------------ MMA issuers (one per row block) ------------------------------
+    reg_release<kRegsOthersL>();
     const int rb = warp - kMmaWarpL;
-    int64_t gs = 0;
+    uint32_t gs = 0;
     bool ok = true;
-    if (ARES && !mbar_wait(smem_u32(bar_a_full), 0)) {
-      if (lane == 0) atomicExch(p.status + kStatusTimeout, kErrMma | 1);
-      *abort_flag = 1;
+    if (ARES && !mbar_wait(sm + kAFull, 0)) {
+      if (lane == 0) report_timeout(p.status, kErrMma | 1);
+      st_shared_i32_volatile(sm + kAbort, 1);
       ok = false;
     }
     for (int j = 0; ok && j < ntiles; ++j) {
       const int buf = j & 1;
-      if (*abort_flag) break;
+      if (ld_shared_i32_volatile(sm + kAbort)) break;
       // this row block's accumulator of this buffer must have been drained (tile j - 2)
-      if (!mbar_wait(smem_u32(bar_t_empty + rb * 2 + buf), ((j >> 1) & 1) ^ 1)) {
-        if (lane == 0) atomicExch(p.status + kStatusTimeout, kErrMma | 3);
-        *abort_flag = 1;
+      if (!mbar_wait(sm + kTEmpty + 8 * (rb * 2 + buf), ((j >> 1) & 1) ^ 1)) {
+        if (lane == 0) report_timeout(p.status, kErrMma | 3);
+        st_shared_i32_volatile(sm + kAbort, 1);
         break;
       }
       const uint32_t d_tmem = tmem_base + (uint32_t)((rb * 2 + buf) * kColsPerTile);
       for (int s = 0; s < nslab; ++s, ++gs) {
-        const int stage = (int)(gs % S);
-        if (!mbar_wait(smem_u32(bar_s_full + stage), (uint32_t)((gs / S) & 1))) {
-          if (lane == 0) atomicExch(p.status + kStatusTimeout, kErrMma | 2);
-          *abort_flag = 1;
+        const int stage = (int)(gs % (uint32_t)S);
+        if (!mbar_wait(sm + kSFull + 8 * stage, (gs / (uint32_t)S) & 1u)) {
+          if (lane == 0) report_timeout(p.status, kErrMma | 2);
+          st_shared_i32_volatile(sm + kAbort, 1);
           ok = false;
           break;
         }
         tc_fence_after();
         if (elect_one()) {
-          const uint32_t sbase = smem_u32(ring) + stage * kStageBytes;
+          const uint32_t sbase = sm + kRingOff + stage * kStageBytes;
           const uint64_t b_desc = make_smem_desc(sbase + (ARES ? 0 : 2) * kSlabBytes);
-          const uint64_t a_desc = make_smem_desc(ARES ? smem_u32(a_res) + (rb * nslab + s) * kSlabBytes
+          const uint64_t a_desc = make_smem_desc(ARES ? sm + (rb * nslab + s) * kSlabBytes
                                                       : sbase + rb * kSlabBytes);
           const int nks = min(2, p.ksteps - 2 * s);  // K-steps of this slab that carry data
           for (int ks = 0; ks < nks; ++ks)
             mma_f16(d_tmem, a_desc + (uint64_t)(ks * 2), b_desc + (uint64_t)(ks * 2), kInstrDesc,
                     (s > 0 || ks > 0) ? 1u : 0u);
-          mma_commit(smem_u32(bar_s_empty + stage));
-          if (s == nslab - 1) mma_commit(smem_u32(bar_t_full + rb * 2 + buf));
+          mma_commit(sm + kSEmpty + 8 * stage);
+          if (s == nslab - 1) mma_commit(sm + kTFull + 8 * (rb * 2 + buf));
         }
         __syncwarp();
       }
     }
   } else {
     // ------------------------------ epilogue warps ------------------------------
+    reg_claim<kRegsEpilogueL>();
     const int q = warp & 3;
     const int rb = (warp >> 2) & 1;
     const int half = warp >> 3;  // columns half * 64 .. + 63 of every tile
@@ -402,18 +412,18 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
     const int j1 = min(j0 + tc::kFlushTiles, ntiles);
     for (int j = j0; j < j1; ++j) {
       const int vstage = j % VS, buf = j & 1;
-      if (*abort_flag) { epi_ok = false; break; }
-      if (!mbar_wait(smem_u32(bar_v_full + vstage), (j / VS) & 1) ||
-          !mbar_wait(smem_u32(bar_t_full + rb * 2 + buf), (j >> 1) & 1)) {
-        atomicExch(p.status + kStatusTimeout, kErrEpilogue | 1);
-        *abort_flag = 1;
+      if (ld_shared_i32_volatile(sm + kAbort)) { epi_ok = false; break; }
+      if (!mbar_wait(sm + kVFull + 8 * vstage, (j / VS) & 1) ||
+          !mbar_wait(sm + kTFull + 8 * (rb * 2 + buf), (j >> 1) & 1)) {
+        report_timeout(p.status, kErrEpilogue | 1);
+        st_shared_i32_volatile(sm + kAbort, 1);
         epi_ok = false;
         break;
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) +
                              (uint32_t)((rb * 2 + buf) * kColsPerTile + half * 64);
-      const float* vsm = vs + (vstage * kColsPerTile + half * 64) * TT;
+      const float* vsm = reinterpret_cast<const float*>(tck_smem_raw + pad + kVecOff) + (vstage * kColsPerTile + half * 64) * TT;
       if constexpr (TT == kWideTT) {
         // 32 running sums per thread leave room for one 32-column piece at a time
         uint32_t ra[32];
@@ -424,7 +434,7 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
         tmem_ld_wait_on(ra);
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(bar_t_empty + rb * 2 + buf));
+        if (lane == 0) mbar_arrive(sm + kTEmpty + 8 * (rb * 2 + buf));
         epilogue_wide32<KT>(ra, vsm + 32 * TT, osum);
       } else {
         uint32_t ra[32], rc[32];
@@ -435,12 +445,12 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
         // this warp's 64 columns are in registers: hand the accumulator back before evaluating them
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(bar_t_empty + rb * 2 + buf));
+        if (lane == 0) mbar_arrive(sm + kTEmpty + 8 * (rb * 2 + buf));
         epilogue_32<KT, TT>(ra, vsm, osum);
         epilogue_32<KT, TT>(rc, vsm + 32 * TT, osum);
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(bar_v_empty + vstage));
+      if (lane == 0) mbar_arrive(sm + kVEmpty + 8 * vstage);
     }
     }
     // per-thread sums of this column half
@@ -469,13 +479,14 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
       }
     }
     const int rloc = rb * kTileRows + q * 32 + lane;
+    float* combine = reinterpret_cast<float*>(tck_smem_raw + pad + kCombineOff);  // [256 rows][TT]
     if (half == 1) {
 #pragma unroll
       for (int t = 0; t < TT; ++t) combine[rloc * TT + t] = o[t];
     }
     // all sixteen epilogue warps meet here (named barrier 1; the issuer and producer warps do not take part)
     asm volatile("bar.sync 1, %0;" ::"n"(kEpiWarpsL * 32) : "memory");
-    if (half == 0 && epi_ok && *abort_flag == 0) {
+    if (half == 0 && epi_ok && ld_shared_i32_volatile(sm + kAbort) == 0) {
       const int64_t row = (int64_t)row_tile * kRowsPerCtaL + rloc;
       float* dst = p.raw + ((int64_t)chunk * p.r_pad + row) * p.tp + tchunk * TT;
 #pragma unroll
@@ -486,16 +497,16 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
   // ------------------------------ teardown ------------------------------
   tc_fence_before();
   __syncthreads();
-  const bool aborted = (*abort_flag != 0);
+  const bool aborted = (ld_shared_i32_volatile(sm + kAbort) != 0);
   if (aborted && warp == kProducerWarpL && lane == 0) {
     // give this CTA's own bulk copies a bounded chance to land before the shared memory is released
-    if (ARES) mbar_wait(smem_u32(bar_a_full), 0);
-    for (int s = 0; s < S; ++s)
-      for (int par = 0; par < 2; ++par)
-        if (mbar_try_wait(smem_u32(bar_s_full + s), par)) break;
-    for (int s = 0; s < VS; ++s)
-      for (int par = 0; par < 2; ++par)
-        if (mbar_try_wait(smem_u32(bar_v_full + s), par)) break;
+    if (ARES) mbar_wait(sm + kAFull, 0);
+#pragma unroll 1
+    for (uint32_t bar = sm + kSFull; bar < sm + kSFull + 8 * S; bar += 8)
+      if (!mbar_try_wait(bar, 0)) mbar_try_wait(bar, 1);
+#pragma unroll 1
+    for (uint32_t bar = sm + kVFull; bar < sm + kVFull + 8 * VS; bar += 8)
+      if (!mbar_try_wait(bar, 0)) mbar_try_wait(bar, 1);
   }
   __syncthreads();
   if (warp == kMmaWarpL) {

@@ -157,3 +157,31 @@ def test_status_maps_to_reference_exception_types(lib):
         _lib.raise_for_status(_lib.FLK_ERR_UNSUPPORTED)
     with pytest.raises(RuntimeError):
         _lib.raise_for_status(_lib.FLK_ERR_CUDA)
+
+
+def test_register_report_parser_and_guard():
+    """The build reads `ptxas -v` and refuses a tensor-core sweep that spills or whose launch register count is not
+    the one its register re-partitioning assumes (falkon_b200/_lib.py: parse_ptxas, check_ptxas)."""
+    from falkon_b200 import _lib
+
+    def entry(mangled, stack, st, ld, regs):
+        return (f"ptxas info    : Compiling entry function '{mangled}' for 'sm_100a'\n"
+                f"ptxas info    : Function properties for {mangled}\n"
+                f"    {stack} bytes stack frame, {st} bytes spill stores, {ld} bytes spill loads\n"
+                f"ptxas info    : Used {regs} registers, used 1 barriers, 16 bytes smem\n")
+
+    tc = "_ZN3flk2tc13kmv_tc_kernelILi0ELi3ELi1ELb1EEEvNS0_9SweepArgsE"
+    tck = "_ZN3flk3tck14kmv_tck_kernelILi0ELi1ELb0EEEvNS0_10SweepArgsLE"
+    good = _lib.parse_ptxas(entry(tc, 0, 0, 0, 80) + entry(tck, 8, 8, 40, 96))
+    assert len(good) == 2 and _lib.check_ptxas(good) == []
+    assert any("spill" in p for p in _lib.check_ptxas(_lib.parse_ptxas(entry(tc, 8, 4, 4, 80))))
+    assert any("registers per thread" in p for p in _lib.check_ptxas(_lib.parse_ptxas(entry(tc, 0, 0, 0, 72))))
+    assert any("allowance" in p for p in _lib.check_ptxas(_lib.parse_ptxas(entry(tc, 0, 0, 0, 80) + entry(tck, 64, 80, 200, 96))))
+    assert any("no tc::kmv_tc_kernel" in p for p in _lib.check_ptxas(_lib.parse_ptxas(entry(tck, 0, 0, 0, 96))))
+    # the library on disk was built under the same guard: its report has no offending row
+    import os
+
+    if os.path.exists(_lib.PTXAS_REPORT):
+        rows = [l.split(" | ") for l in open(_lib.PTXAS_REPORT).read().splitlines()[2:]]
+        tc_rows = [r for r in rows if "tc::kmv_tc_kernel" in r[0]]
+        assert tc_rows and all(r[1] == "80" and r[3] == "0" and r[4] == "0" for r in tc_rows)
