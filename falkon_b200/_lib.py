@@ -242,7 +242,7 @@ def workspace(device: torch.device, nbytes: int) -> torch.Tensor:
         if buf is not None:
             del _workspaces[key]
             del buf
-        buf = torch.empty(int(nbytes * 1.05) + 4096, dtype=torch.uint8, device=device)
+        buf = torch.empty(int(nbytes) + 4096, dtype=torch.uint8, device=device)
         _workspaces[key] = buf
     return buf
 
@@ -300,6 +300,87 @@ def _check_operands(host: bool, **named):
                 raise ValueError(f"{name} must be on a CUDA device (found {t.device})")
             if t.device != device:
                 raise ValueError(f"All operands must be on the same device ({name} is on {t.device}, expected {device})")
+
+
+def rows_within_budget(query, n: int, budget: Optional[float]) -> int:
+    """Largest number of rows r <= n (a multiple of 512 unless r == n) whose workspace ``query(r)`` fits ``budget``
+    bytes; n itself when there is no budget.  Raises MemoryError when even 512 rows do not fit, as the reference
+    does when its block-size model cannot place a single block (falkon/utils/helpers.py:83-84)."""
+    if budget is None or budget == float("inf") or query(n) <= budget:
+        return n
+    lo = 512
+    if n <= lo or query(lo) > budget:
+        raise MemoryError(
+            f"Available memory ({budget / 2**20:.1f} MiB) is not enough for the workspace of even {min(n, lo)} rows "
+            f"({query(min(n, lo)) / 2**20:.1f} MiB); raise max_gpu_mem")
+    hi = n  # query(hi) > budget
+    while hi - lo > 512:
+        mid = (lo + hi) // 2 // 512 * 512
+        if mid <= lo:
+            break
+        if query(mid) <= budget:
+            lo = mid
+        else:
+            hi = mid
+    return lo
+
+
+def call_fmmv_budgeted(kernel_id, sigma, X1, X2, v, out, flags=0, host=False, device=None, budget=None):
+    """``call_fmmv`` under a device-memory budget (bytes): when the workspace of the whole problem exceeds it, the
+    larger operand is cut into row chunks -- rows of X1 produce independent rows of ``out``; rows of X2 (with the
+    matching rows of v) are summed into ``out`` with FLK_FLAG_ACCUMULATE."""
+    lib = load()
+    dt = dtype_code(X1.dtype)
+    n, d = X1.shape
+    m = X2.shape[0]
+    t = v.shape[1] if v.dim() == 2 else 1
+    wsq = lib.flk_fmmv_host_workspace_bytes if host else lib.flk_fmmv_workspace_bytes
+    if budget is None or wsq(dt, kernel_id, n, m, d, t, flags) <= budget:
+        return call_fmmv(kernel_id, sigma, X1, X2, v, out, flags=flags, host=host, device=device)
+    if n >= m:
+        step = rows_within_budget(lambda r: wsq(dt, kernel_id, r, m, d, t, flags), n, budget)
+        for r0 in range(0, n, step):
+            call_fmmv(kernel_id, sigma, X1[r0:r0 + step], X2, v, out[r0:r0 + step], flags=flags, host=host, device=device)
+        return out
+    step = rows_within_budget(lambda r: wsq(dt, kernel_id, n, r, d, t, flags), m, budget)
+    part = torch.empty_like(out) if host else None
+    for i, r0 in enumerate(range(0, m, step)):
+        if host:  # the host-buffer entry point writes host memory: sum the partial results there
+            call_fmmv(kernel_id, sigma, X1, X2[r0:r0 + step], v[r0:r0 + step], out if i == 0 else part, flags=flags,
+                      host=True, device=device)
+            if i > 0:
+                out.add_(part)
+        else:
+            call_fmmv(kernel_id, sigma, X1, X2[r0:r0 + step], v[r0:r0 + step], out,
+                      flags=flags | (FLAG_ACCUMULATE if i > 0 else 0))
+    return out
+
+
+def call_fdmmv_budgeted(kernel_id, sigma, X1, X2, v, w, out, flags=0, host=False, device=None, budget=None):
+    """``call_fdmmv`` under a device-memory budget (bytes): K^T (K v + w) is a sum over row blocks of X1 (the
+    reference's own blocking, falkon/mmv_ops/fmmv.py:740-760), accumulated into ``out``."""
+    lib = load()
+    dt = dtype_code(X1.dtype)
+    n, d = X1.shape
+    m = X2.shape[0]
+    lead = v if v is not None else w
+    t = lead.shape[1] if lead is not None and lead.dim() == 2 else 1
+    wsq = lib.flk_fdmmv_host_workspace_bytes if host else lib.flk_fdmmv_workspace_bytes
+    if budget is None or wsq(dt, kernel_id, n, m, d, t, flags) <= budget:
+        return call_fdmmv(kernel_id, sigma, X1, X2, v, w, out, flags=flags, host=host, device=device)
+    step = rows_within_budget(lambda r: wsq(dt, kernel_id, r, m, d, t, flags), n, budget)
+    part = torch.empty_like(out) if host else None
+    for i, r0 in enumerate(range(0, n, step)):
+        wc = None if w is None else w[r0:r0 + step]
+        if host:
+            call_fdmmv(kernel_id, sigma, X1[r0:r0 + step], X2, v, wc, out if i == 0 else part, flags=flags, host=True,
+                       device=device)
+            if i > 0:
+                out.add_(part)
+        else:
+            call_fdmmv(kernel_id, sigma, X1[r0:r0 + step], X2, v, wc, out,
+                       flags=flags | (FLAG_ACCUMULATE if i > 0 else 0))
+    return out
 
 
 def call_fmmv(kernel_id, sigma, X1, X2, v, out, flags=0, host=False, device=None):

@@ -589,8 +589,11 @@ static int fmmv_impl(int dtype, int kernel, const Mat& X1, const Mat& X2, const 
   FLK_TRY(run_prep_vec<T>(v, L.vbuf, L.s1.s_pad, L.s1.tp, L.s1.tt, stream));
   FoldSigma fs;
   if constexpr (sizeof(T) == 4) fs = FoldSigma{sig_dev, sig_scalar, (int)sigma_len};
-  FLK_TRY(sweep_and_finalize<T>(L, kernel, dtype, d, t, L.s1, L.f1, L.x1, L.x2, L.vbuf, L.raw1, L.fraw1, nullptr,
-                                out, out_rs, out_cs, false, stream, 0, X2, fs));
+  // FLK_FLAG_ACCUMULATE: out += K v (column chunks of a product whose reduction side is split under a memory budget)
+  const Mat prev{out, n, t, out_rs, out_cs};
+  FLK_TRY(sweep_and_finalize<T>(L, kernel, dtype, d, t, L.s1, L.f1, L.x1, L.x2, L.vbuf, L.raw1, L.fraw1,
+                                (flags & FLK_FLAG_ACCUMULATE) ? &prev : nullptr, out, out_rs, out_cs, false, stream, 0,
+                                X2, fs));
   return FLK_OK;
 }
 

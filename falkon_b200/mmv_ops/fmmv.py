@@ -48,6 +48,26 @@ def _flags(opt) -> int:
     return int(getattr(opt, "flk_flags", 0) or 0)
 
 
+def device_budget(opt, dev: torch.device) -> Optional[float]:
+    """Bytes the products may take on ``dev`` for their workspace: ``min(free, max_gpu_mem) * memory_slack``, the
+    reference's rule (falkon/mmv_ops/utils.py:47-57); "free" counts the cached workspace of this package as
+    available, since it is what would be reused.  None when neither limit binds (max_gpu_mem = inf and no way to
+    ask the device, e.g. in CPU-only tests)."""
+    limit = float(getattr(opt, "max_gpu_mem", float("inf")) or float("inf")) if opt is not None else float("inf")
+    slack = float(getattr(opt, "memory_slack", 0.9) or 0.9) if opt is not None else 0.9
+    free = float("inf")
+    if torch.cuda.is_available() and dev.type == "cuda":
+        try:
+            free_now, _ = torch.cuda.mem_get_info(dev)
+            held = _lib._workspaces.get((dev.type, dev.index))
+            cached = torch.cuda.memory_reserved(dev) - torch.cuda.memory_allocated(dev)
+            free = float(free_now + cached + (held.numel() if held is not None else 0))
+        except Exception:  # pragma: no cover - a device that cannot be queried imposes no limit of its own
+            free = float("inf")
+    budget = min(free, limit)
+    return None if budget == float("inf") else budget * slack
+
+
 def _pick_device(devs):
     cuda = [d for d in devs if d.type == "cuda"]
     if cuda:
@@ -76,11 +96,12 @@ def _fmmv_forward(X1, X2, v, kernel, out, opt):
             if len(devices) > 1:
                 multi_device.fmmv_host_multi(kernel_id, sigma, X1, X2, v, out, _flags(opt), devices)
             else:
-                _lib.call_fmmv(kernel_id, sigma, X1, X2, v, out, flags=_flags(opt), host=True, device=devices[0])
+                _lib.call_fmmv_budgeted(kernel_id, sigma, X1, X2, v, out, flags=_flags(opt), host=True,
+                                        device=devices[0], budget=device_budget(opt, devices[0]))
         else:
             o_dev = out if out.device == dev else torch.empty(out.shape, dtype=out.dtype, device=dev)
-            _lib.call_fmmv(kernel_id, sigma, _to_dev(X1, dev), _to_dev(X2, dev), _to_dev(v, dev), o_dev,
-                           flags=_flags(opt))
+            _lib.call_fmmv_budgeted(kernel_id, sigma, _to_dev(X1, dev), _to_dev(X2, dev), _to_dev(v, dev), o_dev,
+                                    flags=_flags(opt), budget=device_budget(opt, dev))
             if o_dev is not out:
                 out.copy_(o_dev)
     return out
@@ -218,12 +239,12 @@ def fdmmv(
             if len(devices) > 1:
                 multi_device.fdmmv_host_multi(kernel_id, sigma, X1, X2, v, w, out, _flags(opt), devices)
             else:
-                _lib.call_fdmmv(kernel_id, sigma, X1, X2, v, w, out, flags=_flags(opt), host=True,
-                                device=devices[0])
+                _lib.call_fdmmv_budgeted(kernel_id, sigma, X1, X2, v, w, out, flags=_flags(opt), host=True,
+                                         device=devices[0], budget=device_budget(opt, devices[0]))
         else:
             o_dev = out if out.device == dev else torch.empty(out.shape, dtype=out.dtype, device=dev)
-            _lib.call_fdmmv(kernel_id, sigma, _to_dev(X1, dev), _to_dev(X2, dev), _to_dev(v, dev),
-                            _to_dev(w, dev), o_dev, flags=_flags(opt))
+            _lib.call_fdmmv_budgeted(kernel_id, sigma, _to_dev(X1, dev), _to_dev(X2, dev), _to_dev(v, dev),
+                                     _to_dev(w, dev), o_dev, flags=_flags(opt), budget=device_budget(opt, dev))
             if o_dev is not out:
                 out.copy_(o_dev)
     return out

@@ -57,8 +57,8 @@ typedef enum flk_kernel {
 #define FLK_FLAG_FP64_MATH 4  /* flk_fmm / flk_kgrad: evaluate fp32 data in fp64, round on store */
 #define FLK_FLAG_NO_FOLD 8    /* Gaussian, t = 1, tensor-core path: keep the vector out of the operand images
                                  (the sweep then multiplies by it in its epilogue; diagnostics / comparison) */
-#define FLK_FLAG_ACCUMULATE 16 /* flk_fdmmv: add the result to what `out` holds instead of overwriting it
-                                 (row chunks of X1 are summed this way under a memory budget) */
+#define FLK_FLAG_ACCUMULATE 16 /* flk_fmmv / flk_fdmmv: add the result to what `out` holds instead of overwriting it
+                                 (chunks of the reduction side are summed this way under a memory budget) */
 
 /* Library version (major * 10000 + minor * 100 + patch). */
 int flk_version(void);

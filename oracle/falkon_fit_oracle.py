@@ -127,3 +127,25 @@ def falkon_fit(X: torch.Tensor, Y: torch.Tensor, kernel: str, sigma, nu, penalty
 
     beta = conjugate_gradient(B, mmv, maxiter)
     return pc.apply(beta), beta, idx
+
+
+def krr_gradient_norm(X, Y, C, alpha, kernel: str, sigma, nu, penalty: float, weights=None,
+                      max_block_elems: int = 64 * 2**20) -> float:
+    """How well ``alpha`` solves the Nystrom ridge problem, as a backward error evaluated in fp64:
+
+        || K_mn W (K_nm alpha - Y) / n + penalty K_mm alpha ||  /  || K_mn W Y / n ||
+
+    (the gradient of the objective the fit minimises, falkon/models/falkon.py:34-60, relative to its value at
+    alpha = 0).  Unlike alpha itself this is not amplified by the conditioning of the preconditioner's factors, so
+    two fp32 solvers of equal quality give comparable values."""
+    X, Y, C, alpha = (t.double() for t in (X, Y, C, alpha))
+    n = X.shape[0]
+    w = None if weights is None else weights.double()
+    resid = fo.fmmv(X, C, alpha, kernel, sigma, nu, max_block_elems=max_block_elems) - Y
+    y0 = Y
+    if w is not None:
+        resid, y0 = resid * w, Y * w
+    g = fo.fmmv(C, X, resid / n, kernel, sigma, nu, max_block_elems=max_block_elems)
+    g = g + penalty * (kernel_matrix(C, C, kernel, sigma, nu) @ alpha)
+    g0 = fo.fmmv(C, X, y0 / n, kernel, sigma, nu, max_block_elems=max_block_elems)
+    return float(g.norm() / g0.norm())

@@ -211,3 +211,26 @@ def test_falkon_passes_extra_attributes_down():
     o.flk_flags = _lib.FLAG_FORCE_TC
     model = Falkon(kernel=GaussianKernel(1.0), penalty=1e-3, M=5, options=o)
     assert model.kernel._merged(model.options).flk_flags == _lib.FLAG_FORCE_TC
+
+
+def test_rows_within_budget_uses_the_workspace_queries():
+    """Chunk sizing under a memory budget is host arithmetic over the C ABI's workspace queries."""
+    lib = _lib.load()
+
+    def need(r):
+        return lib.flk_fdmmv_workspace_bytes(_lib.FLK_F32, _lib.FLK_GAUSSIAN, r, 50_000, 28, 1, 0)
+
+    n = 10_000_000
+    assert _lib.rows_within_budget(need, n, None) == n
+    assert _lib.rows_within_budget(need, n, float("inf")) == n
+    assert _lib.rows_within_budget(need, n, need(n)) == n
+    budget = 1 * 2**30
+    r = _lib.rows_within_budget(need, n, budget)
+    assert 0 < r < n and r % 512 == 0 and need(r) <= budget < need(r + 1024)
+    with pytest.raises(MemoryError, match="not enough"):
+        _lib.rows_within_budget(need, n, 1 * 2**20)
+    # the budget rule of the products: min(free, max_gpu_mem) * memory_slack; no limit -> None on a CPU-only box
+    from falkon_b200.mmv_ops.fmmv import device_budget
+
+    assert device_budget(FalkonOptions(), torch.device("cpu")) is None
+    assert device_budget(FalkonOptions(max_gpu_mem=1000.0, memory_slack=0.5), torch.device("cpu")) == 500.0
