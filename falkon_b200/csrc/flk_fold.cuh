@@ -96,36 +96,19 @@ __global__ void __launch_bounds__(1024) fold_scan_kernel(int* __restrict__ blk_p
   }
 }
 
-// Writes one reduction-side row (K layout [ch | cl | ch | 1.. | -m.. | 0..]) into its place of the tile images.
-// `xt` = the row's scaled features in shared memory (stride 1), `live_data` false for a null row.
-__device__ __forceinline__ void fold_store_row(__half* __restrict__ img, int64_t dst_row, int kp, int d, int npieces,
-                                               const float* xt, bool live_data, const float (&piece)[3]) {
+// Shared-memory staging of the build kernel: every thread assembles the K-vector of its row ([ch | cl | ch | 1.. |
+// -m.. | 0..], kp fp16 values) in a private strip, region by region, and then moves it out with 16-byte stores.
+// The strips are kFoldStripHalves apart: 104 fp16 = 52 words, an odd multiple of 4 words, so that the 16-byte
+// reads of consecutive rows spread over the banks.
+constexpr int kFoldStripHalves = 104;  // >= the largest padded K of the resident kernel (96), multiple of 8
+
+__device__ __forceinline__ void fold_store_strip(__half* __restrict__ img, int64_t dst_row, int kp,
+                                                 const __half* strip) {
   const int64_t tile = dst_row / kTileRows;
   const int r = (int)(dst_row - tile * kTileRows);
   __half* base = img + tile * ((int64_t)kTileRows * kp);
-  const __half one = __float2half_rn(1.0f), zero = __float2half_rn(0.0f);
-  for (int c = 0; c < kp / 8; ++c) {
-    __align__(16) __half vals[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int k = c * 8 + i;
-      __half h = zero;
-      if (k < 3 * d) {
-        if (live_data) {
-          const int region = k / d, f = k - region * d;
-          const float x = xt[f];
-          const __half hi = __float2half_rn(x);
-          h = region == 1 ? __float2half_rn(x - __half2float(hi)) : hi;  // B: hi, lo, hi
-        }
-      } else if (k < 3 * d + npieces) {
-        h = live_data ? one : zero;
-      } else if (k < 3 * d + 2 * npieces) {
-        h = __float2half_rn(-piece[k - 3 * d - npieces]);
-      }
-      vals[i] = h;
-    }
-    *reinterpret_cast<uint4*>(base + image_offset(r, c * 8)) = *reinterpret_cast<const uint4*>(vals);
-  }
+  for (int c = 0; c < kp / 8; ++c)
+    *reinterpret_cast<uint4*>(base + image_offset(r, c * 8)) = *reinterpret_cast<const uint4*>(strip + c * 8);
 }
 
 __global__ void __launch_bounds__(128) fold_build_kernel(const float* __restrict__ X, int64_t s, int64_t rs, int64_t cs,
@@ -136,21 +119,36 @@ __global__ void __launch_bounds__(128) fold_build_kernel(const float* __restrict
                                                          const int* __restrict__ fold, int n_col_tiles,
                                                          __half* __restrict__ img_b, int* __restrict__ status) {
   __shared__ float xin[kTileRows * 33];
+  __shared__ __align__(16) __half strips[kTileRows * kFoldStripHalves];
   __shared__ float sig[32];
   __shared__ int warp_pos[4];
   const int tid = threadIdx.x;
   const int64_t positives = fold[kFoldPositives];
   const int64_t neg_start = (int64_t)n_col_tiles * kTileRows - (s - positives);
-  float piece[3] = {kFoldNullPiece, 0.0f, 0.0f};
+  __half* strip = strips + tid * kFoldStripHalves;
+  const __half one = __float2half_rn(1.0f), zero = __float2half_rn(0.0f);
+  {  // a null row to start with: every slot zero (the exponent piece is set below)
+    uint4* z = reinterpret_cast<uint4*>(strip);
+    for (int c = 0; c < kp / 8; ++c) z[c] = make_uint4(0u, 0u, 0u, 0u);
+  }
   if ((int)blockIdx.x >= nblk) {
     // the gap between the non-negative entries and the (right-aligned) negative ones: null rows
     const int64_t g = positives + (int64_t)((int)blockIdx.x - nblk) * kTileRows + tid;
-    if (g < neg_start) fold_store_row(img_b, g, kp, d, npieces, xin, false, piece);
+    strip[3 * d + npieces] = __float2half_rn(-kFoldNullPiece);
+    if (g < neg_start) fold_store_strip(img_b, g, kp, strip);
     return;
   }
   const int64_t row0 = (int64_t)blockIdx.x * kTileRows;
   if (tid < 32) sig[tid] = (tid < d) ? (sigma != nullptr ? sigma[sigma_len == 1 ? 0 : tid] : sigma_scalar) : 1.0f;
-  if (cs == 1) {
+  if (cs == 1 && rs == d) {
+    // dense row-major rows: the tile is one contiguous run
+    const int64_t base = row0 * d;
+    const int64_t limit = s * d;
+    for (int idx = tid; idx < kTileRows * d; idx += 128) {
+      const int r = idx / d, k = idx - r * d;
+      xin[r * 33 + k] = (base + idx < limit) ? X[base + idx] : 0.0f;
+    }
+  } else if (cs == 1) {
     for (int idx = tid; idx < kTileRows * d; idx += 128) {
       const int r = idx / d, k = idx - r * d;
       const int64_t gi = row0 + r;
@@ -166,20 +164,30 @@ __global__ void __launch_bounds__(128) fold_build_kernel(const float* __restrict
   __syncthreads();
   const int r = tid;
   const bool live = (row0 + r) < s;
+  const float v = live ? vec[row0 + r] : 0.0f;
+  const float a = fabsf(v);
+  // the row's data: scaled features split into fp16 hi + lo, squared norm of what the two parts represent.  A row
+  // whose vector entry is zero stays a null row and needs none of it.
+  bool data = live && a > 0.0f && a <= 3.4028234663852886e38f;
   double nrm = 0.0;
   bool out_of_range = false;
-  for (int k = 0; k < d; ++k) {
-    const float xs = xin[r * 33 + k] / sig[k];  // x / sigma, rounded as in the reference
-    float xt = xs * scale;
-    if (!(fabsf(xt) <= 400.0f)) {
-      out_of_range = true;
-      xt = 0.0f;
+  if (data || live) {
+    for (int k = 0; k < d; ++k) {
+      const float xs = xin[r * 33 + k] / sig[k];  // x / sigma, rounded as in the reference
+      float xt = xs * scale;
+      if (!(fabsf(xt) <= 400.0f)) {
+        out_of_range = true;
+        xt = 0.0f;
+      }
+      const __half hi = __float2half_rn(xt);
+      const float hif = __half2float(hi);
+      const __half lo = __float2half_rn(xt - hif);
+      const double rep = (double)hif + (double)__half2float(lo);
+      nrm += rep * rep;
+      strip[k] = hi;           // B: [ch | cl | ch]
+      strip[d + k] = lo;
+      strip[2 * d + k] = hi;
     }
-    xin[r * 33 + k] = xt;
-    const float hi = __half2float(__float2half_rn(xt));
-    const float lo = __half2float(__float2half_rn(xt - hi));
-    const double rep = (double)hi + (double)lo;
-    nrm += rep * rep;
   }
   double half_norm = 0.5 * nrm;
   if (half_norm > (double)kNormLimit) {
@@ -187,7 +195,6 @@ __global__ void __launch_bounds__(128) fold_build_kernel(const float* __restrict
     half_norm = 0.0;
   }
   if (out_of_range && live) atomicOr(status + kStatusRange, 1);
-  const float v = live ? vec[row0 + r] : 0.0f;
   const bool nonneg = !(v < 0.0f);
   // position among the block's rows of the same sign
   const unsigned ballot = __ballot_sync(0xFFFFFFFFu, live && nonneg);
@@ -200,26 +207,29 @@ __global__ void __launch_bounds__(128) fold_build_kernel(const float* __restrict
   const int64_t blk_before = blk_pos[blockIdx.x];  // non-negative rows in earlier blocks (all of which are live)
   const int64_t dst = nonneg ? blk_before + pos_before : neg_start + (row0 - blk_before) + (r - pos_before);
   // the exponent piece: |b|^2 / 2 - (log2 |v| - e), split into fp16 pieces (last one rounded up)
-  const float a = fabsf(v);
-  bool data = !out_of_range && a > 0.0f && a <= 3.4028234663852886e38f;
+  float lg = 0.0f;
   if (data) {
-    const double lg = log2((double)a) - (double)fold[kFoldExp];
-    if (lg < kFoldFlushBelow) {
-      data = false;
-    } else {
-      double rem = half_norm - lg;
-      for (int i = 0; i < 3; ++i) {
-        float pc = 0.0f;
-        if (i < npieces) {
-          const float remf = __double2float_ru(rem);
-          pc = __half2float(i == npieces - 1 ? __float2half_ru(remf) : __float2half_rn(remf));
-        }
-        piece[i] = pc;
-        rem -= (double)pc;
-      }
-    }
+    // log2 |v| - e in fp32: |v| = 2^ex * mant with mant in [1, 2); log2f of the mantissa is accurate to an ulp of a
+    // number below 1, the exponents subtract exactly
+    int ex;
+    const float mant = frexpf(a, &ex);  // a = mant * 2^ex, mant in [0.5, 1)
+    lg = (float)(ex - fold[kFoldExp]) + log2f(mant);
+    if ((double)lg < kFoldFlushBelow || out_of_range) data = false;
   }
-  fold_store_row(img_b, dst, kp, d, npieces, xin + r * 33, data, piece);
+  if (data) {
+    double rem = half_norm - (double)lg;
+    for (int i = 0; i < npieces; ++i) {
+      const float remf = __double2float_ru(rem);
+      const float pc = __half2float(i == npieces - 1 ? __float2half_ru(remf) : __float2half_rn(remf));
+      strip[3 * d + npieces + i] = __float2half_rn(-pc);
+      strip[3 * d + i] = one;
+      rem -= (double)pc;
+    }
+  } else {
+    for (int k = 0; k < 3 * d; ++k) strip[k] = zero;
+    strip[3 * d + npieces] = __float2half_rn(-kFoldNullPiece);
+  }
+  fold_store_strip(img_b, dst, kp, strip);
 }
 
 // Builds the folded image of X (s live rows) for the vector `vec` (dense, s entries) into img_b

@@ -38,7 +38,9 @@ def test_products_stay_within_max_gpu_mem(dtype):
     C = X[:m].contiguous()
     v = torch.randn(m, 1, generator=g, device="cuda", dtype=dtype)
     w = torch.randn(n, 1, generator=g, device="cuda", dtype=dtype)
-    y = torch.randn(n, 1, generator=g, device="cuda", dtype=dtype)
+    # positive entries: a sum of 1e6 terms of random sign has a condition number of ~1e3, which would turn the
+    # fp32 rounding of two different summation orders (chunked or not) into a 1e-4 difference
+    y = torch.rand(n, 1, generator=g, device="cuda", dtype=dtype) + 0.1
     k = GaussianKernel(5.0)
     limit = (192 if dtype == torch.float32 else 32) * MIB
     tight = FalkonOptions(max_gpu_mem=limit)
