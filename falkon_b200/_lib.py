@@ -21,6 +21,7 @@ LIB_PATH = os.environ.get("FALKON_B200_LIB") or os.path.join(_HERE, "libfalkon_b
 FLK_F32, FLK_F64 = 0, 1
 FLK_GAUSSIAN, FLK_LAPLACIAN, FLK_MATERN15, FLK_MATERN25 = 0, 1, 2, 3
 FLAG_FORCE_SIMT, FLAG_FORCE_TC, FLAG_FP64_MATH, FLAG_NO_FOLD, FLAG_ACCUMULATE = 1, 2, 4, 8, 16
+FLAG_KEEP_X1, FLAG_KEEP_X2 = 32, 64
 STATIC_SCRATCH_BYTES = 64 << 20
 
 FLK_ERR_BAD_ARG, FLK_ERR_LAYOUT, FLK_ERR_WORKSPACE = -1, -2, -3
@@ -234,11 +235,52 @@ def raise_for_status(status: int):
 # ---------------------------------------------------------------------------------------------
 _workspaces = {}
 
+# Resident operands.  What a product prepares from X1 and X2 (operand images, scaled rows and norms, the range
+# check) stays in the device's workspace after the call.  The next product on that workspace may keep it
+# (FLK_FLAG_KEEP_X1 / _X2) when it is the same entry point with the same sizes, sigma, kernel and flags AND the
+# operand is the same tensor, unchanged: same storage address, shape, strides, dtype and torch version counter
+# (every in-place torch operation bumps the counter).  That is the pattern of a conjugate-gradient solve: the same
+# X and centres in every iteration.  Tensors without a version counter (created under torch.inference_mode) are
+# never kept.  The record is dropped whenever anything else touches the workspace.
+_resident = {}
+
+
+def _tensor_key(t: Optional[torch.Tensor]):
+    if t is None:
+        return None
+    try:
+        version = t._version
+    except RuntimeError:  # inference tensors do not track versions: an in-place edit could not be noticed
+        return None
+    return (t.data_ptr(), tuple(t.shape), tuple(t.stride()), t.dtype, version)
+
+
+def _keep_flags(dev_key, signature, key1, key2) -> int:
+    rec = _resident.get(dev_key)
+    if rec is None or rec[0] != signature:
+        return 0
+    keep = 0
+    if key1 is not None and rec[1] == key1:
+        keep |= FLAG_KEEP_X1
+    if key2 is not None and rec[2] == key2:
+        keep |= FLAG_KEEP_X2
+    return keep
+
+
+def forget_resident(device: Optional[torch.device] = None):
+    """Drops the record of what the workspace(s) hold (a caller who edits operand memory behind torch's back --
+    through a raw pointer or another library -- calls this before the next product)."""
+    if device is None:
+        _resident.clear()
+    else:
+        _resident.pop((device.type, device.index), None)
+
 
 def workspace(device: torch.device, nbytes: int) -> torch.Tensor:
     key = (device.type, device.index)
     buf = _workspaces.get(key)
     if buf is None or buf.numel() < nbytes:
+        _resident.pop(key, None)
         if buf is not None:
             del _workspaces[key]
             del buf
@@ -249,6 +291,7 @@ def workspace(device: torch.device, nbytes: int) -> torch.Tensor:
 
 def release_workspaces():
     _workspaces.clear()
+    _resident.clear()
 
 
 def dtype_code(dtype: torch.dtype) -> int:
@@ -325,6 +368,24 @@ def rows_within_budget(query, n: int, budget: Optional[float]) -> int:
     return lo
 
 
+def _resolve_budget(budget, need: int, device) -> Optional[float]:
+    """None when the whole problem may run in one call, else the byte budget to chunk under.  ``budget`` is a number,
+    None, or a callable ``budget(device) -> bytes or None`` that is only evaluated when the answer is not already
+    clear: a problem whose workspace fits the buffer this package already holds on the device needs no query of
+    the device's free memory (a driver call on every product would show up in short products)."""
+    if budget is None:
+        return None
+    if callable(budget):
+        limit = getattr(budget, "limit", float("inf"))
+        held = _workspaces.get((device.type, device.index)) if device is not None else None
+        if held is not None and need <= held.numel() and need <= limit:
+            return None
+        budget = budget(device)
+        if budget is None:
+            return None
+    return None if need <= budget else float(budget)
+
+
 def call_fmmv_budgeted(kernel_id, sigma, X1, X2, v, out, flags=0, host=False, device=None, budget=None):
     """``call_fmmv`` under a device-memory budget (bytes): when the workspace of the whole problem exceeds it, the
     larger operand is cut into row chunks -- rows of X1 produce independent rows of ``out``; rows of X2 (with the
@@ -335,7 +396,8 @@ def call_fmmv_budgeted(kernel_id, sigma, X1, X2, v, out, flags=0, host=False, de
     m = X2.shape[0]
     t = v.shape[1] if v.dim() == 2 else 1
     wsq = lib.flk_fmmv_host_workspace_bytes if host else lib.flk_fmmv_workspace_bytes
-    if budget is None or wsq(dt, kernel_id, n, m, d, t, flags) <= budget:
+    budget = _resolve_budget(budget, wsq(dt, kernel_id, n, m, d, t, flags), device if host else X1.device)
+    if budget is None:
         return call_fmmv(kernel_id, sigma, X1, X2, v, out, flags=flags, host=host, device=device)
     if n >= m:
         step = rows_within_budget(lambda r: wsq(dt, kernel_id, r, m, d, t, flags), n, budget)
@@ -366,7 +428,8 @@ def call_fdmmv_budgeted(kernel_id, sigma, X1, X2, v, w, out, flags=0, host=False
     lead = v if v is not None else w
     t = lead.shape[1] if lead is not None and lead.dim() == 2 else 1
     wsq = lib.flk_fdmmv_host_workspace_bytes if host else lib.flk_fdmmv_workspace_bytes
-    if budget is None or wsq(dt, kernel_id, n, m, d, t, flags) <= budget:
+    budget = _resolve_budget(budget, wsq(dt, kernel_id, n, m, d, t, flags), device if host else X1.device)
+    if budget is None:
         return call_fdmmv(kernel_id, sigma, X1, X2, v, w, out, flags=flags, host=host, device=device)
     step = rows_within_budget(lambda r: wsq(dt, kernel_id, r, m, d, t, flags), n, budget)
     part = torch.empty_like(out) if host else None
@@ -397,14 +460,24 @@ def call_fmmv(kernel_id, sigma, X1, X2, v, out, flags=0, host=False, device=None
     if need < 0:
         raise_for_status(int(need))
     keep, sig_ptr, sig_len = _sigma_args(sigma)
+    dev_key = (dev.type, dev.index)
     with torch.cuda.device(dev):
         ws = workspace(dev, need)
         stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
         fn = lib.flk_fmmv_host if host else lib.flk_fmmv
+        signature = key1 = key2 = None
+        kept = 0
+        if not host:
+            signature = ("fmmv", dt, kernel_id, keep.tobytes(), n, m, d, t, flags, ws.data_ptr(), stream.value)
+            key1, key2 = _tensor_key(X1), _tensor_key(X2)
+            kept = _keep_flags(dev_key, signature, key1, key2)
+        _resident.pop(dev_key, None)
         status = fn(dt, kernel_id, *_mat_args(X1), *_mat_args(X2), d,
                     ctypes.c_void_p(v.data_ptr()), t, v.stride(0), v.stride(1),
                     *_mat_args(out, with_rows=False), sig_ptr, sig_len,
-                    ctypes.c_void_p(ws.data_ptr()), ws.numel(), flags, stream)
+                    ctypes.c_void_p(ws.data_ptr()), ws.numel(), flags | kept, stream)
+        if status == 0 and signature is not None:
+            _resident[dev_key] = (signature, key1, key2)
     del keep
     raise_for_status(status)
     return out
@@ -427,14 +500,25 @@ def call_fdmmv(kernel_id, sigma, X1, X2, v, w, out, flags=0, host=False, device=
     if need < 0:
         raise_for_status(int(need))
     keep, sig_ptr, sig_len = _sigma_args(sigma)
+    dev_key = (dev.type, dev.index)
     with torch.cuda.device(dev):
         ws = workspace(dev, need)
         stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
         fn = lib.flk_fdmmv_host if host else lib.flk_fdmmv
+        signature = key1 = key2 = None
+        kept = 0
+        if not host:
+            signature = ("fdmmv", dt, kernel_id, keep.tobytes(), n, m, d, t, v is None, flags, ws.data_ptr(),
+                         stream.value)
+            key1, key2 = _tensor_key(X1), _tensor_key(X2)
+            kept = _keep_flags(dev_key, signature, key1, key2)
+        _resident.pop(dev_key, None)
         status = fn(dt, kernel_id, *_mat_args(X1), *_mat_args(X2), d,
                     *_mat_args(v, with_rows=False), *_mat_args(w, with_rows=False), t,
                     *_mat_args(out, with_rows=False), sig_ptr, sig_len,
-                    ctypes.c_void_p(ws.data_ptr()), ws.numel(), flags, stream)
+                    ctypes.c_void_p(ws.data_ptr()), ws.numel(), flags | kept, stream)
+        if status == 0 and signature is not None:
+            _resident[dev_key] = (signature, key1, key2)
     del keep
     raise_for_status(status)
     return out
@@ -454,6 +538,7 @@ def call_fmm(kernel_id, sigma, X1, X2, out, flags=0):
     keep, sig_ptr, sig_len = _sigma_args(sigma)
     with torch.cuda.device(dev):
         ws = workspace(dev, need)
+        forget_resident(dev)
         stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
         status = lib.flk_fmm(dt, kernel_id, *_mat_args(X1), *_mat_args(X2), d, *_mat_args(out, with_rows=False),
                              sig_ptr, sig_len, ctypes.c_void_p(ws.data_ptr()), ws.numel(), flags, stream)
@@ -480,6 +565,7 @@ def call_kgrad(kernel_id, sigma, X1, X2, G, v, out, flags=0):
     keep, sig_ptr, sig_len = _sigma_args(sigma)
     with torch.cuda.device(dev):
         ws = workspace(dev, need)
+        forget_resident(dev)
         stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
         if v is None:
             v_args = (None, 0, 0, 0)

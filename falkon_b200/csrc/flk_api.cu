@@ -63,6 +63,15 @@ __global__ void __launch_bounds__(512) mufu_probe_kernel(int iters, float* sink)
   if (s == 123.456f) *sink = s;  // keeps the loop alive; never true in practice
 }
 
+// Clears the 64-word status block at the start of a call, except the range words of operands whose prepared form
+// the caller keeps from the previous call.
+__global__ void reset_status_kernel(int* status, int keep_x1, int keep_x2) {
+  const int i = threadIdx.x;
+  if (i >= 64) return;
+  if ((keep_x1 && i == tc::kStatusRangeX1) || (keep_x2 && i == tc::kStatusRangeX2)) return;
+  status[i] = 0;
+}
+
 struct Mat {
   const void* ptr;
   int64_t rows, cols, rs, cs;
@@ -384,7 +393,7 @@ static int upload_sigma(const double* sigma, int64_t sigma_len, void* dst, T* sc
 template <typename T, typename TIn = T>
 static int run_prep_rows(const Mat& X, const T* sigma_dev, T sigma_scalar, int sigma_len, void* xs, int ld,
                          int64_t rows_pad, void* norms, Gate gate, cudaStream_t stream) {
-  int blocks = (int)ceil_div(rows_pad, kPrepRows);
+  int blocks = (int)ceil_div(rows_pad, (int64_t)kPrepRows * kPrepSubBlocks);
   prep_rows_kernel<T, TIn><<<blocks, 256, 0, stream>>>(reinterpret_cast<const TIn*>(X.ptr), X.rows, (int)X.cols, X.rs,
                                                   X.cs, sigma_dev, sigma_scalar, sigma_len,
                                                   reinterpret_cast<T*>(xs), ld, rows_pad,
@@ -501,32 +510,45 @@ static inline Gate gate_tc(const Layout& L) { return Gate{L.range_flag(), 0}; }
 static inline Gate gate_simt(const Layout& L) { return L.tc ? Gate{L.range_flag(), 1} : Gate{nullptr, 0}; }
 
 // Builds the operand forms both paths need: tensor-core tile images (which also raise the range
-// flag) and, gated, the scaled rows + norms of the SIMT kernels.
+// flags) and, gated, the scaled rows + norms of the SIMT kernels.  Operands the caller keeps from the previous
+// call on this workspace (FLK_FLAG_KEEP_X1 / _X2) are skipped: their images, SIMT forms and range words are
+// still in place.
 template <typename T>
 static int prepare_operands(const Layout& L, int kernel, const Mat& X1, const Mat& X2, int64_t d, const T* sig_dev,
-                            T sig_scalar, int sigma_len, int dtype, bool reset_status, cudaStream_t stream) {
+                            T sig_scalar, int sigma_len, int dtype, bool reset_status, int flags, cudaStream_t stream) {
+  const bool keep1 = (flags & FLK_FLAG_KEEP_X1) != 0, keep2 = (flags & FLK_FLAG_KEEP_X2) != 0;
+  int* status = reinterpret_cast<int*>(L.status);
   if (L.tc) {
-    if (reset_status) FLK_CUDA_TRY(cudaMemsetAsync(L.status, 0, 256, stream));
-    else if (L.fold)  // the fold blocks start from zero in every call (the two leading status words are kept)
+    if (reset_status) {
+      reset_status_kernel<<<1, 64, 0, stream>>>(status, keep1 ? 1 : 0, keep2 ? 1 : 0);
+      FLK_CUDA_TRY(cudaGetLastError());
+    } else if (L.fold) {  // the fold blocks start from zero in every call (the leading status words are kept)
       FLK_CUDA_TRY(cudaMemsetAsync(L.fold_block(0), 0, 2 * tc::kFoldWords * sizeof(int), stream));
+    }
     auto prep = L.s1.kloop ? tck::prep_images_large : tc::prep_images;
-    // folded sweeps build their reduction-side images per sweep, with the vector (fold_operand)
+    // folded sweeps build their reduction-side images per sweep, with the vector (build_folded_image)
     void* x1_b = L.fold ? nullptr : L.x1.img_b;
     void* x2_b = L.fold ? nullptr : L.x2.img_b;
-    if (L.x1.img_a != nullptr || x1_b != nullptr) {
+    if (!keep1 && (L.x1.img_a != nullptr || x1_b != nullptr)) {
       FLK_TRY(prep(kernel, X1.ptr, X1.rows, X1.rs, X1.cs, (int)d, (const float*)sig_dev, (float)sig_scalar, sigma_len,
-                   L.s1.r_pad, L.x1.img_a, x1_b, reinterpret_cast<int*>(L.status), stream));
+                   L.s1.r_pad, L.x1.img_a, x1_b, status + tc::kStatusRangeX1, stream));
       count_launch();
     }
-    if (L.x2.img_a != nullptr || x2_b != nullptr) {
+    if (!keep2 && (L.x2.img_a != nullptr || x2_b != nullptr)) {
       FLK_TRY(prep(kernel, X2.ptr, X2.rows, X2.rs, X2.cs, (int)d, (const float*)sig_dev, (float)sig_scalar, sigma_len,
-                   L.s1.s_pad, L.x2.img_a, x2_b, reinterpret_cast<int*>(L.status), stream));
+                   L.s1.s_pad, L.x2.img_a, x2_b, status + tc::kStatusRangeX2, stream));
       count_launch();
     }
   }
   const int ld = ld_for(dtype, d);
-  FLK_TRY(run_prep_rows<T>(X1, sig_dev, sig_scalar, sigma_len, L.x1.xs, ld, L.s1.r_pad, L.x1.norms, gate_simt(L), stream));
-  FLK_TRY(run_prep_rows<T>(X2, sig_dev, sig_scalar, sigma_len, L.x2.xs, ld, L.s1.s_pad, L.x2.norms, gate_simt(L), stream));
+  // (the SIMT form of a kept operand is as valid as it was: built if its gate was open then, and the gate of a call
+  // that keeps every operand can only differ through the per-call range word, i.e. through the vector -- in which
+  // case it is built now)
+  const bool simt_only = !L.tc;
+  if (!(keep1 && simt_only))
+    FLK_TRY(run_prep_rows<T>(X1, sig_dev, sig_scalar, sigma_len, L.x1.xs, ld, L.s1.r_pad, L.x1.norms, gate_simt(L), stream));
+  if (!(keep2 && simt_only))
+    FLK_TRY(run_prep_rows<T>(X2, sig_dev, sig_scalar, sigma_len, L.x2.xs, ld, L.s1.s_pad, L.x2.norms, gate_simt(L), stream));
   return FLK_OK;
 }
 
@@ -585,7 +607,7 @@ static int fmmv_impl(int dtype, int kernel, const Mat& X1, const Mat& X2, const 
   T sig_scalar;
   const T* sig_dev;
   FLK_TRY(upload_sigma<T>(sigma, sigma_len, L.sigma, &sig_scalar, &sig_dev, stream));
-  FLK_TRY(prepare_operands<T>(L, kernel, X1, X2, d, sig_dev, sig_scalar, (int)sigma_len, dtype, reset_status, stream));
+  FLK_TRY(prepare_operands<T>(L, kernel, X1, X2, d, sig_dev, sig_scalar, (int)sigma_len, dtype, reset_status, flags, stream));
   FLK_TRY(run_prep_vec<T>(v, L.vbuf, L.s1.s_pad, L.s1.tp, L.s1.tt, stream));
   FoldSigma fs;
   if constexpr (sizeof(T) == 4) fs = FoldSigma{sig_dev, sig_scalar, (int)sigma_len};
@@ -615,7 +637,7 @@ static int fdmmv_impl(int dtype, int kernel, const Mat& X1, const Mat& X2, const
   T sig_scalar;
   const T* sig_dev;
   FLK_TRY(upload_sigma<T>(sigma, sigma_len, L.sigma, &sig_scalar, &sig_dev, stream));
-  FLK_TRY(prepare_operands<T>(L, kernel, X1, X2, d, sig_dev, sig_scalar, (int)sigma_len, dtype, reset_status, stream));
+  FLK_TRY(prepare_operands<T>(L, kernel, X1, X2, d, sig_dev, sig_scalar, (int)sigma_len, dtype, reset_status, flags, stream));
   FoldSigma fs;
   if constexpr (sizeof(T) == 4) fs = FoldSigma{sig_dev, sig_scalar, (int)sigma_len};
   if (has_v) {
@@ -841,6 +863,7 @@ static int copy_lane_for_current_device(CopyLane** out) {
 static int run_host(bool dmmv, int dtype, int kernel, const Mat& a, const Mat& b, const Mat& vv, const Mat& ww,
                     const Mat& oo, int64_t t, const double* sigma_host, int64_t sigma_len, void* workspace,
                     int64_t workspace_bytes, int flags, cudaStream_t st) {
+  flags &= ~(FLK_FLAG_KEEP_X1 | FLK_FLAG_KEEP_X2 | FLK_FLAG_ACCUMULATE);  // staged copies are fresh in every call
   const int64_t n = a.rows, m = b.rows, d = a.cols;
   HostLayout H = make_host_layout(workspace, dmmv, dtype, kernel, a, b, vv, ww, oo, t, flags);
   FLK_TRY(check_workspace(workspace, workspace_bytes, H.total));
@@ -1164,7 +1187,7 @@ int flk_range_flag(const void* workspace, void* stream, int* flag_out) {
   int host[4] = {0, 0, 0, 0};
   FLK_CUDA_TRY(cudaMemcpyAsync(host, workspace, sizeof(host), cudaMemcpyDeviceToHost, st));
   FLK_CUDA_TRY(cudaStreamSynchronize(st));
-  *flag_out = host[tc::kStatusRange] != 0 ? 1 : 0;
+  *flag_out = (host[tc::kStatusRange] | host[tc::kStatusRangeX1] | host[tc::kStatusRangeX2]) != 0 ? 1 : 0;
   return FLK_OK;
 }
 

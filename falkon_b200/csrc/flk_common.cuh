@@ -49,16 +49,22 @@ inline int64_t ceil_div(int64_t x, int64_t m) { return (x + m - 1) / m; }
 constexpr int64_t kRowPad = 512;
 
 // Device-side gate.  When the tensor-core path is chosen its SIMT alternative is launched behind
-// it; which of the two does the work is decided by a flag the image builder writes in device
-// memory, so the choice costs no host round trip.  A gated kernel returns at once unless
-// (*flag != 0) == want.  flag == nullptr means "always run".
+// it; which of the two does the work is decided by flags the image builders write in device
+// memory, so the choice costs no host round trip.  There are kRangeWords consecutive flag words
+// (one for what changes with every call, one per operand whose images may be kept across calls);
+// a gated kernel returns at once unless (any word != 0) == want.  flag == nullptr means "always run".
+constexpr int kRangeWords = 3;
 struct Gate {
   const int* flag;
   int want;
 };
+__device__ __forceinline__ bool range_raised(const int* words) {
+  const volatile int* w = reinterpret_cast<const volatile int*>(words);
+  return (w[0] | w[1] | w[2]) != 0;
+}
 __device__ __forceinline__ bool gate_open(const Gate& g) {
   if (g.flag == nullptr) return true;
-  return (*reinterpret_cast<const volatile int*>(g.flag) != 0) == (g.want != 0);
+  return range_raised(g.flag) == (g.want != 0);
 }
 
 // ---------------------------------------------------------------------------------------------

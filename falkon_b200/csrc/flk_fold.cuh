@@ -31,20 +31,29 @@ inline int fold_tiles(int64_t s) { return (int)ceil_div(std::max<int64_t>(s, 1),
 inline int64_t fold_image_rows(int64_t s) { return round_up((int64_t)fold_tiles(s) * kTileRows, kRowPad); }
 inline int fold_blocks(int64_t s) { return (int)ceil_div(std::max<int64_t>(s, 1), (int64_t)kTileRows); }
 
-__global__ void __launch_bounds__(128) fold_count_kernel(const float* __restrict__ vec, int64_t s,
+constexpr int kFoldCountSub = 8;  // 128-row blocks counted per CTA (fewer, fatter CTAs: the kernel is all overhead)
+
+__global__ void __launch_bounds__(128) fold_count_kernel(const float* __restrict__ vec, int64_t s, int nblk,
                                                          int* __restrict__ blk_pos, int* __restrict__ fold,
                                                          int* __restrict__ status) {
-  const int64_t row = (int64_t)blockIdx.x * kTileRows + threadIdx.x;
-  const bool live = row < s;
-  const float v = live ? vec[row] : 0.0f;
-  const float a = fabsf(v);
-  const bool finite = a <= 3.4028234663852886e38f;  // false for inf and NaN
-  if (live && !finite) atomicOr(status + kStatusRange, 1);  // the SIMT kernels reproduce inf / NaN propagation
-  const int cnt = __syncthreads_count(live && !(v < 0.0f));
-  if (threadIdx.x == 0) blk_pos[blockIdx.x] = cnt;
-  unsigned bits = (live && finite) ? __float_as_uint(a) : 0u;
-  bits = __reduce_max_sync(0xFFFFFFFFu, bits);
-  if ((threadIdx.x & 31) == 0 && bits != 0u) atomicMax(reinterpret_cast<unsigned*>(fold + kFoldMaxBits), bits);
+  unsigned max_bits = 0u;
+  bool bad = false;
+  for (int sub = 0; sub < kFoldCountSub; ++sub) {
+    const int b = blockIdx.x * kFoldCountSub + sub;
+    if (b >= nblk) break;  // uniform across the block
+    const int64_t row = (int64_t)b * kTileRows + threadIdx.x;
+    const bool live = row < s;
+    const float v = live ? vec[row] : 0.0f;
+    const float a = fabsf(v);
+    const bool finite = a <= 3.4028234663852886e38f;  // false for inf and NaN
+    bad = bad || (live && !finite);
+    const int cnt = __syncthreads_count(live && !(v < 0.0f));
+    if (threadIdx.x == 0) blk_pos[b] = cnt;
+    if (live && finite) max_bits = max(max_bits, __float_as_uint(a));
+  }
+  if (bad) atomicOr(status + kStatusRange, 1);  // the SIMT kernels reproduce inf / NaN propagation
+  max_bits = __reduce_max_sync(0xFFFFFFFFu, max_bits);
+  if ((threadIdx.x & 31) == 0 && max_bits != 0u) atomicMax(reinterpret_cast<unsigned*>(fold + kFoldMaxBits), max_bits);
 }
 
 // One CTA: blk_pos[nblk] -> exclusive prefix sums in place; fold block filled in.
@@ -241,7 +250,7 @@ inline int build_folded_image(int kernel, const void* X, int64_t s, int64_t rs, 
   const int nblk = fold_blocks(s), tiles = fold_tiles(s);
   const int kp = (int)padded_k(d);
   const float scale = (float)sqrt(scale_sq_for(kernel));
-  fold_count_kernel<<<nblk, 128, 0, stream>>>(vec, s, blk_pos, fold, status);
+  fold_count_kernel<<<(nblk + kFoldCountSub - 1) / kFoldCountSub, 128, 0, stream>>>(vec, s, nblk, blk_pos, fold, status);
   FLK_CUDA_TRY(cudaGetLastError());
   fold_scan_kernel<<<1, 1024, 0, stream>>>(blk_pos, nblk, s, tiles, fold);
   FLK_CUDA_TRY(cudaGetLastError());

@@ -16,6 +16,8 @@ namespace flk {
 // ---------------------------------------------------------------------------------------------
 constexpr int kPrepRows = 64;
 constexpr int kPrepCols = 64;
+constexpr int kPrepSubBlocks = 8;  // 64-row groups per CTA of prep_rows_kernel: a gated-off launch over 1e7 rows is
+                                   // then 2e4 empty CTAs instead of 1.6e5 (0.3 ms of pure block scheduling)
 
 template <typename T, typename TIn = T>
 __global__ void __launch_bounds__(256) prep_rows_kernel(const TIn* __restrict__ X, int64_t n, int d,
@@ -28,7 +30,9 @@ __global__ void __launch_bounds__(256) prep_rows_kernel(const TIn* __restrict__ 
   __shared__ T tile[kPrepRows][kPrepCols + 1];
   __shared__ T sig[kPrepCols];
   const int tid = threadIdx.x;
-  const int64_t row0 = (int64_t)blockIdx.x * kPrepRows;
+  for (int sub = 0; sub < kPrepSubBlocks; ++sub) {
+  const int64_t row0 = ((int64_t)blockIdx.x * kPrepSubBlocks + sub) * kPrepRows;
+  if (row0 >= n_pad) break;  // uniform across the block
   T nrm = 0;
   for (int k0 = 0; k0 < ld; k0 += kPrepCols) {
     const int kw = min(kPrepCols, ld - k0);
@@ -79,6 +83,8 @@ __global__ void __launch_bounds__(256) prep_rows_kernel(const TIn* __restrict__ 
   if (tid < kPrepRows) {
     int64_t gi = row0 + tid;
     if (gi < n_pad && norms != nullptr) norms[gi] = nrm;
+  }
+  __syncthreads();
   }
 }
 

@@ -91,7 +91,10 @@ constexpr float kNormLimit = 60000.0f;              // largest half squared norm
 constexpr int kPolyPairs = FLK_TC_POLY_PAIRS;
 
 // words of the 256-byte status block at the front of the workspace
-enum { kStatusTimeout = 0, kStatusRange = 1 };
+// kStatusRange: raised by what is built per call (folded images: a vector entry that is not finite, a row out of
+// range); kStatusRangeX1 / X2: raised by the image builder of that operand (kept when the caller keeps the images)
+enum { kStatusTimeout = 0, kStatusRange = 1, kStatusRangeX1 = 2, kStatusRangeX2 = 3 };
+static_assert(kStatusRangeX2 - kStatusRange + 1 == kRangeWords, "the gate reads these words as one group");
 
 inline bool supports_d(int64_t d) { return d >= 1 && d <= kMaxD; }
 // number of fp16 pieces half the squared norm is split into (3 when it costs no extra MMA K-step)
@@ -408,7 +411,7 @@ __global__ void __launch_bounds__(128) prep_images_kernel(const float* __restric
                                                           int64_t cs, int d, const float* __restrict__ sigma,
                                                           float sigma_scalar, int sigma_len, float scale,
                                                           int kp, int npieces, __half* __restrict__ img_a,
-                                                          __half* __restrict__ img_b, int* __restrict__ status) {
+                                                          __half* __restrict__ img_b, int* __restrict__ range_word) {
   extern __shared__ __align__(16) unsigned char prep_smem_raw[];
   float* xin = reinterpret_cast<float*>(prep_smem_raw);            // [128][33] scaled inputs
   __half* img = reinterpret_cast<__half*>(xin + kTileRows * 33);   // [128 * kp]
@@ -454,7 +457,7 @@ __global__ void __launch_bounds__(128) prep_images_kernel(const float* __restric
     out_of_range = true;
     half_norm = 0.0;
   }
-  if (out_of_range && live) atomicOr(status + kStatusRange, 1);
+  if (out_of_range && live) atomicOr(range_word, 1);
   float piece[3];
   {
     // the last piece is rounded up: the represented norm is never below the true one, so the
@@ -505,7 +508,7 @@ __global__ void __launch_bounds__(128) prep_images_kernel(const float* __restric
 }
 
 inline int prep_images(int kernel, const void* X, int64_t n, int64_t rs, int64_t cs, int d, const float* sigma_dev,
-                       float sigma_scalar, int sigma_len, int64_t rows_pad, void* img_a, void* img_b, int* status,
+                       float sigma_scalar, int sigma_len, int64_t rows_pad, void* img_a, void* img_b, int* range_word,
                        cudaStream_t stream) {
   const int kp = (int)padded_k(d);
   const size_t smem = sizeof(float) * (size_t)(kTileRows * 33) + sizeof(__half) * (size_t)(kTileRows * kp);
@@ -514,7 +517,7 @@ inline int prep_images(int kernel, const void* X, int64_t n, int64_t rs, int64_t
   prep_images_kernel<<<blocks, 128, smem, stream>>>(reinterpret_cast<const float*>(X), n, rs, cs, d, sigma_dev,
                                                     sigma_scalar, sigma_len, scale, kp, norm_pieces(d),
                                                     reinterpret_cast<__half*>(img_a),
-                                                    reinterpret_cast<__half*>(img_b), status);
+                                                    reinterpret_cast<__half*>(img_b), range_word);
   FLK_CUDA_TRY(cudaGetLastError());
   return FLK_OK;
 }
@@ -757,7 +760,7 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
   __shared__ int skip_launch;
   if (tid == 0) {
     const volatile int* st = reinterpret_cast<const volatile int*>(p.status);
-    skip_launch = (st[kStatusTimeout] != 0 || st[kStatusRange] != 0) ? 1 : 0;
+    skip_launch = (st[kStatusTimeout] != 0 || range_raised(p.status + kStatusRange)) ? 1 : 0;
   }
   __syncthreads();
   if (skip_launch) return;

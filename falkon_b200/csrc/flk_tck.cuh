@@ -61,7 +61,7 @@ __global__ void __launch_bounds__(128) prep_images_large_kernel(const float* __r
                                                                 int64_t cs, int d, const float* __restrict__ sigma,
                                                                 float sigma_scalar, int sigma_len, float scale,
                                                                 int nslab, __half* __restrict__ img_a,
-                                                                __half* __restrict__ img_b, int* __restrict__ status) {
+                                                                __half* __restrict__ img_b, int* __restrict__ range_word) {
   __shared__ __align__(16) __half slab[2][kTileRows * kSlabK];  // A and B version of the current slab
   const int r = threadIdx.x;
   const int64_t row = (int64_t)blockIdx.x * kTileRows + r;
@@ -92,7 +92,7 @@ __global__ void __launch_bounds__(128) prep_images_large_kernel(const float* __r
     out_of_range = true;
     half_norm = 0.0;
   }
-  if (out_of_range && live) atomicOr(status + kStatusRange, 1);
+  if (out_of_range && live) atomicOr(range_word, 1);
   float piece[3];
   {
     double rem = half_norm;
@@ -145,13 +145,13 @@ __global__ void __launch_bounds__(128) prep_images_large_kernel(const float* __r
 
 inline int prep_images_large(int kernel, const void* X, int64_t n, int64_t rs, int64_t cs, int d,
                              const float* sigma_dev, float sigma_scalar, int sigma_len, int64_t rows_pad, void* img_a,
-                             void* img_b, int* status, cudaStream_t stream) {
+                             void* img_b, int* range_word, cudaStream_t stream) {
   const float scale = (float)sqrt(scale_sq_for(kernel));
   const int blocks = (int)(rows_pad / kTileRows);
   prep_images_large_kernel<<<blocks, 128, 0, stream>>>(reinterpret_cast<const float*>(X), n, rs, cs, d, sigma_dev,
                                                        sigma_scalar, sigma_len, scale, n_slabs(d),
                                                        reinterpret_cast<__half*>(img_a),
-                                                       reinterpret_cast<__half*>(img_b), status);
+                                                       reinterpret_cast<__half*>(img_b), range_word);
   FLK_CUDA_TRY(cudaGetLastError());
   return FLK_OK;
 }
@@ -251,7 +251,7 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
   __shared__ int skip_launch;
   if (tid == 0) {
     const volatile int* st = reinterpret_cast<const volatile int*>(p.status);
-    skip_launch = (st[kStatusTimeout] != 0 || st[kStatusRange] != 0) ? 1 : 0;
+    skip_launch = (st[kStatusTimeout] != 0 || range_raised(p.status + kStatusRange)) ? 1 : 0;
   }
   __syncthreads();
   if (skip_launch) return;

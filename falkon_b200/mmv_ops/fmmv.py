@@ -68,6 +68,18 @@ def device_budget(opt, dev: torch.device) -> Optional[float]:
     return None if budget == float("inf") else budget * slack
 
 
+def lazy_budget(opt):
+    """``device_budget`` as a callable for the ctypes layer, which asks only when it has to; ``limit`` is the part of
+    the budget that is known without asking the device."""
+    def ask(dev):
+        return device_budget(opt, dev)
+
+    limit = float(getattr(opt, "max_gpu_mem", float("inf")) or float("inf")) if opt is not None else float("inf")
+    slack = float(getattr(opt, "memory_slack", 0.9) or 0.9) if opt is not None else 0.9
+    ask.limit = limit * slack
+    return ask
+
+
 def _pick_device(devs):
     cuda = [d for d in devs if d.type == "cuda"]
     if cuda:
@@ -97,11 +109,11 @@ def _fmmv_forward(X1, X2, v, kernel, out, opt):
                 multi_device.fmmv_host_multi(kernel_id, sigma, X1, X2, v, out, _flags(opt), devices)
             else:
                 _lib.call_fmmv_budgeted(kernel_id, sigma, X1, X2, v, out, flags=_flags(opt), host=True,
-                                        device=devices[0], budget=device_budget(opt, devices[0]))
+                                        device=devices[0], budget=lazy_budget(opt))
         else:
             o_dev = out if out.device == dev else torch.empty(out.shape, dtype=out.dtype, device=dev)
             _lib.call_fmmv_budgeted(kernel_id, sigma, _to_dev(X1, dev), _to_dev(X2, dev), _to_dev(v, dev), o_dev,
-                                    flags=_flags(opt), budget=device_budget(opt, dev))
+                                    flags=_flags(opt), budget=lazy_budget(opt))
             if o_dev is not out:
                 out.copy_(o_dev)
     return out
@@ -240,11 +252,11 @@ def fdmmv(
                 multi_device.fdmmv_host_multi(kernel_id, sigma, X1, X2, v, w, out, _flags(opt), devices)
             else:
                 _lib.call_fdmmv_budgeted(kernel_id, sigma, X1, X2, v, w, out, flags=_flags(opt), host=True,
-                                         device=devices[0], budget=device_budget(opt, devices[0]))
+                                         device=devices[0], budget=lazy_budget(opt))
         else:
             o_dev = out if out.device == dev else torch.empty(out.shape, dtype=out.dtype, device=dev)
             _lib.call_fdmmv_budgeted(kernel_id, sigma, _to_dev(X1, dev), _to_dev(X2, dev), _to_dev(v, dev),
-                                     _to_dev(w, dev), o_dev, flags=_flags(opt), budget=device_budget(opt, dev))
+                                     _to_dev(w, dev), o_dev, flags=_flags(opt), budget=lazy_budget(opt))
             if o_dev is not out:
                 out.copy_(o_dev)
     return out

@@ -171,8 +171,10 @@ class Falkon:
         self._reset_state()
         t_s = time.time()
         dev = self._device(X, Y)
+        # moved outside inference mode: ordinary tensors carry a version counter, which lets the products keep what
+        # they prepared from X across the iterations of the solve (falkon_b200/_lib.py, resident operands)
+        Xd, Yd = X.to(dev), Y.to(dev)
         with torch.inference_mode():
-            Xd, Yd = X.to(dev), Y.to(dev)
             Xts_d = None if Xts is None else Xts.to(dev)
             Yts_d = None if Yts is None else Yts.to(dev)
             if self.weight_fn is None:

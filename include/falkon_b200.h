@@ -57,6 +57,13 @@ typedef enum flk_kernel {
 #define FLK_FLAG_FP64_MATH 4  /* flk_fmm / flk_kgrad: evaluate fp32 data in fp64, round on store */
 #define FLK_FLAG_NO_FOLD 8    /* Gaussian, t = 1, tensor-core path: keep the vector out of the operand images
                                  (the sweep then multiplies by it in its epilogue; diagnostics / comparison) */
+#define FLK_FLAG_KEEP_X1 32    /* flk_fmmv / flk_fdmmv (device pointers): the workspace still holds what the previous call
+                                 on it prepared from X1 -- that call had the same entry point, sizes, strides, sigma,
+                                 kernel and the other flag bits, and X1's contents have not changed since -- so X1 is
+                                 not prepared again (its operand images and range check stay resident).  The caller
+                                 vouches for all of that; nothing can be verified here.  Ignored by the _host entry
+                                 points. */
+#define FLK_FLAG_KEEP_X2 64    /* the same for X2 */
 #define FLK_FLAG_ACCUMULATE 16 /* flk_fmmv / flk_fdmmv: add the result to what `out` holds instead of overwriting it
                                  (chunks of the reduction side are summed this way under a memory budget) */
 
