@@ -40,6 +40,38 @@ def _require_cuda(opt: Optional[BaseOptions], *tensors):
         raise RuntimeError("falkon_b200 needs a CUDA device (B200, sm_100); none is available.")
 
 
+class _DebugTimer:
+    """``opt.debug = True``: per-call timing report of a product, the role of the reference's ``TicToc`` around its
+    kernel calls (falkon/utils/tictoc.py:19-63, used at falkon/optim/conjgrad.py:245).  Device times come from the
+    CUDA events the library records around its sweep launches (``flk_set_timing``) and from an event pair around
+    the whole call; reading them synchronises, which is why this is off unless asked for."""
+
+    def __init__(self, opt, what: str, dev: torch.device, shape_note: str):
+        self.on = bool(getattr(opt, "debug", False)) and dev.type == "cuda"
+        self.what, self.dev, self.note = what, dev, shape_note
+
+    def __enter__(self):
+        if self.on:
+            _lib.set_timing(True)
+            self.e0 = torch.cuda.Event(enable_timing=True)
+            self.e1 = torch.cuda.Event(enable_timing=True)
+            self.e0.record(torch.cuda.current_stream(self.dev))
+        return self
+
+    def __exit__(self, exc_type, exc, tb):
+        if not self.on:
+            return False
+        self.e1.record(torch.cuda.current_stream(self.dev))
+        self.e1.synchronize()
+        s1, s2 = _lib.sweep_ms()
+        _lib.set_timing(False)
+        if exc_type is None:
+            sweeps = ", ".join(f"sweep {i + 1} {ms:.3f} ms" for i, ms in enumerate((s1, s2)) if ms >= 0)
+            print(f"[falkon_b200] {self.what} {self.note}: {self.e0.elapsed_time(self.e1):.3f} ms on {self.dev}"
+                  + (f" ({sweeps})" if sweeps else ""), flush=True)
+        return False
+
+
 def _is_sparse(*xs):
     return any(type(x).__name__ == "SparseTensor" or (isinstance(x, torch.Tensor) and x.is_sparse) for x in xs)
 
@@ -112,8 +144,9 @@ def _fmmv_forward(X1, X2, v, kernel, out, opt):
                                         device=devices[0], budget=lazy_budget(opt))
         else:
             o_dev = out if out.device == dev else torch.empty(out.shape, dtype=out.dtype, device=dev)
-            _lib.call_fmmv_budgeted(kernel_id, sigma, _to_dev(X1, dev), _to_dev(X2, dev), _to_dev(v, dev), o_dev,
-                                    flags=_flags(opt), budget=lazy_budget(opt))
+            with _DebugTimer(opt, "fmmv", dev, f"n={n} m={X2.shape[0]} d={X1.shape[1]} t={t}"):
+                _lib.call_fmmv_budgeted(kernel_id, sigma, _to_dev(X1, dev), _to_dev(X2, dev), _to_dev(v, dev), o_dev,
+                                        flags=_flags(opt), budget=lazy_budget(opt))
             if o_dev is not out:
                 out.copy_(o_dev)
     return out
@@ -255,8 +288,9 @@ def fdmmv(
                                          device=devices[0], budget=lazy_budget(opt))
         else:
             o_dev = out if out.device == dev else torch.empty(out.shape, dtype=out.dtype, device=dev)
-            _lib.call_fdmmv_budgeted(kernel_id, sigma, _to_dev(X1, dev), _to_dev(X2, dev), _to_dev(v, dev),
-                                     _to_dev(w, dev), o_dev, flags=_flags(opt), budget=lazy_budget(opt))
+            with _DebugTimer(opt, "fdmmv", dev, f"n={X1.shape[0]} m={m} d={X1.shape[1]} t={t}"):
+                _lib.call_fdmmv_budgeted(kernel_id, sigma, _to_dev(X1, dev), _to_dev(X2, dev), _to_dev(v, dev),
+                                         _to_dev(w, dev), o_dev, flags=_flags(opt), budget=lazy_budget(opt))
             if o_dev is not out:
                 out.copy_(o_dev)
     return out

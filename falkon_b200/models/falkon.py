@@ -182,19 +182,32 @@ class Falkon:
             else:
                 ny_points, ny_indices = self.center_selection.select_indices(Xd, None)
             n_total = Xd.shape[0]
-            if self.group is not None:
-                import torch.distributed as dist
-
-                ny_points = ny_points.contiguous()
-                dist.broadcast(ny_points, src=dist.get_global_rank(self.group, 0), group=self.group)
-                cnt = torch.tensor([n_total], dtype=torch.int64, device=dev)
-                dist.all_reduce(cnt, group=self.group)
-                n_total = int(cnt.item())
             ny_weight_vec = None
             if self.weight_fn is not None:
                 ny_weight_vec = self.weight_fn(Yd[ny_indices], Xd[ny_indices], ny_indices)
+            if self.group is not None:
+                import torch.distributed as dist
+
+                # Every rank must build the same preconditioner: the centres AND their weights are rank 0's.
+                # The selector clamps the number of centres to the rows of the local shard, so the ranks first
+                # agree that they all hold the same count (tensors of different shapes in one broadcast would
+                # hang the collective instead of failing).
+                src = dist.get_global_rank(self.group, 0)
+                cnt = torch.tensor([n_total, ny_points.shape[0], -ny_points.shape[0]], dtype=torch.int64, device=dev)
+                dist.all_reduce(cnt[:1], group=self.group)
+                dist.all_reduce(cnt[1:], op=dist.ReduceOp.MAX, group=self.group)
+                n_total = int(cnt[0].item())
+                if int(cnt[1].item()) != -int(cnt[2].item()):
+                    raise ValueError(
+                        f"the ranks selected different numbers of centres ({-int(cnt[2].item())} to {int(cnt[1].item())}): "
+                        f"every shard must hold at least M rows")
+                ny_points = ny_points.contiguous()
+                dist.broadcast(ny_points, src=src, group=self.group)
+                if ny_weight_vec is not None:
+                    ny_weight_vec = ny_weight_vec.contiguous()
+                    dist.broadcast(ny_weight_vec, src=src, group=self.group)
             self.precond = FalkonPreconditioner(self.penalty, self.kernel, self.options)
-            self.precond.init(ny_points, weight_vec=ny_weight_vec)
+            self.precond.init(ny_points, weight_vec=ny_weight_vec, group=self.group)
             self.fit_times_.append(time.time() - t_s)
             cback = None
             if self.error_fn is not None and self.error_every is not None:

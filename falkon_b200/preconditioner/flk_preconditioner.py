@@ -119,9 +119,15 @@ class FalkonPreconditioner(Preconditioner):
     def dA(self):
         return None if self.A is None else self.A.diagonal()
 
-    def init(self, X: torch.Tensor, weight_vec: Optional[torch.Tensor] = None):
+    def init(self, X: torch.Tensor, weight_vec: Optional[torch.Tensor] = None, group=None):
         """Builds T and A from the (M x D) centres ``X`` (optionally with per-centre weights for
-        re-weighted least squares, flk_preconditioner.py:131-152)."""
+        re-weighted least squares, flk_preconditioner.py:131-152).
+
+        ``group``: a ``torch.distributed`` process group whose ranks all call ``init`` with the same centres.  The
+        M^3 steps of the fp32 tensor-core path (two factorisations, T T^T) are then shared between the ranks
+        (``tensor_core_la``: block-cyclic trailing updates with a broadcast of each panel, block products completed
+        by an all-reduce); every rank ends up with the same T and A.  Other paths (fp64, library fp32) compute
+        everything on every rank."""
         if weight_vec is not None and weight_vec.shape[0] != X.shape[0]:
             raise ValueError(
                 f"Weights and Nystrom centers should have the same first dimension. "
@@ -140,7 +146,7 @@ class FalkonPreconditioner(Preconditioner):
             tensor_cores = C.dtype == torch.float32 and getattr(self.params, "pc_tensor_cores", True)
             # T^T T = C.  Failure is reported as a status instead of a device assert.
             if tensor_cores:
-                L, code = cholesky_lower_3xtf32(C)  # in place; T is its transpose, as a view
+                L, code = cholesky_lower_3xtf32(C, group=group)  # in place; T is its transpose, as a view
                 T = L.mT
             else:
                 L, info = torch.linalg.cholesky_ex(C, upper=False)
@@ -152,14 +158,14 @@ class FalkonPreconditioner(Preconditioner):
                     f"K_MM is not positive definite; increase pc_epsilon (now {eps})."
                 )
             del C
-            TTt = triu_times_transpose_3xtf32(T) if tensor_cores else _triu_times_transpose(T)
+            TTt = triu_times_transpose_3xtf32(T, group=group) if tensor_cores else _triu_times_transpose(T)
             if weight_vec is not None:
                 s = weight_vec.to(dev, TTt.dtype).reshape(-1).sqrt()
                 TTt.mul_(s.reshape(-1, 1)).mul_(s.reshape(1, -1))
             TTt.mul_(1.0 / M)
             TTt.diagonal().add_(self._lambda)
             if tensor_cores:
-                L2, code = cholesky_lower_3xtf32(TTt)
+                L2, code = cholesky_lower_3xtf32(TTt, group=group)
                 A = L2.mT
             else:
                 L2, info = torch.linalg.cholesky_ex(TTt, upper=False)

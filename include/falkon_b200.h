@@ -10,6 +10,9 @@
  *     from the matching *_workspace_bytes query,
  *   - enqueues its work on the given CUDA stream and returns without synchronising, unless its
  *     description says otherwise (the *_host variants synchronise before returning).
+ * A workspace belongs to one call at a time: calls whose GPU work can overlap (different streams, different host
+ * threads) need a workspace each.  (The Python layer of this repository keeps ONE workspace per device, so its
+ * product calls on a device are meant to come from one thread on one stream.)
  *
  * Matrices are 2-D, described by (pointer, rows, row_stride, col_stride) with strides in
  * elements; one of the two strides must be 1 (C order or Fortran order), as the reference
@@ -192,7 +195,7 @@ int flk_fdmmv_host(int dtype, int kernel,
  * Limits and rules:
  *  - the problem must fit: flk_fmmv_workspace_bytes(dtype, kernel, n, m, d, t, flags) must not exceed
  *    FLK_STATIC_SCRATCH_BYTES, otherwise FLK_ERR_WORKSPACE is returned with a message and nothing runs
- *    (fp32 Gaussian, d = 28, t = 1: about 170,000 rows of X1 and X2 together);
+ *    (fp32 Gaussian, d = 28, t = 1: about 200,000 rows of X1 and X2 together);
  *  - the first call on each device looks up the array's device address (the device must be current);
  *    make that first call outside any stream capture;
  *  - all calls share the one array: two calls whose GPU work can overlap (different streams, or

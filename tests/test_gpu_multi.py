@@ -52,7 +52,17 @@ def _worker(rank, world, port, ret):
         model.fit(Xs, Ys)
         alpha = model.alpha_.cpu().numpy()
         e_alpha = float(np.linalg.norm(alpha - gold["alpha"]) / np.linalg.norm(gold["alpha"]))
-        ret[rank] = (e_dmmv, e_alpha)
+        # fp32 preconditioner with its M^3 steps shared between the ranks against the one a single rank builds
+        from falkon_b200 import FalkonOptions
+        from falkon_b200.preconditioner import FalkonPreconditioner
+
+        g = torch.Generator(device=dev).manual_seed(77)  # the same centres on every rank
+        C32 = torch.randn(5000, 10, generator=g, device=dev)
+        shared = FalkonPreconditioner(1e-6, GaussianKernel(3.0), FalkonOptions()).init(C32, group=dist.group.WORLD)
+        alone = FalkonPreconditioner(1e-6, GaussianKernel(3.0), FalkonOptions()).init(C32)
+        e_T = float((shared.T - alone.T).norm() / alone.T.norm())
+        e_A = float((shared.A - alone.A).norm() / alone.A.norm())
+        ret[rank] = (e_dmmv, e_alpha, e_T, e_A)
     finally:
         dist.destroy_process_group()
 
@@ -68,6 +78,7 @@ def test_sharded_products_and_fit_two_gpus_nccl():
     for r in range(world):
         assert ret[r][0] <= 1e-12, ret[r]   # fp64 products: only the summation order differs
         assert ret[r][1] <= 1e-6, ret[r]    # alpha of the fit on shards = the reference's
+        assert ret[r][2] <= 1e-5 and ret[r][3] <= 1e-4, ret[r]  # shared factorisations = single-rank factorisations
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")

@@ -130,3 +130,45 @@ def test_shard_rows_partition():
             assert max(length for _, length in spans) - min(length for _, length in spans) <= 1
     with pytest.raises(ValueError):
         shard_rows(10, 2, 2)
+
+
+def _pc_worker(rank, world, port, ret):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from falkon_b200.preconditioner.tensor_core_la import cholesky_lower_3xtf32, triu_times_transpose_3xtf32
+
+        g = torch.Generator().manual_seed(7)
+        m = 700
+        X = torch.randn(m, 5, generator=g)
+        K = torch.exp(-0.125 * torch.cdist(X, X).pow(2)) + 0.5 * torch.eye(m)
+        serial, info0 = cholesky_lower_3xtf32(K.clone(), panel=96, trailing=96, k_chunk=64)
+        shared, info1 = cholesky_lower_3xtf32(K.clone(), panel=96, trailing=192, k_chunk=64, group=dist.group.WORLD)
+        e_chol = float((shared - serial).abs().max() / serial.abs().max())
+        T = serial.mT
+        prod_serial = triu_times_transpose_3xtf32(T, block=128, k_chunk=64)
+        prod_shared = triu_times_transpose_3xtf32(T, block=128, k_chunk=64, group=dist.group.WORLD)
+        e_prod = float((prod_shared - prod_serial).abs().max() / prod_serial.abs().max())
+        bad = K.clone()
+        bad[400, 400] = -1.0
+        _, info_bad = cholesky_lower_3xtf32(bad, panel=96, trailing=96, group=dist.group.WORLD)
+        ret[rank] = (e_chol, e_prod, info0, info1, info_bad, bool(torch.equal(prod_shared, prod_shared.T)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_preconditioner_steps_shared_between_ranks_gloo(world):
+    """The fp32 factorisation and T T^T spread over the ranks of a group give every rank the factor / product the
+    single-process routine computes (same block arithmetic, only who does it changes)."""
+    port = 32500 + (os.getpid() % 2000) + world
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_pc_worker, args=(world, port, ret), nprocs=world, join=True)
+    assert sorted(ret.keys()) == list(range(world))
+    for r in range(world):
+        e_chol, e_prod, info0, info1, info_bad, sym = ret[r]
+        assert e_chol < 1e-6 and e_prod < 1e-6, ret[r]
+        assert info0 == 0 and info1 == 0 and info_bad == 401 and sym
