@@ -142,8 +142,8 @@ def cholesky_lower_3xtf32(C: torch.Tensor, panel: int = 2048, trailing: int = 40
     With a process ``group`` (every rank holding the same ``C``) the block columns belong to the ranks in turn
     (block-cyclic, as the reference's multi-GPU POTRF distributes its tiles, falkon/c_ext/ops/cuda/parallel_potrf.cu:121-349):
     a rank applies the trailing updates to its own block columns only; before a panel is factorised its owner
-    broadcasts the up-to-date panel columns, then every rank factorises the panel itself (the panel work is
-    M^2 x panel, the updates M^3 / 3), so all ranks end up with the whole factor and no gather is needed."""
+    broadcasts the up-to-date panel columns; every rank factorises the small diagonal block itself, solves an
+    equal slice of the rows below it and gathers the others' slices, so all ranks end up with the whole factor."""
     if C.dim() != 2 or C.shape[0] != C.shape[1] or C.dtype != torch.float32:
         raise ValueError("cholesky_lower_3xtf32 expects a square float32 matrix")
     M = C.shape[0]
@@ -170,7 +170,22 @@ def cholesky_lower_3xtf32(C: torch.Tensor, panel: int = 2048, trailing: int = 40
         C[k0:k1, k0:k1] = Lkk
         if k1 == M:
             break
-        P = torch.linalg.solve_triangular(Lkk.mT, C[k1:, k0:k1], upper=True, left=False)  # A21 L11^-T
+        if world > 1:
+            # the rows below the diagonal block are independent in A21 L11^-T: every rank solves an equal slice
+            # of them and the slices are gathered (padded to equal length for the collective)
+            below = M - k1
+            chunk = (below + world - 1) // world
+            lo, hi = min(rank * chunk, below), min((rank + 1) * chunk, below)
+            mine = torch.zeros((chunk, k1 - k0), dtype=C.dtype, device=C.device)
+            if hi > lo:
+                mine[: hi - lo] = torch.linalg.solve_triangular(Lkk.mT, C[k1 + lo:k1 + hi, k0:k1], upper=True,
+                                                                left=False)
+            parts = [torch.empty_like(mine) for _ in range(world)]
+            dist.all_gather(parts, mine, group=group)
+            P = torch.cat(parts, dim=0)[:below]
+            del parts, mine
+        else:
+            P = torch.linalg.solve_triangular(Lkk.mT, C[k1:, k0:k1], upper=True, left=False)  # A21 L11^-T
         C[k1:, k0:k1] = P
         p_hi, p_lo = split_tf32(P)
         del P
