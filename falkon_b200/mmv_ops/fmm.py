@@ -133,6 +133,19 @@ def fmm(
         raise NotImplementedError("Sparse kernel matrices are not implemented by falkon_b200.")
     if kwargs_m1 or kwargs_m2:
         raise NotImplementedError("Distance kernels take no per-row keyword tensors (kwargs_m1 / kwargs_m2).")
+    if getattr(kernel, "_flk_spec", None) is None and callable(getattr(kernel, "compute", None)):
+        # a kernel that only implements `compute` (the reference's extension contract): its own code fills the block
+        check_contiguity((X1, "X1"), (X2, "X2"), (out, "out"))
+        _require_cuda(opt, X1, X2)
+        dev = _pick_device((X1.device, X2.device) + (() if out is None else (out.device,)))
+        if out is None:
+            shape = (X1.shape[0],) if diag else (X1.shape[0], X2.shape[0])
+            out = torch.empty(shape, dtype=X1.dtype, device=X1.device)
+        o_dev = out if out.device == dev else torch.empty(out.shape, dtype=out.dtype, device=dev)
+        res = kernel.compute(_to_dev(X1, dev), _to_dev(X2, dev), o_dev, diag)
+        if res is not out:
+            out.copy_(res)
+        return out
     kernel_id, _ = _kernel_spec(kernel)
     check_contiguity((X1, "X1"), (X2, "X2"), (out, "out"))
     _require_cuda(opt, X1, X2)

@@ -30,6 +30,34 @@ def _kernel_spec(kernel):
     return spec()
 
 
+def _is_user_defined(kernel) -> bool:
+    """A kernel that only implements ``compute`` (the reference's extension contract): its products run block by
+    block through that ``compute`` on the GPU (mmv_ops/generic.py), not through the fused CUDA kernels."""
+    return getattr(kernel, "_flk_spec", None) is None and callable(getattr(kernel, "compute", None))
+
+
+def _generic_product(which, X1, X2, v, w, kernel, out, opt):
+    from . import generic
+
+    _require_cuda(opt, X1, X2)
+    tensors = [t for t in (X1, X2, v, w) if t is not None]
+    data_devs = [t.device for t in tensors]
+    lead = v if v is not None else w
+    rows = X1.shape[0] if which == "mmv" else X2.shape[0]
+    out = create_output_mat(out, data_devs, (rows, lead.shape[1]), lead.dtype, "cuda", X1)
+    with torch.inference_mode():
+        dev = _pick_device(tuple(data_devs) + (out.device,))
+        budget = device_budget(opt, dev)
+        o_dev = out if out.device == dev else torch.empty(out.shape, dtype=out.dtype, device=dev)
+        if which == "mmv":
+            generic.generic_fmmv(X1, X2, v, kernel, o_dev, dev, budget)
+        else:
+            generic.generic_fdmmv(X1, X2, v, w, kernel, o_dev, dev, budget)
+        if o_dev is not out:
+            out.copy_(o_dev)
+    return out
+
+
 def _require_cuda(opt: Optional[BaseOptions], *tensors):
     if opt is not None and getattr(opt, "use_cpu", False):
         raise RuntimeError(
@@ -223,6 +251,9 @@ def fmmv(
         raise NotImplementedError("Sparse kernel-vector products are not implemented by falkon_b200.")
     if kwargs_m1 or kwargs_m2:
         raise NotImplementedError("Distance kernels take no per-row keyword tensors (kwargs_m1 / kwargs_m2).")
+    if _is_user_defined(kernel):
+        check_contiguity((X1, "X1"), (X2, "X2"), (v, "v"), (out, "out"))
+        return _generic_product("mmv", X1, X2, v.reshape(-1, 1) if v.dim() == 1 else v, None, kernel, out, opt)
     _kernel_spec(kernel)
     check_contiguity((X1, "X1"), (X2, "X2"), (v, "v"), (out, "out"))
     _require_cuda(opt, X1, X2, v)
@@ -260,6 +291,11 @@ def fdmmv(
         raise NotImplementedError("Distance kernels take no per-row keyword tensors (kwargs_m1 / kwargs_m2).")
     if v is None and w is None:
         raise ValueError("One of v and w must be specified to run fdMMV.")
+    if _is_user_defined(kernel):
+        check_contiguity((X1, "X1"), (X2, "X2"), (v, "v"), (w, "w"), (out, "out"))
+        v2 = v.reshape(-1, 1) if v is not None and v.dim() == 1 else v
+        w2 = w.reshape(-1, 1) if w is not None and w.dim() == 1 else w
+        return _generic_product("dmmv", X1, X2, v2, w2, kernel, out, opt)
     kernel_id, sigma = _kernel_spec(kernel)
     check_contiguity((X1, "X1"), (X2, "X2"), (v, "v"), (w, "w"), (out, "out"))
     _require_cuda(opt, X1, X2)

@@ -104,8 +104,12 @@ def test_products_fail_loudly_without_gpu_or_with_use_cpu():
         def compute(self, X1, X2, out, diag, **kw):
             return out
 
-    with pytest.raises(NotImplementedError, match="_flk_spec"):
-        Custom("custom", None).mmv(X, C, v)
+    # a kernel that only implements `compute` takes the blocked path through its own compute -- on the GPU only
+    if not torch.cuda.is_available():
+        with pytest.raises(RuntimeError, match="needs a CUDA device"):
+            Custom("custom", None).mmv(X, C, v)
+    with pytest.raises(RuntimeError, match="no CPU implementation"):
+        Custom("custom", None).dmmv(X, C, v, None, opt=FalkonOptions(use_cpu=True))
 
 
 def test_output_allocation_rules():
