@@ -444,6 +444,7 @@ static int run_sweep_simt(int kernel, const SweepPlan& sp, const Operand& a, con
   args.row_tiles = sp.row_tiles;
   args.n_col_tiles = sp.n_col_tiles;
   args.tiles_per_chunk = sp.tiles_per_chunk;
+  args.n_chunks = sp.n_chunks;
   args.gate = gate;
   const bool timed = gate.flag == nullptr;  // the gated alternative is not the timed kernel
   if (timed) FLK_TRY(timer_mark(2 * sweep_idx, stream));
@@ -803,7 +804,7 @@ struct HostLayout {
   int64_t chunk_rows = 0;  // rows per chunk (the last one may be shorter)
 };
 
-constexpr int kMaxHostChunks = 4;
+constexpr int kMaxHostChunks = 8;  // the copy of the first chunk is the only one no kernel hides: keep it short
 constexpr int64_t kMinChunkRows = 131072;
 
 static HostLayout make_host_layout(void* ws, bool dmmv, int dtype, int kernel, const Mat& X1, const Mat& X2,

@@ -57,6 +57,7 @@ struct SimtArgs {
   int row_tiles;        // ceil(r / BR)
   int n_col_tiles;      // ceil(s / BC)
   int tiles_per_chunk;  // column tiles per chunk
+  int n_chunks;         // chunks of the reduction side (row_tiles x n_chunks virtual blocks per column group)
   Gate gate;            // run only when the gate is open (see flk_common.cuh)
 };
 
@@ -83,8 +84,12 @@ __global__ void __launch_bounds__(256, (TT == 1 ? 2 : 1)) kmv_simt_kernel(SimtAr
 
   const int tid = threadIdx.x;
   const int tx = tid & 15, ty = tid >> 4;
-  const int row_tile = blockIdx.x % p.row_tiles;
-  const int chunk = blockIdx.x / p.row_tiles;
+  // Virtual block index: a launch may cover the (row tile, chunk) pairs with fewer CTAs than pairs.  The gated
+  // alternative of a tensor-core call is launched that way -- when its gate is closed (the normal case) a few
+  // hundred CTAs return at once instead of tens of thousands.
+  for (int vb = blockIdx.x; vb < p.row_tiles * p.n_chunks; vb += gridDim.x) {
+  const int row_tile = vb % p.row_tiles;
+  const int chunk = vb / p.row_tiles;
   const int t0 = blockIdx.y * TT;
   const int tile_begin = chunk * p.tiles_per_chunk;
   const int tile_end = min(tile_begin + p.tiles_per_chunk, p.n_col_tiles);
@@ -216,6 +221,8 @@ __global__ void __launch_bounds__(256, (TT == 1 ? 2 : 1)) kmv_simt_kernel(SimtAr
       }
     }
   }
+  __syncthreads();  // the next virtual block reuses the shared buffers
+  }
 }
 
 // Launch helper: one instantiation per (dtype, kernel function, TT).
@@ -233,7 +240,10 @@ int launch_simt(const SimtArgs<T>& args, int n_chunks, int t_chunks, cudaStream_
     FLK_CUDA_TRY(cudaFuncSetAttribute(kmv_simt_kernel<T, KT, TT>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   }
-  dim3 grid((unsigned)(args.row_tiles * n_chunks), (unsigned)t_chunks, 1);
+  // one CTA per (row tile, chunk); the gated alternative gets a small grid that walks them (see the kernel)
+  const int64_t blocks = (int64_t)args.row_tiles * n_chunks;
+  dim3 grid((unsigned)(args.gate.flag != nullptr && args.gate.want ? std::min<int64_t>(blocks, 148 * 4) : blocks),
+            (unsigned)t_chunks, 1);
   kmv_simt_kernel<T, KT, TT><<<grid, 256, smem, stream>>>(args);
   FLK_CUDA_TRY(cudaGetLastError());
   return FLK_OK;

@@ -261,6 +261,12 @@ __device__ __forceinline__ void tmem_ld_wait_on(uint32_t (&r)[32], uint64_t (&ac
 __device__ __forceinline__ void tmem_ld_wait_on(uint32_t (&r)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" : FLK_R32_INOUT(r) : : "memory");
 }
+__device__ __forceinline__ void tmem_ld_wait_on(uint32_t (&r)[32], float (&acc)[4]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : FLK_R32_INOUT(r), "+f"(acc[0]), "+f"(acc[1]), "+f"(acc[2]), "+f"(acc[3])
+               :
+               : "memory");
+}
 // 16-column variants for the many-column epilogue (its 32 running sums leave room for 16 accumulator columns).
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
@@ -600,6 +606,9 @@ __host__ __device__ constexpr int poly_pairs_of() {
 #ifndef FLK_TC_POLY_PAIRS_FOLD
 #define FLK_TC_POLY_PAIRS_FOLD 6
 #endif
+#ifndef FLK_TC_FOLD_SCALAR_SUM
+#define FLK_TC_FOLD_SCALAR_SUM 0
+#endif
   return KT == FLK_GAUSSIAN ? (FOLD ? FLK_TC_POLY_PAIRS_FOLD : kPolyPairs)
                             : (KT == FLK_MATERN25 ? FLK_TC_POLY_PAIRS_M25 : FLK_TC_POLY_PAIRS_LM);
 }
@@ -659,6 +668,23 @@ __device__ __forceinline__ void epilogue_32_fold(const uint32_t (&r)[32], uint64
     osum[0] = fma2(pack2(k0, k1), sgn2, osum[0]);
     osum[1] = fma2(pack2(k2, k3), sgn2, osum[1]);
     epilogue_32_fold<KT, C0 + 4>(r, sgn2, osum);
+  }
+}
+
+// The same with scalar adds into four running sums.  The packed f32x2 instructions execute on the heavy FMA pipe
+// only (two cycles each); scalar FFMA can also go to the light pipe, at twice the issue slots.  Which form of the
+// sum is faster depends on which of the two is scarcer: FLK_TC_FOLD_SCALAR_SUM selects it (measured, see the value).
+template <int KT, int C0 = 0>
+__device__ __forceinline__ void epilogue_32_fold_scalar(const uint32_t (&r)[32], float sgn, float (&fs)[4]) {
+  if constexpr (C0 < 32) {
+    float k0, k1, k2, k3;
+    eval_pair<KT, poly_pair<KT, true>(C0 / 2)>(r[C0], r[C0 + 1], k0, k1);
+    eval_pair<KT, poly_pair<KT, true>(C0 / 2 + 1)>(r[C0 + 2], r[C0 + 3], k2, k3);
+    fs[0] = fmaf(k0, sgn, fs[0]);
+    fs[1] = fmaf(k1, sgn, fs[1]);
+    fs[2] = fmaf(k2, sgn, fs[2]);
+    fs[3] = fmaf(k3, sgn, fs[3]);
+    epilogue_32_fold_scalar<KT, C0 + 4>(r, sgn, fs);
   }
 }
 
@@ -916,6 +942,30 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
         }
         tc_fence_after();
         if constexpr (FOLD) {
+#if FLK_TC_FOLD_SCALAR_SUM
+          const float sgn = j >= neg_first ? -1.0f : 1.0f;
+          float fs[4];
+          unpack2(osum[0], fs[0], fs[1]);
+          unpack2(osum[1], fs[2], fs[3]);
+          uint32_t ra[32], rc[32];
+          tmem_ld32(taddr, ra);
+          tmem_ld_wait_on(ra);
+          tmem_ld32(taddr + 32, rc, ra);
+          epilogue_32_fold_scalar<KT>(ra, sgn, fs);
+          tmem_ld_wait_on(rc, fs);
+          tmem_ld32(taddr + 64, ra, rc);
+          epilogue_32_fold_scalar<KT>(rc, sgn, fs);
+          tmem_ld_wait_on(ra, fs);
+          tmem_ld32(taddr + 96, rc, ra);
+          tmem_ld_wait_on(rc);
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(sm + M::T_EMPTY + 8 * rb);
+          epilogue_32_fold_scalar<KT>(ra, sgn, fs);
+          epilogue_32_fold_scalar<KT>(rc, sgn, fs);
+          osum[0] = pack2(fs[0], fs[1]);
+          osum[1] = pack2(fs[2], fs[3]);
+#else
           const uint64_t sgn2 = j >= neg_first ? 0xBF800000BF800000ull : 0x3F8000003F800000ull;
           uint32_t ra[32], rc[32];
           tmem_ld32(taddr, ra);
@@ -933,6 +983,7 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
           if (lane == 0) mbar_arrive(sm + M::T_EMPTY + 8 * rb);
           epilogue_32_fold<KT>(ra, sgn2, osum);
           epilogue_32_fold<KT>(rc, sgn2, osum);
+#endif
         } else {
           const float* vsm = reinterpret_cast<const float*>(tc_smem_raw + pad + M::V) + (j % VS) * kColsPerTile * TT;
           if constexpr (TT == kWideTT) {
