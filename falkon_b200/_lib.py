@@ -365,6 +365,13 @@ def rows_within_budget(query, n: int, budget: Optional[float]) -> int:
             lo = mid
         else:
             hi = mid
+    # The workspace is not strictly monotonic in the row count (the sweep planner's choice of reduction chunks
+    # moves the size of the partial-result buffers): make sure the shorter last chunk fits as well.
+    for _ in range(32):
+        last = n % lo
+        if last == 0 or query(last) <= budget or lo <= 512:
+            break
+        lo = max(512, (lo * 15 // 16) // 512 * 512)
     return lo
 
 

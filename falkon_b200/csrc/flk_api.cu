@@ -821,8 +821,15 @@ static HostLayout make_host_layout(void* ws, bool dmmv, int dtype, int kernel, c
   H.n_chunks = (int)std::max<int64_t>(1, std::min<int64_t>(kMaxHostChunks, n / kMinChunkRows));
   H.chunk_rows = round_up(ceil_div(std::max<int64_t>(n, 1), H.n_chunks), kRowPad);
   H.n_chunks = (int)ceil_div(std::max<int64_t>(n, 1), H.chunk_rows);
-  H.inner_bytes = make_layout(nullptr, dmmv, v.ptr != nullptr, dtype, kernel, std::min(n, H.chunk_rows), X2.rows,
-                              X1.cols, t, flags).total;
+  // The workspace of a product is not monotonic in its row count (the sweep planner picks the number of reduction
+  // chunks, hence of partial-result buffers, from how the tiles fill waves of CTAs): size the inner workspace for
+  // both chunk lengths that occur, the full one and the shorter last one.
+  const int64_t full_rows = std::min(n, H.chunk_rows);
+  const int64_t last_rows = n - (int64_t)(H.n_chunks - 1) * H.chunk_rows;
+  H.inner_bytes = make_layout(nullptr, dmmv, v.ptr != nullptr, dtype, kernel, full_rows, X2.rows, X1.cols, t, flags).total;
+  if (last_rows > 0 && last_rows != full_rows)
+    H.inner_bytes = std::max(H.inner_bytes, make_layout(nullptr, dmmv, v.ptr != nullptr, dtype, kernel, last_rows,
+                                                        X2.rows, X1.cols, t, flags).total);
   H.inner = c.take(H.inner_bytes);
   H.total = c.off;
   return H;

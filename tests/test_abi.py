@@ -59,6 +59,25 @@ def test_workspace_queries_are_pure_host_arithmetic(lib):
     assert lib.flk_fmmv_workspace_bytes(0, 0, -1, 10, 2, 1, 0) == _lib.FLK_ERR_BAD_ARG
 
 
+def test_host_workspace_covers_the_shorter_last_chunk(lib):
+    """The host-buffer entry points stage the operands and run the product in row chunks inside one workspace.  A
+    product's workspace is not monotonic in its row count, so the part left after the staged operands must hold the
+    need of BOTH chunk lengths (1,250,000 rows in eight chunks used to size it for the full chunk only, and the
+    shorter last chunk asked for 11 MB more)."""
+    pad = lambda b: -(-max(b, 1) // 256) * 256
+    m, d, t = 50_000, 28, 1
+    for n in (1_250_000, 2_500_000, 5_000_000, 10_000_000, 3_333_333, 400_001, 131_072 * 3 + 17):
+        chunks = max(1, min(8, n // 131_072))
+        chunk_rows = -(-(-(-n // chunks)) // 512) * 512
+        n_chunks = -(-n // chunk_rows)
+        last = n - (n_chunks - 1) * chunk_rows
+        total = lib.flk_fdmmv_host_workspace_bytes(0, 0, n, m, d, t, 0)
+        staged = pad(n * d * 4) + pad(m * d * 4) + pad(m * t * 4) + pad(n * t * 4) + pad(m * t * 4)
+        inner = total - staged
+        for rows in {min(n, chunk_rows), last}:
+            assert inner >= lib.flk_fdmmv_workspace_bytes(0, 0, rows, m, d, t, 0), (n, rows)
+
+
 def test_argument_errors_return_status_codes(lib):
     sig = (ctypes.c_double * 1)(1.0)
     dummy = ctypes.c_void_p(4096)

@@ -109,3 +109,24 @@ def test_no_host_read_inside_the_loop_without_refresh(monkeypatch):
     monkeypatch.setattr(torch.Tensor, "__bool__", lambda self: (_ for _ in ()).throw(AssertionError("host decision")))
     ConjugateGradient(ConjugateGradientOptions(cg_full_gradient_every=0)).solve(None, B, lambda v: A @ v, 30)
     assert reads == ["int"]
+
+
+def test_device_timeout_status_becomes_an_exception(monkeypatch):
+    """A tensor-core sweep that gave up on a bounded wait leaves a code in the device status word (and NaN in its
+    results); the Falkon solver turns the word into FlkError after the solve.  The mapping is host logic: exercised
+    here with a stand-in for the status read, no GPU and no hung kernel involved."""
+    from falkon_b200 import _lib
+    from falkon_b200.optim import FalkonConjugateGradient
+
+    class OnDevice:  # what _check_device_status looks at: where the tensor lives
+        is_cuda = True
+        device = torch.device("cuda", 0)
+
+    solver = FalkonConjugateGradient(kernel=object(), preconditioner=object())
+    monkeypatch.setattr(_lib, "tc_status", lambda device: 0)
+    solver._check_device_status(None, OnDevice())  # clean status: nothing happens
+    monkeypatch.setattr(_lib, "tc_status", lambda device: 0x31)
+    with pytest.raises(_lib.FlkError) as err:
+        solver._check_device_status(OnDevice())
+    assert err.value.status == _lib.FLK_ERR_TIMEOUT and "0x31" in str(err.value)
+    solver._check_device_status(torch.zeros(3))  # host tensors (the gloo tests) are not asked about
