@@ -8,6 +8,7 @@ from __future__ import annotations
 import ctypes
 import os
 import subprocess
+import re
 import threading
 from typing import Optional
 
@@ -36,9 +37,10 @@ PTXAS_REPORT = LIB_PATH + ".ptxas.txt"
 # to fill must never be spilled, so the resident kernel has to compile without any spill.  It re-partitions
 # registers between its warp roles and relies on being launched with exactly this many per thread:
 TC_LAUNCH_REGISTERS = 80
-# The K-loop kernel still spills a few bytes outside its hot loop in some instantiations; the build tolerates up
-# to this many bytes there and fails beyond (a regression guard, not an endorsement).
-TCK_SPILL_ALLOWANCE = 64
+# A few instantiations of the K-loop kernel still spill one or two 32-bit values that are stored once before the
+# warp roles split (none inside a tile loop); the build tolerates up to this many bytes of spill stores / loads
+# there and fails beyond (a regression guard, not an endorsement).
+TCK_SPILL_ALLOWANCE = (16, 48)
 
 _lock = threading.Lock()
 _lib: Optional[ctypes.CDLL] = None
@@ -130,7 +132,7 @@ def check_ptxas(table):
                 problems.append(f"{name}: {st} bytes of spill stores, {ld} of spill loads (must be 0)")
             if regs != TC_LAUNCH_REGISTERS:
                 problems.append(f"{name}: launched with {regs} registers per thread, {TC_LAUNCH_REGISTERS} assumed")
-        elif "tck::kmv_tck_kernel" in name and max(st, ld) > TCK_SPILL_ALLOWANCE:
+        elif "tck::kmv_tck_kernel" in name and (st > TCK_SPILL_ALLOWANCE[0] or ld > TCK_SPILL_ALLOWANCE[1]):
             problems.append(f"{name}: {st} / {ld} bytes of spill stores / loads exceed the allowance")
     if table and not seen_tc:
         problems.append("no tc::kmv_tc_kernel instantiation found in the ptxas output")

@@ -148,8 +148,10 @@ static bool wide_pays_off(bool tc, int dtype, int kernel, int64_t d, int64_t t) 
 
 // `allow_wide`: the plan may group 32 vector columns per pass.  The SIMT alternative of a tensor-core plan shares
 // its vector buffers and therefore must be planned with the same column grouping.
+// `kloop_d`: feature count when the K-loop tensor-core kernel runs the sweep (its tile shape depends on it), else 0.
 static SweepPlan plan_sweep(bool tc, int dtype, int64_t r, int64_t s, int64_t t, bool allow_wide = false,
-                            bool kloop = false, bool fold = false) {
+                            int64_t kloop_d = 0, bool fold = false) {
+  const bool kloop = kloop_d > 0;
   SweepPlan p;
   p.tc = tc;
   p.kloop = tc && kloop;
@@ -161,8 +163,9 @@ static SweepPlan plan_sweep(bool tc, int dtype, int64_t r, int64_t s, int64_t t,
   choose_tt(t, allow_wide, &p.tt, &p.tp);
   p.t_chunks = p.tp / p.tt;
   if (tc) {
-    p.br = kloop ? tck::kRowsPerCtaL : tc::kRowsPerCta;
-    p.bc = tc::kColsPerTile;
+    const int mode = kloop ? tck::tile_mode(kloop_d, p.tt) : 0;
+    p.br = kloop ? tck::rows_per_cta(mode) : tc::kRowsPerCta;
+    p.bc = kloop ? tck::cols_per_step(mode) : tc::kColsPerTile;
   } else {
     p.br = 128;
     p.bc = (dtype == FLK_F32) ? 128 : 64;
@@ -307,8 +310,8 @@ static Layout make_layout(void* ws, bool dmmv, bool has_v, int dtype, int kernel
   const bool kloop = L.tc && tck::supports_d(d);
   const bool wide_ok = wide_pays_off(L.tc, dtype, kernel, d, t);  // every path has a 32-columns-per-pass kernel
   L.fold = L.tc && !kloop && kernel == FLK_GAUSSIAN && t == 1 && !(flags & FLK_FLAG_NO_FOLD);
-  L.s1 = plan_sweep(L.tc, dtype, n, m, t, wide_ok, kloop, L.fold);  // rows = X1, reduction over X2
-  L.s2 = plan_sweep(L.tc, dtype, m, n, t, wide_ok, kloop, L.fold);  // rows = X2, reduction over X1 (fdmmv only)
+  L.s1 = plan_sweep(L.tc, dtype, n, m, t, wide_ok, kloop ? d : 0, L.fold);  // rows = X1, reduction over X2
+  L.s2 = plan_sweep(L.tc, dtype, m, n, t, wide_ok, kloop ? d : 0, L.fold);  // rows = X2, reduction over X1 (fdmmv only)
   const int64_t n_pad = L.s1.r_pad, m_pad = L.s1.s_pad;
   const bool first = !dmmv || has_v;  // is the first sweep executed?
   if (L.tc) {

@@ -12,10 +12,23 @@
 // accumulators each (512 columns in all), so the MMAs of tile j+1 run under the epilogue of tile j.  The
 // kernel is bound by the tensor pipe / the L2 traffic of the re-streamed operands (3 x the bytes of a plain
 // GEMM of the same shape, because every feature appears three times in the split), not by MUFU.
-// Warps 0-15: epilogue (TMEM lane quarter = warp % 4, row block = (warp / 4) % 2, column half of the tile =
-// warp / 8; the two halves of a row are added at the end through shared memory); warps 16, 17: MMA issuers, one
-// per row block (the barrier round trip between two slabs of one issuer runs under the MMAs of the other; warp 16
-// owns the TMEM allocation); warp 18: bulk-copy producer.  Every wait is bounded as in flk_tc.cuh.
+// Warps 0-15: epilogue (TMEM lane quarter = warp % 4, accumulator group = (warp / 4) % 2, 64-column half of the
+// group's 128 columns = warp / 8; the partial sums of a row are added at the end through shared memory); warps 16,
+// 17: MMA issuers, one per accumulator group (the barrier round trip between two slabs of one issuer runs under the
+// MMAs of the other; warp 16 owns the TMEM allocation); warp 18: bulk-copy producer.  Every wait is bounded as in
+// flk_tc.cuh.
+//
+// What bounds the kernel is operand delivery from L2: a 128 x 128 x 16 MMA takes 64 clocks, and every byte of both
+// operands of every MMA is read from shared memory, which the bulk copies must refill.  Three shapes, by the number
+// of slabs of an operand row (bytes per clock and SM that the copies must sustain for the tensor pipe to stay busy):
+//   kResident2 (up to 8 slabs, d <= 83): both 128-row blocks of the CTA stay in shared memory, a ring stage is one
+//       B slab of 128 columns: 8 KB per four MMAs = 32 B/clk;
+//   kResident1 (9..16 slabs, d <= 168): ONE 128-row block stays resident and the CTA walks PAIRS of column tiles
+//       (256 columns): the two accumulator groups are the two tiles of the pair, a ring stage is their two B slabs
+//       (16 KB per 256 clocks of MMA = 64 B/clk), and one issuer covers both groups with 128 x 256 x 16 MMAs, which
+//       read 12 KB of operands from shared memory per 128 clocks where two 128 x 128 x 16 read 16 KB -- the
+//       operand reads of the MMAs and the writes of the bulk copies share the shared memory's 128 B/clk;
+//   kStream (more slabs): nothing fits; two row blocks, a stage carries both A slabs and the B slab: 96 B/clk.
 #pragma once
 
 #include "flk_tc.cuh"
@@ -25,30 +38,48 @@ namespace tck {
 
 using namespace tc;  // PTX wrappers, image layout, epilogue helpers
 
-constexpr int kRowBlocksL = 2;
-constexpr int kRowsPerCtaL = kRowBlocksL * kTileRows;  // 256
+constexpr int kGroupsL = 2;                             // accumulator groups = MMA issuers
 constexpr int kMaxDL = 1024;
 constexpr int kSlabBytes = kTileRows * kSlabK * 2;      // 8 KB: one 128-row slab of an operand image
 constexpr int kStages = 8;
-constexpr int kMaxResidentSlabs = 8;                    // both A blocks stay in shared memory up to this many slabs
-constexpr int kColSplitL = 2;                           // epilogue warps per (row block, lane quarter): each takes 64 columns of a tile
-constexpr int kEpiWarpsL = 4 * kRowBlocksL * kColSplitL;
-constexpr int kMmaWarpL = kEpiWarpsL;                   // warps 16, 17: MMA issuer of row block (warp - 16)
-constexpr int kProducerWarpL = kEpiWarpsL + kRowBlocksL;
+constexpr int kMaxStagesL = 12;                         // barrier slots of the operand ring
+constexpr int kMaxResidentSlabs = 8;                    // kResident2: both A blocks stay in shared memory up to this many slabs
+constexpr int kMaxResidentSlabs1 = 16;                  // kResident1: one A block stays in shared memory up to this many slabs
+constexpr int kColSplitL = 2;                           // epilogue warps per (group, lane quarter): each takes 64 columns
+constexpr int kEpiWarpsL = 4 * kGroupsL * kColSplitL;
+constexpr int kMmaWarpL = kEpiWarpsL;                   // warps 16, 17: MMA issuer of group (warp - 16)
+constexpr int kProducerWarpL = kEpiWarpsL + kGroupsL;
 // warp 19 does no work: it completes the warpgroup of the two issuers and the producer, so that this group can
 // hand registers to the four epilogue warpgroups (setmaxnreg works on whole warpgroups, see flk_tc.cuh).  20 warps
 // = 5 per SM sub-partition = 96 registers per thread at launch; afterwards 16 x 104 + 4 x 64 = 20 x 96.
-constexpr int kThreadsL = (kEpiWarpsL + kRowBlocksL + 2) * 32;
+constexpr int kThreadsL = (kEpiWarpsL + kGroupsL + 2) * 32;
 constexpr int kRegsEpilogueL = 104;
 constexpr int kRegsOthersL = 64;
 static_assert(kEpiWarpsL * kRegsEpilogueL + 4 * kRegsOthersL <= (kThreadsL / 32) * 96,
               "register re-partitioning exceeds the pool the CTA is launched with");
+constexpr int kMaxSmemL = 226 * 1024;  // dynamic shared memory of a CTA: the 227 KB limit less the kernel's static variables
+
+// M = 128, N = 256 form of the instruction descriptor (see tc::kInstrDesc)
+constexpr uint32_t kInstrDescN256 = (1u << 4) | ((uint32_t)((2 * kColsPerTile) >> 3) << 17) | ((uint32_t)(kTileRows >> 4) << 24);
+
+enum TileMode { kStream = 0, kResident2 = 1, kResident1 = 2 };
+// rows of a CTA and columns of one step of its tile loop
+__host__ __device__ constexpr int rows_per_cta(int mode) { return mode == kResident1 ? kTileRows : 2 * kTileRows; }
+__host__ __device__ constexpr int cols_per_step(int mode) { return mode == kResident1 ? 2 * kColsPerTile : kColsPerTile; }
+constexpr int kRowsPerCtaL = 2 * kTileRows;  // 256, the kStream / kResident2 shapes
 
 inline bool supports_d(int64_t d) { return d > tc::kMaxD && d <= kMaxDL; }
 inline int used_k(int64_t d) { return (int)(3 * d + 6); }  // always three norm pieces
 inline int k_steps(int64_t d) { return (int)(round_up(used_k(d), kMmaK) / kMmaK); }
 inline int64_t padded_k(int64_t d) { return round_up(used_k(d), kSlabK); }
 inline int n_slabs(int64_t d) { return (int)(padded_k(d) / kSlabK); }
+// tile shape for `d` features and `tt` vector columns per pass (the 32-column epilogue needs its shared memory for
+// vector tiles and partial sums: it streams)
+inline int tile_mode(int64_t d, int tt) {
+  if (tt == tc::kWideTT) return kStream;
+  const int ns = n_slabs(d);
+  return ns <= kMaxResidentSlabs ? kResident2 : (ns <= kMaxResidentSlabs1 ? kResident1 : kStream);
+}
 
 // ---------------------------------------------------------------------------------------------
 // Operand images for any feature count: one block = one 128-row tile, one thread = one row.  The image is
@@ -168,15 +199,14 @@ struct SweepArgsL {
   int tp;
   int64_t r_pad;
   int64_t s_pad;
-  int row_tiles;        // ceil(r / 256)
-  int n_col_tiles;      // ceil(s / 128)
-  int tiles_per_chunk;
+  int row_tiles;        // ceil(r / rows of a CTA)
+  int n_col_tiles;      // steps of the tile loop over the whole reduction side: ceil(s / columns per step)
+  int tiles_per_chunk;  // in the same unit
   int nslab;            // K slabs per operand tile
   int ksteps;           // MMA K-steps carrying data (two per slab, possibly one in the last slab)
+  int ring;             // stages of the operand ring (kResident1: as many as the shared memory left by A holds)
 };
 
-// ARES: the two A blocks of the CTA (256 rows x nslab slabs, at most 128 KB) are loaded once and stay resident;
-// a ring stage then carries the B slab only (8 KB instead of 24 KB), which cuts the L2 traffic three-fold.
 // With 32 vector columns per pass the vector tiles are 16 KB each: two of them and a six-stage operand ring.
 template <int TT>
 struct RingCfg {
@@ -184,59 +214,64 @@ struct RingCfg {
   static constexpr int VS = TT == kWideTT ? 2 : kVecStages;
 };
 
-template <int TT, bool ARES>
-constexpr size_t tck_smem_bytes() {
-  return 1024 + (ARES ? (size_t)kRowBlocksL * kMaxResidentSlabs * kSlabBytes : 0) +
-         (size_t)RingCfg<TT>::S * (ARES ? 1 : 3) * kSlabBytes + (size_t)RingCfg<TT>::VS * kColsPerTile * TT * 4 + 512 +
-         (size_t)kRowsPerCtaL * TT * 4 /* partial sums of the second column half */;
-}
-
-// Kernel function + contraction with 32 vector columns for 32 accumulator columns held in registers: per kernel
-// value one exponential, then 16 packed multiply-adds against the 32 vector entries of that column (read as
-// eight 16-byte broadcasts from shared memory).
-template <int KT, int C0 = 0>
-__device__ __forceinline__ void epilogue_wide32(const uint32_t (&r)[32], const float* vsm, uint64_t (&osum)[16]) {
-  if constexpr (C0 < 32) {
-    float k0, k1;
-    eval_pair<KT, poly_pair<KT>(C0 / 2)>(r[C0], r[C0 + 1], k0, k1);
-    const float kv[2] = {k0, k1};
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      const uint64_t kk = pack2(kv[c], kv[c]);
-      const ulonglong2* v = reinterpret_cast<const ulonglong2*>(vsm + (C0 + c) * kWideTT);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const ulonglong2 vv = v[i];
-        osum[2 * i] = fma2(kk, vv.x, osum[2 * i]);
-        osum[2 * i + 1] = fma2(kk, vv.y, osum[2 * i + 1]);
-      }
-    }
-    epilogue_wide32<KT, C0 + 2>(r, vsm, osum);
+// Shared-memory map, as offsets from a 1024-byte aligned base: barrier block (512 B) | partial sums of the other
+// column groups | vector ring | [resident A slabs] | operand ring.  The first three have fixed sizes.
+template <int TT, int MODE>
+struct SmemMapL {
+  static constexpr int VS = RingCfg<TT>::VS;
+  static constexpr uint32_t kVecTileBytes = cols_per_step(MODE) * TT * 4;
+  // kResident1: three of the four column groups of a row hand their sums over; otherwise one of two
+  static constexpr uint32_t kCombineBytes = (MODE == kResident1 ? 3 * kTileRows : kRowsPerCtaL) * TT * 4;
+  static constexpr uint32_t kCombineOff = 512;
+  static constexpr uint32_t kVecOff = kCombineOff + kCombineBytes;
+  static constexpr uint32_t kFixedBytes = (kVecOff + VS * kVecTileBytes + 1023u) & ~1023u;
+  static constexpr uint32_t kStageBytes = (MODE == kStream ? 3 : (MODE == kResident1 ? 2 : 1)) * kSlabBytes;
+  // barrier block: s_full[12] | s_empty[12] | v_full[VS] | v_empty[VS] | t_full[4] | t_empty[4] (index
+  // group * 2 + buf) | a_full | tmem pointer | abort flag
+  static constexpr uint32_t kSFull = 0, kSEmpty = kSFull + 8 * kMaxStagesL, kVFull = kSEmpty + 8 * kMaxStagesL;
+  static constexpr uint32_t kVEmpty = kVFull + 8 * VS, kTFull = kVEmpty + 8 * VS, kTEmpty = kTFull + 32;
+  static constexpr uint32_t kAFull = kTEmpty + 32, kTmemPtr = kAFull + 8, kAbort = kTmemPtr + 4;
+  static_assert(kAbort + 4 <= kCombineOff, "barrier block overflows its 512 bytes");
+  static __host__ __device__ constexpr uint32_t resident_bytes(int nslab) {
+    return MODE == kResident2 ? 2u * kMaxResidentSlabs * kSlabBytes : (MODE == kResident1 ? (uint32_t)nslab * kSlabBytes : 0u);
   }
-}
+  // stages of the operand ring for `nslab` slabs per row
+  static int ring_stages(int nslab) {
+    if (MODE != kResident1) return RingCfg<TT>::S;
+    const int room = (kMaxSmemL - 1024 - (int)kFixedBytes - (int)resident_bytes(nslab)) / (int)kStageBytes;
+    return room < kMaxStagesL ? room : kMaxStagesL;
+  }
+  static size_t total_bytes(int nslab) {
+    return 1024 + (size_t)kFixedBytes + resident_bytes(nslab) + (size_t)ring_stages(nslab) * kStageBytes;
+  }
+};
 
 __device__ __forceinline__ void report_timeout(int* status, int code) { atomicExch(status + kStatusTimeout, code); }
 
-template <int KT, int TT, bool ARES>
+template <int KT, int TT, int MODE>
 __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL p) {
-  constexpr int S = RingCfg<TT>::S, VS = RingCfg<TT>::VS;
-  constexpr int kStageBytes = (ARES ? 1 : 3) * kSlabBytes;  // [A block 0 | A block 1 |] B tile
-  constexpr int kAResBytes = ARES ? kRowBlocksL * kMaxResidentSlabs * kSlabBytes : 0;
+  using Map = SmemMapL<TT, MODE>;
+  constexpr int VS = Map::VS;
+  constexpr uint32_t kStageBytes = Map::kStageBytes, kVecTileBytes = Map::kVecTileBytes;
+  constexpr int kRowsCta = rows_per_cta(MODE);
+  // kResident1: the two accumulator groups are neighbouring column tiles of one A block, so ONE issuer covers both
+  // with 256-column MMAs (12 KB of operand reads from shared memory per 128 clocks instead of 16 KB)
+  constexpr bool kOneMma = MODE == kResident1;
+  constexpr int kIssuers = kOneMma ? 1 : kGroupsL;
+  constexpr int kStepCols = cols_per_step(MODE);
+  constexpr uint32_t kSFull = Map::kSFull, kSEmpty = Map::kSEmpty, kVFull = Map::kVFull, kVEmpty = Map::kVEmpty;
+  constexpr uint32_t kTFull = Map::kTFull, kTEmpty = Map::kTEmpty, kAFull = Map::kAFull, kTmemPtr = Map::kTmemPtr;
+  constexpr uint32_t kAbort = Map::kAbort;
   extern __shared__ unsigned char tck_smem_raw[];
   const uint32_t raw_addr = smem_u32(tck_smem_raw);
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
-  // Shared-memory map as 32-bit shared addresses from one base (generic pointers to every ring and barrier would
-  // stay live across all warp roles): [A blocks, ARES only] | operand ring | vector ring | barrier block | combine.
-  // barrier block: s_full[S] | s_empty[S] | v_full[VS] | v_empty[VS] | t_full[4] | t_empty[4] (index rb * 2 + buf) |
-  // a_full | tmem pointer | abort flag
+  // 32-bit shared addresses from one base (generic pointers to every ring and barrier would stay live across all
+  // warp roles)
   const uint32_t sm = raw_addr + pad;
-  constexpr uint32_t kRingOff = kAResBytes;
-  constexpr uint32_t kVecOff = kRingOff + S * kStageBytes;
-  constexpr uint32_t kBarsOff = kVecOff + VS * kColsPerTile * TT * 4;
-  constexpr uint32_t kSFull = kBarsOff, kSEmpty = kSFull + 8 * S, kVFull = kSEmpty + 8 * S, kVEmpty = kVFull + 8 * VS;
-  constexpr uint32_t kTFull = kVEmpty + 8 * VS, kTEmpty = kTFull + 32, kAFull = kTEmpty + 32;
-  constexpr uint32_t kTmemPtr = kAFull + 8, kAbort = kTmemPtr + 4, kCombineOff = kBarsOff + 512;
-  static_assert(kAbort + 4 <= kCombineOff, "barrier block overflows its 512 bytes");
+  const int nslab = p.nslab;
+  const uint32_t S = MODE == kResident1 ? (uint32_t)p.ring : (uint32_t)RingCfg<TT>::S;
+  const uint32_t sm_a = sm + Map::kFixedBytes;                  // resident A slabs (if any)
+  const uint32_t sm_ring = sm_a + Map::resident_bytes(nslab);   // operand ring
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
@@ -246,7 +281,6 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
   const int tile_begin = chunk * p.tiles_per_chunk;
   const int tile_end = min(tile_begin + p.tiles_per_chunk, p.n_col_tiles);
   const int ntiles = tile_end - tile_begin;
-  const int nslab = p.nslab;
 
   __shared__ int skip_launch;
   if (tid == 0) {
@@ -258,9 +292,9 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
 
   if (tid == 0) {
 #pragma unroll 1
-    for (int s = 0; s < S; ++s) {
+    for (uint32_t s = 0; s < S; ++s) {
       mbar_init(sm + kSFull + 8 * s, 1);
-      mbar_init(sm + kSEmpty + 8 * s, kRowBlocksL);  // one MMA commit per issuer
+      mbar_init(sm + kSEmpty + 8 * s, kIssuers);  // one MMA commit per issuer
     }
     for (int s = 0; s < VS; ++s) {
       mbar_init(sm + kVFull + 8 * s, 1);
@@ -268,7 +302,8 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
     }
     for (int i = 0; i < 4; ++i) {
       mbar_init(sm + kTFull + 8 * i, 1);
-      mbar_init(sm + kTEmpty + 8 * i, 4 * kColSplitL);  // the eight warps of that row block
+      // the warps that drain that accumulator: the eight of its group, or all sixteen (one accumulator per buffer)
+      mbar_init(sm + kTEmpty + 8 * i, (kOneMma ? 2 : 1) * 4 * kColSplitL);
     }
     mbar_init(sm + kAFull, 1);
     st_shared_i32_volatile(sm + kAbort, 0);
@@ -288,18 +323,18 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
   } else if (warp == kProducerWarpL) {
     // ------------------------------ bulk-copy producer ------------------------------
     reg_release<kRegsOthersL>();
-    const __half* a_base = p.img_a + (int64_t)row_tile * kRowBlocksL * nslab * (kTileRows * kSlabK);
+    constexpr int kABlocks = kRowsCta / kTileRows;
+    const __half* a_base = p.img_a + (int64_t)row_tile * kABlocks * nslab * (kTileRows * kSlabK);
     const float* vec_base = p.vec + (int64_t)tchunk * p.s_pad * TT;
-    if (ARES && elect_one()) {
-      // the CTA's two A blocks are contiguous in the image: [row block][slab]
-      const uint32_t bytes = (uint32_t)(kRowBlocksL * nslab * kSlabBytes);
+    if (MODE != kStream && elect_one()) {
+      // the CTA's A blocks are contiguous in the image: [row block][slab]
+      const uint32_t bytes = (uint32_t)(kABlocks * nslab * kSlabBytes);
       mbar_expect_tx(sm + kAFull, bytes);
-      for (int i = 0; i < kRowBlocksL * nslab; ++i)
-        bulk_copy_g2s(sm + i * kSlabBytes, a_base + (int64_t)i * (kTileRows * kSlabK), kSlabBytes,
-                      sm + kAFull);
+      for (int i = 0; i < kABlocks * nslab; ++i)
+        bulk_copy_g2s(sm_a + i * kSlabBytes, a_base + (int64_t)i * (kTileRows * kSlabK), kSlabBytes, sm + kAFull);
     }
     __syncwarp();
-    uint32_t gs = 0;  // running slab counter
+    uint32_t stage = 0, wrap = 0;  // ring position of the running slab counter and its wrap parity
     bool ok = true;
     for (int j = 0; ok && j < ntiles; ++j) {
       const int64_t ct = tile_begin + j;
@@ -311,16 +346,15 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
       }
       if (elect_one()) {
         const uint32_t vbar = sm + kVFull + 8 * vstage;
-        mbar_expect_tx(vbar, kColsPerTile * TT * 4);
-        bulk_copy_g2s(sm + kVecOff + vstage * kColsPerTile * TT * 4, vec_base + ct * kColsPerTile * TT,
-                      kColsPerTile * TT * 4, vbar);
+        mbar_expect_tx(vbar, kVecTileBytes);
+        bulk_copy_g2s(sm + Map::kVecOff + vstage * kVecTileBytes, vec_base + ct * kStepCols * TT, kVecTileBytes, vbar);
       }
       __syncwarp();
-      const __half* b_base = p.img_b + ct * nslab * (kTileRows * kSlabK);
-      for (int s = 0; s < nslab; ++s, ++gs) {
-        const int stage = (int)(gs % (uint32_t)S);
+      // first B tile of this step; kResident1 takes the following tile too (the image is padded to four tiles)
+      const __half* b_base = p.img_b + ct * (kStepCols / kColsPerTile) * nslab * (kTileRows * kSlabK);
+      for (int s = 0; s < nslab; ++s) {
         if (ld_shared_i32_volatile(sm + kAbort)) { ok = false; break; }
-        if (!mbar_wait(sm + kSEmpty + 8 * stage, ((gs / (uint32_t)S) & 1u) ^ 1u)) {
+        if (!mbar_wait(sm + kSEmpty + 8 * stage, wrap ^ 1u)) {
           if (lane == 0) report_timeout(p.status, kErrProducer | 1);
           st_shared_i32_volatile(sm + kAbort, 1);
           ok = false;
@@ -328,24 +362,33 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
         }
         if (elect_one()) {
           const uint32_t bar = sm + kSFull + 8 * stage;
-          const uint32_t dst = sm + kRingOff + stage * kStageBytes;
+          const uint32_t dst = sm_ring + stage * kStageBytes;
           mbar_expect_tx(bar, kStageBytes);
-          if (!ARES) {
+          if (MODE == kStream) {
             bulk_copy_g2s(dst, a_base + (int64_t)s * (kTileRows * kSlabK), kSlabBytes, bar);
             bulk_copy_g2s(dst + kSlabBytes, a_base + ((int64_t)nslab + s) * (kTileRows * kSlabK), kSlabBytes, bar);
+            bulk_copy_g2s(dst + 2 * kSlabBytes, b_base + (int64_t)s * (kTileRows * kSlabK), kSlabBytes, bar);
+          } else {
+            bulk_copy_g2s(dst, b_base + (int64_t)s * (kTileRows * kSlabK), kSlabBytes, bar);
+            if (MODE == kResident1)
+              bulk_copy_g2s(dst + kSlabBytes, b_base + ((int64_t)nslab + s) * (kTileRows * kSlabK), kSlabBytes, bar);
           }
-          bulk_copy_g2s(dst + (ARES ? 0 : 2) * kSlabBytes, b_base + (int64_t)s * (kTileRows * kSlabK), kSlabBytes, bar);
         }
         __syncwarp();
+        if (++stage == S) {
+          stage = 0;
+          wrap ^= 1u;
+        }
       }
     }
   } else if (warp >= kMmaWarpL) {
-    // ------------------------------ MMA issuers (one per row block) ------------------------------
+    // ------------------------------ MMA issuers (one per accumulator group) ------------------------------
+    // group = row block of the CTA (kStream, kResident2) or column tile of the pair (kResident1)
     reg_release<kRegsOthersL>();
-    const int rb = warp - kMmaWarpL;
-    uint32_t gs = 0;
-    bool ok = true;
-    if (ARES && !mbar_wait(sm + kAFull, 0)) {
+    const int grp = warp - kMmaWarpL;
+    uint32_t stage = 0, wrap = 0;
+    bool ok = grp < kIssuers;  // kResident1: warp 16 issues 256-column MMAs for both groups, warp 17 has no work
+    if (ok && MODE != kStream && !mbar_wait(sm + kAFull, 0)) {
       if (lane == 0) report_timeout(p.status, kErrMma | 1);
       st_shared_i32_volatile(sm + kAbort, 1);
       ok = false;
@@ -353,16 +396,16 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
     for (int j = 0; ok && j < ntiles; ++j) {
       const int buf = j & 1;
       if (ld_shared_i32_volatile(sm + kAbort)) break;
-      // this row block's accumulator of this buffer must have been drained (tile j - 2)
-      if (!mbar_wait(sm + kTEmpty + 8 * (rb * 2 + buf), ((j >> 1) & 1) ^ 1)) {
+      // this group's accumulator of this buffer must have been drained (step j - 2)
+      const int acc = kOneMma ? buf : grp * 2 + buf;
+      if (!mbar_wait(sm + kTEmpty + 8 * acc, ((j >> 1) & 1) ^ 1)) {
         if (lane == 0) report_timeout(p.status, kErrMma | 3);
         st_shared_i32_volatile(sm + kAbort, 1);
         break;
       }
-      const uint32_t d_tmem = tmem_base + (uint32_t)((rb * 2 + buf) * kColsPerTile);
-      for (int s = 0; s < nslab; ++s, ++gs) {
-        const int stage = (int)(gs % (uint32_t)S);
-        if (!mbar_wait(sm + kSFull + 8 * stage, (gs / (uint32_t)S) & 1u)) {
+      const uint32_t d_tmem = tmem_base + (uint32_t)(acc * (kOneMma ? 2 : 1) * kColsPerTile);
+      for (int s = 0; s < nslab; ++s) {
+        if (!mbar_wait(sm + kSFull + 8 * stage, wrap)) {
           if (lane == 0) report_timeout(p.status, kErrMma | 2);
           st_shared_i32_volatile(sm + kAbort, 1);
           ok = false;
@@ -370,26 +413,39 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
         }
         tc_fence_after();
         if (elect_one()) {
-          const uint32_t sbase = sm + kRingOff + stage * kStageBytes;
-          const uint64_t b_desc = make_smem_desc(sbase + (ARES ? 0 : 2) * kSlabBytes);
-          const uint64_t a_desc = make_smem_desc(ARES ? sm + (rb * nslab + s) * kSlabBytes
-                                                      : sbase + rb * kSlabBytes);
+          const uint32_t sbase = sm_ring + stage * kStageBytes;
+          uint32_t a_addr, b_addr;
+          if (MODE == kStream) {
+            a_addr = sbase + grp * kSlabBytes;
+            b_addr = sbase + 2 * kSlabBytes;
+          } else if (MODE == kResident2) {
+            a_addr = sm_a + (grp * nslab + s) * kSlabBytes;
+            b_addr = sbase;
+          } else {
+            a_addr = sm_a + s * kSlabBytes;
+            b_addr = sbase;  // both B slabs of the stage: 256 rows of 64 bytes, contiguous
+          }
+          const uint64_t a_desc = make_smem_desc(a_addr), b_desc = make_smem_desc(b_addr);
           const int nks = min(2, p.ksteps - 2 * s);  // K-steps of this slab that carry data
           for (int ks = 0; ks < nks; ++ks)
-            mma_f16(d_tmem, a_desc + (uint64_t)(ks * 2), b_desc + (uint64_t)(ks * 2), kInstrDesc,
-                    (s > 0 || ks > 0) ? 1u : 0u);
+            mma_f16(d_tmem, a_desc + (uint64_t)(ks * 2), b_desc + (uint64_t)(ks * 2),
+                    kOneMma ? kInstrDescN256 : kInstrDesc, (s > 0 || ks > 0) ? 1u : 0u);
           mma_commit(sm + kSEmpty + 8 * stage);
-          if (s == nslab - 1) mma_commit(sm + kTFull + 8 * (rb * 2 + buf));
+          if (s == nslab - 1) mma_commit(sm + kTFull + 8 * acc);
         }
         __syncwarp();
+        if (++stage == S) {
+          stage = 0;
+          wrap ^= 1u;
+        }
       }
     }
   } else {
     // ------------------------------ epilogue warps ------------------------------
     reg_claim<kRegsEpilogueL>();
     const int q = warp & 3;
-    const int rb = (warp >> 2) & 1;
-    const int half = warp >> 3;  // columns half * 64 .. + 63 of every tile
+    const int grp = (warp >> 2) & 1;
+    const int half = warp >> 3;  // columns half * 64 .. + 63 of the group's 128
     constexpr int NSUM = TT == kWideTT ? 16 : 2;
     // two-level summation for TT <= 4, as in the resident kernel (here the second level fits in registers);
     // the many-column form keeps one level and relies on the planner's bound on the chunk length
@@ -399,7 +455,12 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
 #pragma unroll
     for (int i = 0; i < (TT == kWideTT ? 1 : NSUM); ++i) otot[i] = 0ull;
     bool epi_ok = true;
-    for (int j0 = 0; j0 < ntiles && epi_ok; j0 += tc::kFlushTiles) {
+    // vector entries of this warp's columns inside a vector tile
+    constexpr int kGroupCols = MODE == kResident1 ? kColsPerTile : 0;
+    const int vcol = grp * kGroupCols + half * 64;
+    // steps summed in one running sum before it is folded away (one level only for the many-column form)
+    constexpr int kFlush = TT == kWideTT ? (1 << 30) : tc::kFlushTiles;
+    for (int j0 = 0; j0 < ntiles && epi_ok; j0 += kFlush) {
     if constexpr (TT != kWideTT) {
       if (j0 > 0) {
 #pragma unroll
@@ -409,12 +470,12 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
         }
       }
     }
-    const int j1 = min(j0 + tc::kFlushTiles, ntiles);
+    const int j1 = TT == kWideTT ? ntiles : min(j0 + kFlush, ntiles);
     for (int j = j0; j < j1; ++j) {
       const int vstage = j % VS, buf = j & 1;
       if (ld_shared_i32_volatile(sm + kAbort)) { epi_ok = false; break; }
-      if (!mbar_wait(sm + kVFull + 8 * vstage, (j / VS) & 1) ||
-          !mbar_wait(sm + kTFull + 8 * (rb * 2 + buf), (j >> 1) & 1)) {
+      const int acc = kOneMma ? buf : grp * 2 + buf;
+      if (!mbar_wait(sm + kVFull + 8 * vstage, (j / VS) & 1) || !mbar_wait(sm + kTFull + 8 * acc, (j >> 1) & 1)) {
         report_timeout(p.status, kErrEpilogue | 1);
         st_shared_i32_volatile(sm + kAbort, 1);
         epi_ok = false;
@@ -422,38 +483,48 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) +
-                             (uint32_t)((rb * 2 + buf) * kColsPerTile + half * 64);
-      const float* vsm = reinterpret_cast<const float*>(tck_smem_raw + pad + kVecOff) + (vstage * kColsPerTile + half * 64) * TT;
+                             (uint32_t)((kOneMma ? buf * 2 + grp : grp * 2 + buf) * kColsPerTile + half * 64);
+      // generic pointer rebuilt from the 32-bit shared address, so that no 64-bit base stays live across the loop
+      const float* vsm = reinterpret_cast<const float*>(
+          __cvta_shared_to_generic(sm + Map::kVecOff + vstage * kVecTileBytes + (uint32_t)(vcol * TT * 4)));
       if constexpr (TT == kWideTT) {
-        // 32 running sums per thread leave room for one 32-column piece at a time
+        // 32 running sums per thread leave room for 16 columns at a time: four pieces; the accumulator goes back
+        // to its issuer once the last one is in registers
+        uint32_t rw[16];
+#pragma unroll
+        for (int pc = 0; pc < 4; ++pc) {
+          tmem_ld16(taddr + pc * 16, rw);
+          tmem_ld_wait_on(rw);
+          if (pc == 3) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(sm + kTEmpty + 8 * acc);
+          }
+          if (pc & 1)
+            epilogue_wide16<KT, 8>(rw, vsm + pc * 16 * TT, osum);
+          else
+            epilogue_wide16<KT, 0>(rw, vsm + pc * 16 * TT, osum);
+        }
+      } else {
+        // 32 columns at a time through one register block (two blocks in flight left no room for the constants of
+        // the polynomial exponential); the accumulator goes back once the second piece is in registers -- the other
+        // buffer of this group keeps the issuer busy meanwhile
         uint32_t ra[32];
         tmem_ld32(taddr, ra);
         tmem_ld_wait_on(ra);
-        epilogue_wide32<KT>(ra, vsm, osum);
+        epilogue_32<KT, TT>(ra, vsm, osum);
         tmem_ld32(taddr + 32, ra);
         tmem_ld_wait_on(ra);
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(sm + kTEmpty + 8 * (rb * 2 + buf));
-        epilogue_wide32<KT>(ra, vsm + 32 * TT, osum);
-      } else {
-        uint32_t ra[32], rc[32];
-        tmem_ld32(taddr, ra);
-        tmem_ld_wait_on(ra);
-        tmem_ld32(taddr + 32, rc, ra);
-        tmem_ld_wait_on(rc);
-        // this warp's 64 columns are in registers: hand the accumulator back before evaluating them
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(sm + kTEmpty + 8 * (rb * 2 + buf));
-        epilogue_32<KT, TT>(ra, vsm, osum);
-        epilogue_32<KT, TT>(rc, vsm + 32 * TT, osum);
+        if (lane == 0) mbar_arrive(sm + kTEmpty + 8 * acc);
+        epilogue_32<KT, TT>(ra, vsm + 32 * TT, osum);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(sm + kVEmpty + 8 * vstage);
     }
     }
-    // per-thread sums of this column half
+    // per-thread sums of this warp's columns
     if constexpr (TT != kWideTT) {
 #pragma unroll
       for (int i = 0; i < NSUM; ++i) osum[i] = tc::add2(otot[i], osum[i]);
@@ -478,19 +549,28 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
         o[3] = b1;
       }
     }
-    const int rloc = rb * kTileRows + q * 32 + lane;
-    float* combine = reinterpret_cast<float*>(tck_smem_raw + pad + kCombineOff);  // [256 rows][TT]
-    if (half == 1) {
+    // Column groups of one output row meet in shared memory; the warp holding group 0 adds them in a fixed order.
+    // kStream / kResident2: a row (row block grp) has the two halves; kResident1: a row has the four (grp, half).
+    constexpr int kParts = MODE == kResident1 ? 4 : 2;
+    const int part = MODE == kResident1 ? grp * 2 + half : half;
+    const int rloc = (MODE == kResident1 ? 0 : grp * kTileRows) + q * 32 + lane;
+    float* combine = reinterpret_cast<float*>(__cvta_shared_to_generic(sm + Map::kCombineOff));  // [kParts - 1][rows of the CTA][TT]
+    if (part > 0) {
 #pragma unroll
-      for (int t = 0; t < TT; ++t) combine[rloc * TT + t] = o[t];
+      for (int t = 0; t < TT; ++t) combine[((part - 1) * kRowsCta + rloc) * TT + t] = o[t];
     }
     // all sixteen epilogue warps meet here (named barrier 1; the issuer and producer warps do not take part)
     asm volatile("bar.sync 1, %0;" ::"n"(kEpiWarpsL * 32) : "memory");
-    if (half == 0 && epi_ok && ld_shared_i32_volatile(sm + kAbort) == 0) {
-      const int64_t row = (int64_t)row_tile * kRowsPerCtaL + rloc;
+    if (part == 0 && epi_ok && ld_shared_i32_volatile(sm + kAbort) == 0) {
+      const int64_t row = (int64_t)row_tile * kRowsCta + rloc;
       float* dst = p.raw + ((int64_t)chunk * p.r_pad + row) * p.tp + tchunk * TT;
 #pragma unroll
-      for (int t = 0; t < TT; ++t) dst[t] = o[t] + combine[rloc * TT + t];
+      for (int t = 0; t < TT; ++t) {
+        float acc = o[t];
+#pragma unroll
+        for (int g = 0; g < kParts - 1; ++g) acc += combine[(g * kRowsCta + rloc) * TT + t];
+        dst[t] = acc;
+      }
     }
   }
 
@@ -500,7 +580,7 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
   const bool aborted = (ld_shared_i32_volatile(sm + kAbort) != 0);
   if (aborted && warp == kProducerWarpL && lane == 0) {
     // give this CTA's own bulk copies a bounded chance to land before the shared memory is released
-    if (ARES) mbar_wait(sm + kAFull, 0);
+    if (MODE != kStream) mbar_wait(sm + kAFull, 0);
 #pragma unroll 1
     for (uint32_t bar = sm + kSFull; bar < sm + kSFull + 8 * S; bar += 8)
       if (!mbar_try_wait(bar, 0)) mbar_try_wait(bar, 1);
@@ -516,48 +596,58 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
   }
 }
 
-template <int KT, int TT, bool ARES>
-int launch_inst(const SweepArgsL& args, int n_chunks, int t_chunks, cudaStream_t stream) {
-  constexpr size_t smem = tck_smem_bytes<TT, ARES>();
-  static_assert(smem > 116 * 1024 && smem <= 227 * 1024, "one CTA per SM is assumed; shared memory budget");
+template <int KT, int TT, int MODE>
+int launch_inst(SweepArgsL args, int n_chunks, int t_chunks, cudaStream_t stream) {
+  using Map = SmemMapL<TT, MODE>;
+  args.ring = Map::ring_stages(args.nslab);
+  const size_t smem = Map::total_bytes(args.nslab);
+  // one CTA per SM is assumed (each takes all 512 TMEM columns): the shared memory must not let a second one in
+  if (smem <= 116 * 1024 || smem > (size_t)kMaxSmemL || args.ring < 3)
+    return fail(FLK_ERR_BAD_ARG, "internal: K-loop kernel shared-memory plan (%zu bytes, %d stages)", smem, args.ring);
   static bool configured[16] = {false};
   int dev = 0;
   FLK_CUDA_TRY(cudaGetDevice(&dev));
   if (dev >= 16 || !configured[dev]) {
-    FLK_CUDA_TRY(cudaFuncSetAttribute(kmv_tck_kernel<KT, TT, ARES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      (int)smem));
+    FLK_CUDA_TRY(cudaFuncSetAttribute(kmv_tck_kernel<KT, TT, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      kMaxSmemL));
     if (dev < 16) configured[dev] = true;
   }
   dim3 grid((unsigned)(args.row_tiles * n_chunks), (unsigned)t_chunks, 1);
-  kmv_tck_kernel<KT, TT, ARES><<<grid, kThreadsL, smem, stream>>>(args);
+  kmv_tck_kernel<KT, TT, MODE><<<grid, kThreadsL, smem, stream>>>(args);
   FLK_CUDA_TRY(cudaGetLastError());
   return FLK_OK;
 }
 
+template <int KT, int TT>
+int launch_mode(const SweepArgsL& args, int mode, int n_chunks, int t_chunks, cudaStream_t stream) {
+  if constexpr (TT != kWideTT) {
+    if (mode == kResident2) return launch_inst<KT, TT, kResident2>(args, n_chunks, t_chunks, stream);
+    if (mode == kResident1) return launch_inst<KT, TT, kResident1>(args, n_chunks, t_chunks, stream);
+  }
+  return launch_inst<KT, TT, kStream>(args, n_chunks, t_chunks, stream);
+}
+
 template <int KT>
-int launch_tt(const SweepArgsL& args, int tt, int n_chunks, int t_chunks, cudaStream_t stream) {
-  const bool ares = args.nslab <= kMaxResidentSlabs;
+int launch_tt(const SweepArgsL& args, int tt, int mode, int n_chunks, int t_chunks, cudaStream_t stream) {
   switch (tt) {
-    case 1: return ares ? launch_inst<KT, 1, true>(args, n_chunks, t_chunks, stream)
-                        : launch_inst<KT, 1, false>(args, n_chunks, t_chunks, stream);
-    case 2: return ares ? launch_inst<KT, 2, true>(args, n_chunks, t_chunks, stream)
-                        : launch_inst<KT, 2, false>(args, n_chunks, t_chunks, stream);
-    case 4: return ares ? launch_inst<KT, 4, true>(args, n_chunks, t_chunks, stream)
-                        : launch_inst<KT, 4, false>(args, n_chunks, t_chunks, stream);
-    case kWideTT:  // 16 KB vector tiles and 32 KB of partial sums leave no room for resident A blocks
-      return launch_inst<KT, kWideTT, false>(args, n_chunks, t_chunks, stream);
+    case 1: return launch_mode<KT, 1>(args, mode, n_chunks, t_chunks, stream);
+    case 2: return launch_mode<KT, 2>(args, mode, n_chunks, t_chunks, stream);
+    case 4: return launch_mode<KT, 4>(args, mode, n_chunks, t_chunks, stream);
+    case kWideTT: return launch_mode<KT, kWideTT>(args, mode, n_chunks, t_chunks, stream);
   }
   return fail(FLK_ERR_BAD_ARG, "internal: unsupported TT=%d", tt);
 }
 
+// `args.row_tiles`, `n_col_tiles` and `tiles_per_chunk` must have been planned for tile_mode(d, tt).
 inline int launch_sweep(int kernel, int d, SweepArgsL args, int tt, int n_chunks, int t_chunks, cudaStream_t stream) {
   args.nslab = n_slabs(d);
   args.ksteps = k_steps(d);
+  const int mode = tile_mode(d, tt);
   switch (kernel) {
-    case FLK_GAUSSIAN: return launch_tt<FLK_GAUSSIAN>(args, tt, n_chunks, t_chunks, stream);
-    case FLK_LAPLACIAN: return launch_tt<FLK_LAPLACIAN>(args, tt, n_chunks, t_chunks, stream);
-    case FLK_MATERN15: return launch_tt<FLK_MATERN15>(args, tt, n_chunks, t_chunks, stream);
-    case FLK_MATERN25: return launch_tt<FLK_MATERN25>(args, tt, n_chunks, t_chunks, stream);
+    case FLK_GAUSSIAN: return launch_tt<FLK_GAUSSIAN>(args, tt, mode, n_chunks, t_chunks, stream);
+    case FLK_LAPLACIAN: return launch_tt<FLK_LAPLACIAN>(args, tt, mode, n_chunks, t_chunks, stream);
+    case FLK_MATERN15: return launch_tt<FLK_MATERN15>(args, tt, mode, n_chunks, t_chunks, stream);
+    case FLK_MATERN25: return launch_tt<FLK_MATERN25>(args, tt, mode, n_chunks, t_chunks, stream);
   }
   return fail(FLK_ERR_BAD_ARG, "unknown kernel id %d", kernel);
 }

@@ -190,12 +190,13 @@ def test_register_report_parser_and_guard():
                 f"ptxas info    : Used {regs} registers, used 1 barriers, 16 bytes smem\n")
 
     tc = "_ZN3flk2tc13kmv_tc_kernelILi0ELi3ELi1ELb1EEEvNS0_9SweepArgsE"
-    tck = "_ZN3flk3tck14kmv_tck_kernelILi0ELi1ELb0EEEvNS0_10SweepArgsLE"
-    good = _lib.parse_ptxas(entry(tc, 0, 0, 0, 80) + entry(tck, 8, 8, 40, 96))
-    assert len(good) == 2 and _lib.check_ptxas(good) == []
+    tck = "_ZN3flk3tck14kmv_tck_kernelILi0ELi1ELi2EEEvNS0_10SweepArgsLE"
+    tck_wide = "_ZN3flk3tck14kmv_tck_kernelILi0ELi32ELi0EEEvNS0_10SweepArgsLE"
+    good = _lib.parse_ptxas(entry(tc, 0, 0, 0, 80) + entry(tck, 0, 0, 0, 96) + entry(tck_wide, 8, 8, 16, 96))
+    assert len(good) == 3 and _lib.check_ptxas(good) == []
     assert any("spill" in p for p in _lib.check_ptxas(_lib.parse_ptxas(entry(tc, 8, 4, 4, 80))))
     assert any("registers per thread" in p for p in _lib.check_ptxas(_lib.parse_ptxas(entry(tc, 0, 0, 0, 72))))
-    assert any("allowance" in p for p in _lib.check_ptxas(_lib.parse_ptxas(entry(tc, 0, 0, 0, 80) + entry(tck, 64, 80, 200, 96))))
+    assert any("allowance" in p for p in _lib.check_ptxas(_lib.parse_ptxas(entry(tc, 0, 0, 0, 80) + entry(tck_wide, 64, 80, 200, 96))))
     assert any("no tc::kmv_tc_kernel" in p for p in _lib.check_ptxas(_lib.parse_ptxas(entry(tck, 0, 0, 0, 96))))
     # the library on disk was built under the same guard: its report has no offending row
     import os
