@@ -141,6 +141,20 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// A warp that read a shared-memory buffer with ordinary loads hands it back to a bulk-copy producer, which will
+// overwrite it through the async proxy.  Two things must hold before the arrive that releases the buffer: the
+// loads have returned -- an arrive does not wait for loads in flight, and nothing else does when their consumers
+// were scheduled after it; `dep` must depend on the last of them (the running sums they feed), and the returned
+// zero is added to the barrier address, so the arrive cannot issue earlier -- and the generic and the async proxy are
+// ordered by a proxy fence.  Without this a vector tile was overwritten under the loads of the previous one
+// whenever the producer stood waiting for exactly that buffer (wrong sums in a few rows, varying from run to run).
+__device__ __forceinline__ uint32_t smem_reads_done(uint64_t dep) {
+  uint32_t lo, hi, zero;
+  asm volatile("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(dep));
+  asm volatile("and.b32 %0, %1, 0;" : "=r"(zero) : "r"(lo ^ hi));
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  return zero;
+}
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -1025,8 +1039,10 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
             epilogue_32<KT, TT>(ra, vsm + 64 * TT, osum);
             epilogue_32<KT, TT>(rc, vsm + 96 * TT, osum);
           }
+          // the vector tile goes back to the producer, whose bulk copy will overwrite it
+          const uint32_t zero = smem_reads_done(osum[0] ^ osum[NSUM - 1]);
           __syncwarp();
-          if (lane == 0) mbar_arrive(sm + M::V_EMPTY + 8 * (j % VS));
+          if (lane == 0) mbar_arrive(sm + M::V_EMPTY + 8 * (j % VS) + zero);
         }
       }
     }

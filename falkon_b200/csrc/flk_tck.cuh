@@ -2,33 +2,34 @@
 //
 //   raw[chunk][i][t] = sum_{j in chunk} k(a_i, b_j) vec[j][t]
 //
-// Same formulation as flk_tc.cuh -- split-fp16 operand images whose MMA accumulator is the exponent of the
-// kernel function, MUFU / FMA-pipe exponential epilogue, the contraction with `vec` fused -- but the K
-// dimension of the exponent GEMM (3 d + 6 fp16 elements) no longer fits shared memory for a resident row
-// block, so this kernel is an ordinary K-loop GEMM pipeline: a CTA owns 256 output rows (two 128-row MMA
-// blocks), walks the 128-column tiles of its chunk, and for every tile streams the operand images slab by slab
-// (32 fp16 = 64 bytes of K per row: 8 KB for each of the two A blocks and for the B tile) through a ring of
-// bulk copies; each slab feeds four tcgen05.mma (2 row blocks x 2 K-steps).  The two row blocks have two TMEM
-// accumulators each (512 columns in all), so the MMAs of tile j+1 run under the epilogue of tile j.  The
-// kernel is bound by the tensor pipe / the L2 traffic of the re-streamed operands (3 x the bytes of a plain
-// GEMM of the same shape, because every feature appears three times in the split), not by MUFU.
+// Same formulation as flk_tc.cuh -- split-fp16 operands whose MMA accumulator is the exponent of the kernel
+// function, MUFU / FMA-pipe exponential epilogue, the contraction with `vec` fused -- but the K dimension of the
+// exponent GEMM no longer fits shared memory for a resident row block of 512 rows, so this kernel is a K-loop GEMM
+// pipeline: a CTA owns one or two 128-row MMA blocks, walks the column tiles of its chunk, and for every tile streams
+// the reduction-side operand slab by slab (32 fp16 = 64 bytes of K per row, 8 KB per 128 rows) through a ring of
+// bulk copies.  Two TMEM accumulators per accumulator group (512 columns in all), so the MMAs of step j+1 run
+// under the epilogue of step j.
+//
+// Compact split.  With x = xh + xl, c = ch + cl in fp16, the exponent needs  xh.ch + xh.cl + xl.ch - |x|^2/2 - |c|^2/2.
+// Instead of laying the three products out along K (three copies of the features in each operand), an operand
+// image holds every part ONCE:
+//     [ hi parts: ds slabs | lo parts: ds slabs | tail slab ],   ds = ceil(d / 32),
+//     tail of an output-side image  = [-n1 -n2 -n3 | 1 1 1 | 0 ...],  of a reduction-side image = [1 1 1 | -m1 -m2 -m3 | 0 ...]
+// and the issuer pairs the slabs: for every feature slab three MMAs per K-step, (A hi, B hi), (A hi, B lo),
+// (A lo, B hi), plus one MMA on the tails.  That is the same number of MMAs (3 ceil(d / 16) + 1 per tile) on two
+// thirds of the operand bytes -- and what bounds a K-loop kernel here is operand delivery from L2 (a 128 x 128 x 16 MMA
+// takes 64 clocks; measured: about 55 B/clk per SM can be streamed while all SMs do the same).  Three shapes, by the
+// number of feature slabs (bytes per clock and SM that the bulk copies must sustain for the tensor pipe to stay busy):
+//   kResident2 (d <= 128): both 128-row blocks of the CTA stay in shared memory (2 x (2 ds + 1) slabs); a ring
+//       stage is the hi and the lo slab of one feature slab of a 128-column tile: 16 KB per twelve MMAs = 21 B/clk;
+//   kResident1 (d <= 192): ONE 128-row block stays resident and the CTA walks PAIRS of column tiles with
+//       128 x 256 x 16 MMAs from a single issuer: 32 KB per six such MMAs = 42 B/clk;
+//   kStream (more features, and the 32-column epilogue whose vector tiles and partial sums need the shared memory):
+//       a stage carries the hi and lo slabs of both row blocks and of the column tile: 48 KB per twelve MMAs = 62 B/clk.
 // Warps 0-15: epilogue (TMEM lane quarter = warp % 4, accumulator group = (warp / 4) % 2, 64-column half of the
 // group's 128 columns = warp / 8; the partial sums of a row are added at the end through shared memory); warps 16,
-// 17: MMA issuers, one per accumulator group (the barrier round trip between two slabs of one issuer runs under the
-// MMAs of the other; warp 16 owns the TMEM allocation); warp 18: bulk-copy producer.  Every wait is bounded as in
-// flk_tc.cuh.
-//
-// What bounds the kernel is operand delivery from L2: a 128 x 128 x 16 MMA takes 64 clocks, and every byte of both
-// operands of every MMA is read from shared memory, which the bulk copies must refill.  Three shapes, by the number
-// of slabs of an operand row (bytes per clock and SM that the copies must sustain for the tensor pipe to stay busy):
-//   kResident2 (up to 8 slabs, d <= 83): both 128-row blocks of the CTA stay in shared memory, a ring stage is one
-//       B slab of 128 columns: 8 KB per four MMAs = 32 B/clk;
-//   kResident1 (9..16 slabs, d <= 168): ONE 128-row block stays resident and the CTA walks PAIRS of column tiles
-//       (256 columns): the two accumulator groups are the two tiles of the pair, a ring stage is their two B slabs
-//       (16 KB per 256 clocks of MMA = 64 B/clk), and one issuer covers both groups with 128 x 256 x 16 MMAs, which
-//       read 12 KB of operands from shared memory per 128 clocks where two 128 x 128 x 16 read 16 KB -- the
-//       operand reads of the MMAs and the writes of the bulk copies share the shared memory's 128 B/clk;
-//   kStream (more slabs): nothing fits; two row blocks, a stage carries both A slabs and the B slab: 96 B/clk.
+// 17: MMA issuers, one per accumulator group (warp 16 alone in kResident1; it owns the TMEM allocation); warp 18:
+// bulk-copy producer.  Every wait is bounded as in flk_tc.cuh.
 #pragma once
 
 #include "flk_tc.cuh"
@@ -36,15 +37,13 @@
 namespace flk {
 namespace tck {
 
-using namespace tc;  // PTX wrappers, image layout, epilogue helpers
+using namespace tc;  // PTX wrappers, swizzle, epilogue helpers
 
-constexpr int kGroupsL = 2;                             // accumulator groups = MMA issuers
+constexpr int kGroupsL = 2;                             // accumulator groups
 constexpr int kMaxDL = 1024;
 constexpr int kSlabBytes = kTileRows * kSlabK * 2;      // 8 KB: one 128-row slab of an operand image
-constexpr int kStages = 8;
 constexpr int kMaxStagesL = 12;                         // barrier slots of the operand ring
-constexpr int kMaxResidentSlabs = 8;                    // kResident2: both A blocks stay in shared memory up to this many slabs
-constexpr int kMaxResidentSlabs1 = 16;                  // kResident1: one A block stays in shared memory up to this many slabs
+constexpr int kMinStagesL = 3;
 constexpr int kColSplitL = 2;                           // epilogue warps per (group, lane quarter): each takes 64 columns
 constexpr int kEpiWarpsL = 4 * kGroupsL * kColSplitL;
 constexpr int kMmaWarpL = kEpiWarpsL;                   // warps 16, 17: MMA issuer of group (warp - 16)
@@ -69,29 +68,57 @@ __host__ __device__ constexpr int cols_per_step(int mode) { return mode == kResi
 constexpr int kRowsPerCtaL = 2 * kTileRows;  // 256, the kStream / kResident2 shapes
 
 inline bool supports_d(int64_t d) { return d > tc::kMaxD && d <= kMaxDL; }
-inline int used_k(int64_t d) { return (int)(3 * d + 6); }  // always three norm pieces
-inline int k_steps(int64_t d) { return (int)(round_up(used_k(d), kMmaK) / kMmaK); }
-inline int64_t padded_k(int64_t d) { return round_up(used_k(d), kSlabK); }
-inline int n_slabs(int64_t d) { return (int)(padded_k(d) / kSlabK); }
-// tile shape for `d` features and `tt` vector columns per pass (the 32-column epilogue needs its shared memory for
-// vector tiles and partial sums: it streams)
+inline int feature_slabs(int64_t d) { return (int)((d + kSlabK - 1) / kSlabK); }   // ds
+inline int n_slabs(int64_t d) { return 2 * feature_slabs(d) + 1; }                 // hi | lo | tail
+inline int64_t padded_k(int64_t d) { return (int64_t)n_slabs(d) * kSlabK; }        // fp16 elements per image row
+inline int last_k_steps(int64_t d) { return (int)((d - (int64_t)(feature_slabs(d) - 1) * kSlabK + kMmaK - 1) / kMmaK); }
+
+// ---- shared-memory plan (host and device agree through these functions) ----
+// fixed part: barrier block (512 B) | partial sums of the other column groups | vector ring, rounded to 1 KB
+__host__ __device__ constexpr int vec_stages(int tt) { return tt == kWideTT ? 2 : kVecStages; }
+__host__ __device__ constexpr uint32_t vec_tile_bytes(int tt, int mode) { return (uint32_t)(cols_per_step(mode) * tt * 4); }
+__host__ __device__ constexpr uint32_t combine_bytes(int tt, int mode) {
+  // kResident1: three of the four column groups of a row hand their sums over; otherwise one of two
+  return (uint32_t)((mode == kResident1 ? 3 * kTileRows : kRowsPerCtaL) * tt * 4);
+}
+__host__ __device__ constexpr uint32_t fixed_bytes(int tt, int mode) {
+  return (512u + combine_bytes(tt, mode) + (uint32_t)vec_stages(tt) * vec_tile_bytes(tt, mode) + 1023u) & ~1023u;
+}
+// a ring stage: [hi | lo] slabs of the column tile (kResident2), of both tiles of the pair (kResident1: hi, hi, lo,
+// lo), or of both row blocks and the column tile (kStream: A0 hi, A0 lo, A1 hi, A1 lo, B hi, B lo)
+__host__ __device__ constexpr uint32_t stage_bytes(int mode) {
+  return (uint32_t)((mode == kStream ? 6 : (mode == kResident1 ? 4 : 2)) * kSlabBytes);
+}
+__host__ __device__ constexpr uint32_t resident_bytes(int mode, int nslab) {
+  return (uint32_t)((mode == kResident2 ? 2 : (mode == kResident1 ? 1 : 0)) * nslab * kSlabBytes);
+}
+__host__ __device__ constexpr int ring_stages(int tt, int mode, int nslab) {
+  const int room = (kMaxSmemL - 1024 - (int)fixed_bytes(tt, mode) - (int)resident_bytes(mode, nslab)) / (int)stage_bytes(mode);
+  return room < kMaxStagesL ? room : kMaxStagesL;
+}
+inline size_t smem_bytes(int tt, int mode, int nslab) {
+  return 1024 + (size_t)fixed_bytes(tt, mode) + resident_bytes(mode, nslab) +
+         (size_t)ring_stages(tt, mode, nslab) * stage_bytes(mode);
+}
+// tile shape for `d` features and `tt` vector columns per pass: the most resident shape whose ring still has four
+// stages (three for the streaming shape)
 inline int tile_mode(int64_t d, int tt) {
   if (tt == tc::kWideTT) return kStream;
   const int ns = n_slabs(d);
-  return ns <= kMaxResidentSlabs ? kResident2 : (ns <= kMaxResidentSlabs1 ? kResident1 : kStream);
+  if (ring_stages(tt, kResident2, ns) >= 4) return kResident2;
+  if (ring_stages(tt, kResident1, ns) >= 3) return kResident1;
+  return kStream;
 }
 
 // ---------------------------------------------------------------------------------------------
 // Operand images for any feature count: one block = one 128-row tile, one thread = one row.  The image is
-// built slab by slab in shared memory (so that the global writes are coalesced 8 KB runs); the row's
-// features are re-read from X for each of the three copies the split needs (they stay in L1 / L2).
-// K layout of a row, as in flk_tc.cuh:  A = [xh | xh | xl | -n1 -n2 -n3 | 1 1 1 | 0..],
-//                                       B = [ch | cl | ch | 1 1 1 | -m1 -m2 -m3 | 0..].
+// built slab by slab in shared memory (so that the global writes are coalesced 8 KB runs).  Layout of a row:
+// see the head of this file; the two images of an operand differ in the tail slab only.
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(128) prep_images_large_kernel(const float* __restrict__ X, int64_t n, int64_t rs,
                                                                 int64_t cs, int d, const float* __restrict__ sigma,
                                                                 float sigma_scalar, int sigma_len, float scale,
-                                                                int nslab, __half* __restrict__ img_a,
+                                                                int ds, __half* __restrict__ img_a,
                                                                 __half* __restrict__ img_b, int* __restrict__ range_word) {
   __shared__ __align__(16) __half slab[2][kTileRows * kSlabK];  // A and B version of the current slab
   const int r = threadIdx.x;
@@ -135,26 +162,26 @@ __global__ void __launch_bounds__(128) prep_images_large_kernel(const float* __r
     }
   }
   const __half one = __float2half_rn(1.0f), zero = __float2half_rn(0.0f);
+  const int nslab = 2 * ds + 1;
   // pass 2: slabs
   for (int s = 0; s < nslab; ++s) {
     for (int e = 0; e < kSlabK; ++e) {
-      const int k = s * kSlabK + e;  // K index
       __half va = zero, vb = zero;
       if (live) {
-        if (k < 3 * d) {
-          const int region = k / d, f = k - region * d;
-          float xt = scaled(f);
-          if (!(fabsf(xt) <= 400.0f)) xt = 0.0f;
-          const __half hi = __float2half_rn(xt);
-          const __half lo = __float2half_rn(xt - __half2float(hi));
-          va = region == 2 ? lo : hi;   // A: hi, hi, lo
-          vb = region == 1 ? lo : hi;   // B: hi, lo, hi
-        } else if (k < 3 * d + 3) {
-          va = __float2half_rn(-piece[k - 3 * d]);
+        if (s < 2 * ds) {
+          const int f = (s < ds ? s : s - ds) * kSlabK + e;
+          if (f < d) {
+            float xt = scaled(f);
+            if (!(fabsf(xt) <= 400.0f)) xt = 0.0f;
+            const __half hi = __float2half_rn(xt);
+            va = vb = s < ds ? hi : __float2half_rn(xt - __half2float(hi));
+          }
+        } else if (e < 3) {
+          va = __float2half_rn(-piece[e]);
           vb = one;
-        } else if (k < 3 * d + 6) {
+        } else if (e < 6) {
           va = one;
-          vb = __float2half_rn(-piece[k - 3 * d - 3]);
+          vb = __float2half_rn(-piece[e - 3]);
         }
       }
       const int off = r * kSlabK + ((((e >> 3) ^ ((r >> 1) & 3))) << 3) + (e & 7);
@@ -180,7 +207,7 @@ inline int prep_images_large(int kernel, const void* X, int64_t n, int64_t rs, i
   const float scale = (float)sqrt(scale_sq_for(kernel));
   const int blocks = (int)(rows_pad / kTileRows);
   prep_images_large_kernel<<<blocks, 128, 0, stream>>>(reinterpret_cast<const float*>(X), n, rs, cs, d, sigma_dev,
-                                                       sigma_scalar, sigma_len, scale, n_slabs(d),
+                                                       sigma_scalar, sigma_len, scale, feature_slabs(d),
                                                        reinterpret_cast<__half*>(img_a),
                                                        reinterpret_cast<__half*>(img_b), range_word);
   FLK_CUDA_TRY(cudaGetLastError());
@@ -202,76 +229,43 @@ struct SweepArgsL {
   int row_tiles;        // ceil(r / rows of a CTA)
   int n_col_tiles;      // steps of the tile loop over the whole reduction side: ceil(s / columns per step)
   int tiles_per_chunk;  // in the same unit
-  int nslab;            // K slabs per operand tile
-  int ksteps;           // MMA K-steps carrying data (two per slab, possibly one in the last slab)
-  int ring;             // stages of the operand ring (kResident1: as many as the shared memory left by A holds)
-};
-
-// With 32 vector columns per pass the vector tiles are 16 KB each: two of them and a six-stage operand ring.
-template <int TT>
-struct RingCfg {
-  static constexpr int S = TT == kWideTT ? 6 : kStages;
-  static constexpr int VS = TT == kWideTT ? 2 : kVecStages;
-};
-
-// Shared-memory map, as offsets from a 1024-byte aligned base: barrier block (512 B) | partial sums of the other
-// column groups | vector ring | [resident A slabs] | operand ring.  The first three have fixed sizes.
-template <int TT, int MODE>
-struct SmemMapL {
-  static constexpr int VS = RingCfg<TT>::VS;
-  static constexpr uint32_t kVecTileBytes = cols_per_step(MODE) * TT * 4;
-  // kResident1: three of the four column groups of a row hand their sums over; otherwise one of two
-  static constexpr uint32_t kCombineBytes = (MODE == kResident1 ? 3 * kTileRows : kRowsPerCtaL) * TT * 4;
-  static constexpr uint32_t kCombineOff = 512;
-  static constexpr uint32_t kVecOff = kCombineOff + kCombineBytes;
-  static constexpr uint32_t kFixedBytes = (kVecOff + VS * kVecTileBytes + 1023u) & ~1023u;
-  static constexpr uint32_t kStageBytes = (MODE == kStream ? 3 : (MODE == kResident1 ? 2 : 1)) * kSlabBytes;
-  // barrier block: s_full[12] | s_empty[12] | v_full[VS] | v_empty[VS] | t_full[4] | t_empty[4] (index
-  // group * 2 + buf) | a_full | tmem pointer | abort flag
-  static constexpr uint32_t kSFull = 0, kSEmpty = kSFull + 8 * kMaxStagesL, kVFull = kSEmpty + 8 * kMaxStagesL;
-  static constexpr uint32_t kVEmpty = kVFull + 8 * VS, kTFull = kVEmpty + 8 * VS, kTEmpty = kTFull + 32;
-  static constexpr uint32_t kAFull = kTEmpty + 32, kTmemPtr = kAFull + 8, kAbort = kTmemPtr + 4;
-  static_assert(kAbort + 4 <= kCombineOff, "barrier block overflows its 512 bytes");
-  static __host__ __device__ constexpr uint32_t resident_bytes(int nslab) {
-    return MODE == kResident2 ? 2u * kMaxResidentSlabs * kSlabBytes : (MODE == kResident1 ? (uint32_t)nslab * kSlabBytes : 0u);
-  }
-  // stages of the operand ring for `nslab` slabs per row
-  static int ring_stages(int nslab) {
-    if (MODE != kResident1) return RingCfg<TT>::S;
-    const int room = (kMaxSmemL - 1024 - (int)kFixedBytes - (int)resident_bytes(nslab)) / (int)kStageBytes;
-    return room < kMaxStagesL ? room : kMaxStagesL;
-  }
-  static size_t total_bytes(int nslab) {
-    return 1024 + (size_t)kFixedBytes + resident_bytes(nslab) + (size_t)ring_stages(nslab) * kStageBytes;
-  }
+  int ds;               // feature slabs; an image row has 2 ds + 1 slabs
+  int last_ksteps;      // K-steps of the last feature slab that carry data (1 or 2)
+  int ring;             // stages of the operand ring
 };
 
 __device__ __forceinline__ void report_timeout(int* status, int code) { atomicExch(status + kStatusTimeout, code); }
 
 template <int KT, int TT, int MODE>
 __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL p) {
-  using Map = SmemMapL<TT, MODE>;
-  constexpr int VS = Map::VS;
-  constexpr uint32_t kStageBytes = Map::kStageBytes, kVecTileBytes = Map::kVecTileBytes;
+  constexpr int VS = vec_stages(TT);
+  constexpr uint32_t kStageBytes = stage_bytes(MODE), kVecTileBytes = vec_tile_bytes(TT, MODE);
   constexpr int kRowsCta = rows_per_cta(MODE);
+  constexpr int kStepCols = cols_per_step(MODE);
+  constexpr int kABlocks = kRowsCta / kTileRows;
+  constexpr int kBTiles = kStepCols / kColsPerTile;
   // kResident1: the two accumulator groups are neighbouring column tiles of one A block, so ONE issuer covers both
-  // with 256-column MMAs (12 KB of operand reads from shared memory per 128 clocks instead of 16 KB)
+  // with 256-column MMAs
   constexpr bool kOneMma = MODE == kResident1;
   constexpr int kIssuers = kOneMma ? 1 : kGroupsL;
-  constexpr int kStepCols = cols_per_step(MODE);
-  constexpr uint32_t kSFull = Map::kSFull, kSEmpty = Map::kSEmpty, kVFull = Map::kVFull, kVEmpty = Map::kVEmpty;
-  constexpr uint32_t kTFull = Map::kTFull, kTEmpty = Map::kTEmpty, kAFull = Map::kAFull, kTmemPtr = Map::kTmemPtr;
-  constexpr uint32_t kAbort = Map::kAbort;
+  // barrier block: s_full[12] | s_empty[12] | v_full[VS] | v_empty[VS] | t_full[4] | t_empty[4] | a_full | tmem
+  // pointer | abort flag;  then the partial sums and the vector ring (fixed sizes), the resident A slabs, the ring
+  constexpr uint32_t kSFull = 0, kSEmpty = kSFull + 8 * kMaxStagesL, kVFull = kSEmpty + 8 * kMaxStagesL;
+  constexpr uint32_t kVEmpty = kVFull + 8 * VS, kTFull = kVEmpty + 8 * VS, kTEmpty = kTFull + 32;
+  constexpr uint32_t kAFull = kTEmpty + 32, kTmemPtr = kAFull + 8, kAbort = kTmemPtr + 4;
+  constexpr uint32_t kCombineOff = 512, kVecOff = kCombineOff + combine_bytes(TT, MODE);
+  static_assert(kAbort + 4 <= kCombineOff, "barrier block overflows its 512 bytes");
   extern __shared__ unsigned char tck_smem_raw[];
   const uint32_t raw_addr = smem_u32(tck_smem_raw);
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
   // 32-bit shared addresses from one base (generic pointers to every ring and barrier would stay live across all
   // warp roles)
   const uint32_t sm = raw_addr + pad;
-  const int nslab = p.nslab;
-  const uint32_t S = MODE == kResident1 ? (uint32_t)p.ring : (uint32_t)RingCfg<TT>::S;
-  const uint32_t sm_a = sm + Map::kFixedBytes;                  // resident A slabs (if any)
-  const uint32_t sm_ring = sm_a + Map::resident_bytes(nslab);   // operand ring
+  const int ds = p.ds;
+  const int nslab = 2 * ds + 1;
+  const uint32_t S = (uint32_t)p.ring;
+  const uint32_t sm_a = sm + fixed_bytes(TT, MODE);            // resident A slabs (if any)
+  const uint32_t sm_ring = sm_a + resident_bytes(MODE, nslab);  // operand ring
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
@@ -323,18 +317,18 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
   } else if (warp == kProducerWarpL) {
     // ------------------------------ bulk-copy producer ------------------------------
     reg_release<kRegsOthersL>();
-    constexpr int kABlocks = kRowsCta / kTileRows;
-    const __half* a_base = p.img_a + (int64_t)row_tile * kABlocks * nslab * (kTileRows * kSlabK);
+    constexpr int64_t kSlabElems = kTileRows * kSlabK;
+    const __half* a_base = p.img_a + (int64_t)row_tile * kABlocks * nslab * kSlabElems;
     const float* vec_base = p.vec + (int64_t)tchunk * p.s_pad * TT;
     if (MODE != kStream && elect_one()) {
       // the CTA's A blocks are contiguous in the image: [row block][slab]
       const uint32_t bytes = (uint32_t)(kABlocks * nslab * kSlabBytes);
       mbar_expect_tx(sm + kAFull, bytes);
       for (int i = 0; i < kABlocks * nslab; ++i)
-        bulk_copy_g2s(sm_a + i * kSlabBytes, a_base + (int64_t)i * (kTileRows * kSlabK), kSlabBytes, sm + kAFull);
+        bulk_copy_g2s(sm_a + i * kSlabBytes, a_base + (int64_t)i * kSlabElems, kSlabBytes, sm + kAFull);
     }
     __syncwarp();
-    uint32_t stage = 0, wrap = 0;  // ring position of the running slab counter and its wrap parity
+    uint32_t stage = 0, wrap = 0;  // ring position of the running stage counter and its wrap parity
     bool ok = true;
     for (int j = 0; ok && j < ntiles; ++j) {
       const int64_t ct = tile_begin + j;
@@ -347,12 +341,12 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
       if (elect_one()) {
         const uint32_t vbar = sm + kVFull + 8 * vstage;
         mbar_expect_tx(vbar, kVecTileBytes);
-        bulk_copy_g2s(sm + Map::kVecOff + vstage * kVecTileBytes, vec_base + ct * kStepCols * TT, kVecTileBytes, vbar);
+        bulk_copy_g2s(sm + kVecOff + vstage * kVecTileBytes, vec_base + ct * kStepCols * TT, kVecTileBytes, vbar);
       }
       __syncwarp();
       // first B tile of this step; kResident1 takes the following tile too (the image is padded to four tiles)
-      const __half* b_base = p.img_b + ct * (kStepCols / kColsPerTile) * nslab * (kTileRows * kSlabK);
-      for (int s = 0; s < nslab; ++s) {
+      const __half* b_base = p.img_b + ct * kBTiles * nslab * kSlabElems;
+      for (int st = 0; st <= ds; ++st) {  // ds feature slabs, then the tail
         if (ld_shared_i32_volatile(sm + kAbort)) { ok = false; break; }
         if (!mbar_wait(sm + kSEmpty + 8 * stage, wrap ^ 1u)) {
           if (lane == 0) report_timeout(p.status, kErrProducer | 1);
@@ -363,15 +357,29 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
         if (elect_one()) {
           const uint32_t bar = sm + kSFull + 8 * stage;
           const uint32_t dst = sm_ring + stage * kStageBytes;
-          mbar_expect_tx(bar, kStageBytes);
+          const bool tail = st == ds;
+          // slab index of the hi part (or of the tail) and distance to the lo part within an image tile
+          const int64_t s_hi = tail ? 2 * ds : st;
+          mbar_expect_tx(bar, tail ? kStageBytes / 2 : kStageBytes);
           if (MODE == kStream) {
-            bulk_copy_g2s(dst, a_base + (int64_t)s * (kTileRows * kSlabK), kSlabBytes, bar);
-            bulk_copy_g2s(dst + kSlabBytes, a_base + ((int64_t)nslab + s) * (kTileRows * kSlabK), kSlabBytes, bar);
-            bulk_copy_g2s(dst + 2 * kSlabBytes, b_base + (int64_t)s * (kTileRows * kSlabK), kSlabBytes, bar);
+            // [A0 hi | A0 lo | A1 hi | A1 lo | B hi | B lo]; the tails take the hi positions
+#pragma unroll
+            for (int rb = 0; rb < 2; ++rb) {
+              const __half* a_tile = a_base + (int64_t)rb * nslab * kSlabElems;
+              bulk_copy_g2s(dst + rb * 2 * kSlabBytes, a_tile + s_hi * kSlabElems, kSlabBytes, bar);
+              if (!tail) bulk_copy_g2s(dst + (rb * 2 + 1) * kSlabBytes, a_tile + (s_hi + ds) * kSlabElems, kSlabBytes, bar);
+            }
+            bulk_copy_g2s(dst + 4 * kSlabBytes, b_base + s_hi * kSlabElems, kSlabBytes, bar);
+            if (!tail) bulk_copy_g2s(dst + 5 * kSlabBytes, b_base + (s_hi + ds) * kSlabElems, kSlabBytes, bar);
           } else {
-            bulk_copy_g2s(dst, b_base + (int64_t)s * (kTileRows * kSlabK), kSlabBytes, bar);
-            if (MODE == kResident1)
-              bulk_copy_g2s(dst + kSlabBytes, b_base + ((int64_t)nslab + s) * (kTileRows * kSlabK), kSlabBytes, bar);
+            // [hi of the step's kBTiles tiles | lo of the same tiles]
+#pragma unroll
+            for (int t = 0; t < kBTiles; ++t) {
+              const __half* b_tile = b_base + (int64_t)t * nslab * kSlabElems;
+              bulk_copy_g2s(dst + t * kSlabBytes, b_tile + s_hi * kSlabElems, kSlabBytes, bar);
+              if (!tail)
+                bulk_copy_g2s(dst + (kBTiles + t) * kSlabBytes, b_tile + (s_hi + ds) * kSlabElems, kSlabBytes, bar);
+            }
           }
         }
         __syncwarp();
@@ -393,6 +401,7 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
       st_shared_i32_volatile(sm + kAbort, 1);
       ok = false;
     }
+    constexpr uint32_t kIdesc = kOneMma ? kInstrDescN256 : kInstrDesc;
     for (int j = 0; ok && j < ntiles; ++j) {
       const int buf = j & 1;
       if (ld_shared_i32_volatile(sm + kAbort)) break;
@@ -404,7 +413,7 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
         break;
       }
       const uint32_t d_tmem = tmem_base + (uint32_t)(acc * (kOneMma ? 2 : 1) * kColsPerTile);
-      for (int s = 0; s < nslab; ++s) {
+      for (int st = 0; st <= ds; ++st) {
         if (!mbar_wait(sm + kSFull + 8 * stage, wrap)) {
           if (lane == 0) report_timeout(p.status, kErrMma | 2);
           st_shared_i32_volatile(sm + kAbort, 1);
@@ -414,24 +423,36 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
         tc_fence_after();
         if (elect_one()) {
           const uint32_t sbase = sm_ring + stage * kStageBytes;
-          uint32_t a_addr, b_addr;
+          const bool tail = st == ds;
+          // hi slab (or tail) of this group's A block and of the step's B columns; the lo slabs follow at fixed distances
+          uint32_t a_hi, a_lo, b_hi, b_lo;
           if (MODE == kStream) {
-            a_addr = sbase + grp * kSlabBytes;
-            b_addr = sbase + 2 * kSlabBytes;
-          } else if (MODE == kResident2) {
-            a_addr = sm_a + (grp * nslab + s) * kSlabBytes;
-            b_addr = sbase;
+            a_hi = sbase + grp * 2 * kSlabBytes;
+            a_lo = a_hi + kSlabBytes;
+            b_hi = sbase + 4 * kSlabBytes;
+            b_lo = b_hi + kSlabBytes;
           } else {
-            a_addr = sm_a + s * kSlabBytes;
-            b_addr = sbase;  // both B slabs of the stage: 256 rows of 64 bytes, contiguous
+            const uint32_t a_blk = sm_a + (MODE == kResident2 ? grp * nslab : 0) * kSlabBytes;
+            a_hi = a_blk + (tail ? 2 * ds : st) * kSlabBytes;
+            a_lo = a_hi + ds * kSlabBytes;
+            b_hi = sbase;
+            b_lo = sbase + kBTiles * kSlabBytes;
           }
-          const uint64_t a_desc = make_smem_desc(a_addr), b_desc = make_smem_desc(b_addr);
-          const int nks = min(2, p.ksteps - 2 * s);  // K-steps of this slab that carry data
-          for (int ks = 0; ks < nks; ++ks)
-            mma_f16(d_tmem, a_desc + (uint64_t)(ks * 2), b_desc + (uint64_t)(ks * 2),
-                    kOneMma ? kInstrDescN256 : kInstrDesc, (s > 0 || ks > 0) ? 1u : 0u);
+          const uint64_t ah = make_smem_desc(a_hi), bh = make_smem_desc(b_hi);
+          if (tail) {
+            mma_f16(d_tmem, ah, bh, kIdesc, 1u);
+          } else {
+            const uint64_t al = make_smem_desc(a_lo), bl = make_smem_desc(b_lo);
+            const int nks = st == ds - 1 ? p.last_ksteps : 2;  // K-steps of this slab that carry data
+            for (int ks = 0; ks < nks; ++ks) {
+              const uint64_t ko = (uint64_t)(ks * 2);  // 32 bytes per K-step inside the 64-byte swizzle row
+              mma_f16(d_tmem, ah + ko, bh + ko, kIdesc, (st > 0 || ks > 0) ? 1u : 0u);
+              mma_f16(d_tmem, ah + ko, bl + ko, kIdesc, 1u);
+              mma_f16(d_tmem, al + ko, bh + ko, kIdesc, 1u);
+            }
+          }
           mma_commit(sm + kSEmpty + 8 * stage);
-          if (s == nslab - 1) mma_commit(sm + kTFull + 8 * acc);
+          if (tail) mma_commit(sm + kTFull + 8 * acc);
         }
         __syncwarp();
         if (++stage == S) {
@@ -486,7 +507,7 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
                              (uint32_t)((kOneMma ? buf * 2 + grp : grp * 2 + buf) * kColsPerTile + half * 64);
       // generic pointer rebuilt from the 32-bit shared address, so that no 64-bit base stays live across the loop
       const float* vsm = reinterpret_cast<const float*>(
-          __cvta_shared_to_generic(sm + Map::kVecOff + vstage * kVecTileBytes + (uint32_t)(vcol * TT * 4)));
+          __cvta_shared_to_generic(sm + kVecOff + vstage * kVecTileBytes + (uint32_t)(vcol * TT * 4)));
       if constexpr (TT == kWideTT) {
         // 32 running sums per thread leave room for 16 columns at a time: four pieces; the accumulator goes back
         // to its issuer once the last one is in registers
@@ -520,8 +541,10 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
         if (lane == 0) mbar_arrive(sm + kTEmpty + 8 * acc);
         epilogue_32<KT, TT>(ra, vsm + 32 * TT, osum);
       }
+      // the vector tile goes back to the producer, whose bulk copy will overwrite it
+      const uint32_t zero = smem_reads_done(osum[0] ^ osum[NSUM - 1]);
       __syncwarp();
-      if (lane == 0) mbar_arrive(sm + kVEmpty + 8 * vstage);
+      if (lane == 0) mbar_arrive(sm + kVEmpty + 8 * vstage + zero);
     }
     }
     // per-thread sums of this warp's columns
@@ -554,7 +577,7 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
     constexpr int kParts = MODE == kResident1 ? 4 : 2;
     const int part = MODE == kResident1 ? grp * 2 + half : half;
     const int rloc = (MODE == kResident1 ? 0 : grp * kTileRows) + q * 32 + lane;
-    float* combine = reinterpret_cast<float*>(__cvta_shared_to_generic(sm + Map::kCombineOff));  // [kParts - 1][rows of the CTA][TT]
+    float* combine = reinterpret_cast<float*>(__cvta_shared_to_generic(sm + kCombineOff));  // [kParts - 1][rows of the CTA][TT]
     if (part > 0) {
 #pragma unroll
       for (int t = 0; t < TT; ++t) combine[((part - 1) * kRowsCta + rloc) * TT + t] = o[t];
@@ -598,11 +621,11 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
 
 template <int KT, int TT, int MODE>
 int launch_inst(SweepArgsL args, int n_chunks, int t_chunks, cudaStream_t stream) {
-  using Map = SmemMapL<TT, MODE>;
-  args.ring = Map::ring_stages(args.nslab);
-  const size_t smem = Map::total_bytes(args.nslab);
+  const int nslab = 2 * args.ds + 1;
+  args.ring = ring_stages(TT, MODE, nslab);
+  const size_t smem = smem_bytes(TT, MODE, nslab);
   // one CTA per SM is assumed (each takes all 512 TMEM columns): the shared memory must not let a second one in
-  if (smem <= 116 * 1024 || smem > (size_t)kMaxSmemL || args.ring < 3)
+  if (smem <= 116 * 1024 || smem > (size_t)kMaxSmemL || args.ring < kMinStagesL)
     return fail(FLK_ERR_BAD_ARG, "internal: K-loop kernel shared-memory plan (%zu bytes, %d stages)", smem, args.ring);
   static bool configured[16] = {false};
   int dev = 0;
@@ -640,8 +663,8 @@ int launch_tt(const SweepArgsL& args, int tt, int mode, int n_chunks, int t_chun
 
 // `args.row_tiles`, `n_col_tiles` and `tiles_per_chunk` must have been planned for tile_mode(d, tt).
 inline int launch_sweep(int kernel, int d, SweepArgsL args, int tt, int n_chunks, int t_chunks, cudaStream_t stream) {
-  args.nslab = n_slabs(d);
-  args.ksteps = k_steps(d);
+  args.ds = feature_slabs(d);
+  args.last_ksteps = last_k_steps(d);
   const int mode = tile_mode(d, tt);
   switch (kernel) {
     case FLK_GAUSSIAN: return launch_tt<FLK_GAUSSIAN>(args, tt, mode, n_chunks, t_chunks, stream);

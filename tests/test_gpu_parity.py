@@ -218,6 +218,27 @@ def test_long_reductions_keep_fp32_accuracy(d):
     assert big < (1e-6 if d <= 30 else 1e-4), errs
 
 
+@pytest.mark.parametrize("d,t", [(48, 1), (64, 1), (64, 2), (20, 2), (96, 1)])
+def test_vector_tiles_are_not_overwritten_under_their_readers(d, t):
+    """Few output rows, a long reduction, few features: the epilogue is the slow side, the bulk-copy producer runs
+    ahead until it waits for the very vector tile the epilogue is reading, and refills it the moment it is
+    released.  The release has to wait for the loads of that tile (a data dependency on the sums they feed plus a
+    proxy fence before the arrive); without it the results were wrong in a few rows and changed from run to run."""
+    from falkon_b200.kernels import GaussianKernel
+
+    g = torch.Generator(device="cuda").manual_seed(5)
+    X1 = torch.randn(1024, d, generator=g, device="cuda")
+    X2 = torch.randn(65_536, d, generator=g, device="cuda")
+    v = torch.randn(65_536, t, generator=g, device="cuda")
+    k = GaussianKernel(float(d) ** 0.5)
+    want = k.mmv(X1.double(), X2.double(), v.double()).cpu().numpy()
+    outs = [k.mmv(X1, X2, v).cpu().numpy() for _ in range(4)]
+    for got in outs:
+        assert fo.rel_l2(got, want) < 2e-5
+    for got in outs[1:]:
+        assert np.array_equal(got, outs[0])  # and bitwise the same every time
+
+
 def test_duplicate_points_clamp():
     """Centres that are exact copies of data rows (distance 0): the clamp keeps sqrt() finite and
     the diagonal entries equal to 1 (falkon/kernels/distance_kernel.py:100)."""
