@@ -441,6 +441,19 @@ def run_config(args):
             line["roofline"] = {"bound": "mufu", "achieved": evals / 1e9, "peak": mufu / 1e9, "unit": "Gexp/s",
                                 "frac": evals / mufu, "note": "per GPU (rank 0), sweep launches only; peak = ex2 "
                                 "rate measured live by the probe kernel"}
+        if dtype == torch.float32 and 30 < d <= 1024:
+            # K-loop tensor-core kernel: bound by the tensor pipe.  fp16 MMA flops the kernel issues per evaluation:
+            # three 16-feature products per feature K-step (hi.hi, hi.lo, lo.hi) plus the K-step of the norm pieces
+            peaks = load_peaks()
+            flops_per_eval = 2.0 * 16.0 * (3 * ((d + 15) // 16) + 1)
+            evals = float(n) * m / (0.5 * (sweeps[0] + sweeps[1]) * 1e-3)
+            line["roofline"] = {"bound": "tensor", "achieved": evals * flops_per_eval / 1e12,
+                                "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                                "frac": evals * flops_per_eval / 1e12 / peaks["bf16_tflops"],
+                                "frac_of_sustained_peak": evals * flops_per_eval / 1e12 / (peaks["bf16_sustained"] or peaks["bf16_tflops"]),
+                                "peak_source": peaks["source"], "flops_per_eval": flops_per_eval,
+                                "note": "per GPU (rank 0), sweep launches only; fp16 MMA flops issued against the "
+                                        "measured bf16 GEMM peaks (burst / seconds-long under the power cap)"}
         if dtype == torch.float64:
             dfma_per_pair = d + (t if t > 4 else 4 + t) + 4
             peak = 148 * 64 * sm_mhz * 1e6
