@@ -748,8 +748,9 @@ struct SmemMap {
   static constexpr uint32_t T_EMPTY = T_FULL + 8 * kRowBlocks;
   static constexpr uint32_t TMEM_PTR = T_EMPTY + 8 * kRowBlocks;
   static constexpr uint32_t ABORT = TMEM_PTR + 4;
+  static constexpr uint32_t FOLD_NPOS = ABORT + 4;  // folded sweep: positive tiles of this CTA's chunk
   static constexpr uint32_t SUMS = BARS + 512;
-  static_assert(ABORT + 4 <= SUMS, "barrier block overflows its 512 bytes");
+  static_assert(FOLD_NPOS + 4 <= SUMS, "barrier block overflows its 512 bytes");
 };
 
 __device__ __forceinline__ int ld_shared_i32_volatile(uint32_t addr) {
@@ -759,6 +760,16 @@ __device__ __forceinline__ int ld_shared_i32_volatile(uint32_t addr) {
 }
 __device__ __forceinline__ void st_shared_i32_volatile(uint32_t addr, int v) {
   asm volatile("st.volatile.shared.b32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+
+// Order in which a folded sweep visits the positive and the negative tiles of its chunk: evenly interleaved.
+// Every role of the CTA steps through the same sequence: step j is a positive tile when the running count
+// acc += npos passes `total` (npos of total steps are).
+__device__ __forceinline__ bool fold_step_is_positive(int& acc, int npos, int total) {
+  acc += npos;
+  const bool pos = acc >= total;
+  if (pos) acc -= total;
+  return pos;
 }
 
 // Epilogue warp w: TMEM lane quarter q = w % 4 (hardware rule: a warp may only touch lanes
@@ -792,8 +803,23 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
     tiles_per_chunk = p.tiles_per_chunk_tail;
   }
   const int tchunk = blockIdx.y;
-  const int tile_begin = chunk * tiles_per_chunk;
-  const int ntiles = min(tile_begin + tiles_per_chunk, p.n_col_tiles) - tile_begin;
+  // Tiles of this CTA's chunk.  Ordinary sweep: tile_begin .. tile_begin + ntiles.  Folded sweep: the image holds
+  // the tiles of non-negative vector entries first and those of negative entries from tile [kFoldNegTile] on; a
+  // chunk takes an equal share of BOTH ranges and walks them interleaved (fold_step_is_positive), so that the running sums of
+  // a thread stay balanced -- summing one sign after the other let them grow to the size of the whole one-sided
+  // sum and cost up to 1e-4 of relative accuracy on strongly cancelling sums over 1e5 and more rows.
+  int tile_begin = chunk * tiles_per_chunk;
+  int ntiles = min(tile_begin + tiles_per_chunk, p.n_col_tiles) - tile_begin;
+  int fold_neg0 = 0, fold_npos = 0;  // first negative tile of this chunk, positive tiles in it (tile_begin = its first positive tile)
+  if constexpr (FOLD) {
+    const int n_chunks = (p.n_col_tiles + tiles_per_chunk - 1) / tiles_per_chunk;
+    const int pos_tiles = min(__ldg(p.fold + kFoldNegTile), p.n_col_tiles), neg_tiles = p.n_col_tiles - pos_tiles;
+    const int pos_share = (pos_tiles + n_chunks - 1) / n_chunks, neg_share = (neg_tiles + n_chunks - 1) / n_chunks;
+    tile_begin = min(chunk * pos_share, pos_tiles);
+    fold_npos = min(tile_begin + pos_share, pos_tiles) - tile_begin;
+    fold_neg0 = pos_tiles + min(chunk * neg_share, neg_tiles);
+    ntiles = fold_npos + min(fold_neg0 + neg_share, p.n_col_tiles) - fold_neg0;
+  }
 
   // Do not start when a CTA of this launch already gave up (keeps a failed launch short) or when
   // the image builder found rows fp16 cannot carry (the SIMT kernels take over).
@@ -823,6 +849,7 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
       mbar_init(sm + M::T_EMPTY + 8 * i, 4);  // the four warps of that row block
     }
     st_shared_i32_volatile(sm + M::ABORT, 0);
+    st_shared_i32_volatile(sm + M::FOLD_NPOS, fold_npos);
     fence_barrier_init();
   }
   if (warp == kMmaWarp0) {
@@ -849,9 +876,12 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
     __syncwarp();
     const __half* b_src = p.img_b + (int64_t)tile_begin * (kTileRows * C::KP);
     const float* v_src = FOLD ? nullptr : p.vec + ((int64_t)tchunk * p.s_pad + (int64_t)tile_begin * kColsPerTile) * TT;
+    int walk = 0, next_pos = 0, next_neg = fold_neg0 - tile_begin;  // tile offsets from tile_begin
     for (int j = 0; j < ntiles; ++j) {
       const int stage = j % S;
       if (ld_shared_i32_volatile(sm + M::ABORT)) break;
+      int tile = j;  // offset of step j's tile from tile_begin
+      if constexpr (FOLD) tile = fold_step_is_positive(walk, fold_npos, ntiles) ? next_pos++ : next_neg++;
       bool ok = mbar_wait(sm + M::B_EMPTY + 8 * stage, ((j / S) & 1) ^ 1);
       if constexpr (!FOLD) ok = ok && mbar_wait(sm + M::V_EMPTY + 8 * (j % VS), ((j / VS) & 1) ^ 1);
       if (!ok) {
@@ -862,7 +892,7 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
       if (elect_one()) {
         const uint32_t bar = sm + M::B_FULL + 8 * stage;
         mbar_expect_tx(bar, C::TILE_BYTES);
-        bulk_copy_g2s(sm + M::B + stage * C::TILE_BYTES, b_src + (int64_t)j * (kTileRows * C::KP), C::TILE_BYTES, bar);
+        bulk_copy_g2s(sm + M::B + stage * C::TILE_BYTES, b_src + (int64_t)tile * (kTileRows * C::KP), C::TILE_BYTES, bar);
         if constexpr (!FOLD) {
           const int vstage = j % VS;
           const uint32_t vbar = sm + M::V_FULL + 8 * vstage;
@@ -927,8 +957,8 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
     const uint32_t tot = sm + M::SUMS + (uint32_t)(warp * 32 + lane) * 16u;
     if constexpr (TT != kWideTT) st_shared_f4(tot, 0.f, 0.f, 0.f, 0.f);
     const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(rb * kColsPerTile);
-    int neg_first = 0;
-    if constexpr (FOLD) neg_first = __ldg(p.fold + kFoldNegTile) - tile_begin;  // first tile of this chunk that is negative
+    int walk = 0;  // folded sweep: the count of fold_step_is_positive; the chunk's positive tiles are read from
+                   // shared memory at every step (one register less in the loop that has none to spare)
     bool epi_ok = true;
 
     // outer loop = blocks of kFlushTiles tiles, with the fold between the blocks and outside the hot inner loop
@@ -957,7 +987,7 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
         tc_fence_after();
         if constexpr (FOLD) {
 #if FLK_TC_FOLD_SCALAR_SUM
-          const float sgn = j >= neg_first ? -1.0f : 1.0f;
+          const float sgn = fold_step_is_positive(walk, ld_shared_i32_volatile(sm + M::FOLD_NPOS), ntiles) ? 1.0f : -1.0f;
           float fs[4];
           unpack2(osum[0], fs[0], fs[1]);
           unpack2(osum[1], fs[2], fs[3]);
@@ -980,7 +1010,9 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
           osum[0] = pack2(fs[0], fs[1]);
           osum[1] = pack2(fs[2], fs[3]);
 #else
-          const uint64_t sgn2 = j >= neg_first ? 0xBF800000BF800000ull : 0x3F8000003F800000ull;
+          const uint64_t sgn2 = fold_step_is_positive(walk, ld_shared_i32_volatile(sm + M::FOLD_NPOS), ntiles)
+                                    ? 0x3F8000003F800000ull
+                                    : 0xBF800000BF800000ull;
           uint32_t ra[32], rc[32];
           tmem_ld32(taddr, ra);
           tmem_ld_wait_on(ra);
