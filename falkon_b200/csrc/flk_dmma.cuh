@@ -82,37 +82,60 @@ __global__ void __launch_bounds__(NT, 1) kmv_dmma_kernel(SimtArgs<double> p) {
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) oacc[mt][nt][0] = oacc[mt][nt][1] = 0.0;
 
+  // row / piece of this thread's 16-byte pieces in a full chunk: the same for the A rows r0 and r0 + 64 and the B row r0
+  static_assert(NT == 512 && BR == 128 && BC == 64 && DK == 16, "the full-chunk copy pattern assumes 512 threads");
+  const int piece_src = (tid >> 3) * ld + (tid & 7) * 2;   // offset of the piece in a row-major operand (doubles)
+  const int piece_dst = (tid >> 3) * LD + (tid & 7) * 2;   // ... in a shared-memory chunk
+  int issue_tl = 0, issue_kc = 0, issue_buf = 0;            // tile, chunk and ring buffer of the next issue() call
   auto issue = [&](int s) {
-    const int tl = s / nk, kc = s - tl * nk;
-    const int buf = s % NST;
+    const int tl = issue_tl, kc = issue_kc;
+    const int buf = issue_buf;
+    if (++issue_kc == nk) {
+      issue_kc = 0;
+      ++issue_tl;
+    }
+    if (++issue_buf == NST) issue_buf = 0;
     const int k0 = kc * DK;
     const int kw = min(DK, ld - k0);   // even (ld is a multiple of 2)
     const int kw4 = (kw + 3) & ~3;     // the MMA consumes features in groups of four
     const int pieces = kw / 2;         // 16-byte pieces per row
-    if (nk > 1 || s == 0) {
-      double* dst = As + (nk > 1 ? buf : 0) * BR * LD;
-      for (int x = tid; x < BR * pieces; x += NT) {
-        int r = x / pieces, pc = x - r * pieces;
-        cp_async16(dst + r * LD + pc * 2, Ag + (int64_t)r * ld + k0 + pc * 2);
-      }
-      if (kw4 != kw)  // zero the features the last group of four reads beyond kw
-        for (int r = tid; r < BR; r += NT) dst[r * LD + kw] = dst[r * LD + kw + 1] = 0.0;
-    }
     const int64_t col0 = (int64_t)(tile_begin + tl) * BC;
     double* dstb = Bs + buf * BC * LD;
     const double* Bg = p.B + col0 * ld + k0;
-    for (int x = tid; x < BC * pieces; x += NT) {
-      int r = x / pieces, pc = x - r * pieces;
-      cp_async16(dstb + r * LD + pc * 2, Bg + (int64_t)r * ld + pc * 2);
+    if (kw == DK) {
+      // full chunk (the common case): eight 16-byte pieces per row, so row and piece are a shift and a mask
+      // (the general form divides by a run-time number, which costs more than the copies themselves)
+      if (nk > 1 || s == 0) {
+        double* dst = As + (nk > 1 ? buf : 0) * BR * LD + piece_dst;
+        const double* src = Ag + k0 + piece_src;
+        cp_async16(dst, src);
+        cp_async16(dst + 64 * LD, src + 64 * ld);
+      }
+      cp_async16(dstb + piece_dst, Bg + piece_src);
+    } else {
+      if (nk > 1 || s == 0) {
+        double* dst = As + (nk > 1 ? buf : 0) * BR * LD;
+        for (int x = tid; x < BR * pieces; x += NT) {
+          int r = x / pieces, pc = x - r * pieces;
+          cp_async16(dst + r * LD + pc * 2, Ag + (int64_t)r * ld + k0 + pc * 2);
+        }
+        if (kw4 != kw)  // zero the features the last group of four reads beyond kw
+          for (int r = tid; r < BR; r += NT) dst[r * LD + kw] = dst[r * LD + kw + 1] = 0.0;
+      }
+      for (int x = tid; x < BC * pieces; x += NT) {
+        int r = x / pieces, pc = x - r * pieces;
+        cp_async16(dstb + r * LD + pc * 2, Bg + (int64_t)r * ld + pc * 2);
+      }
+      if (kw4 != kw)
+        for (int r = tid; r < BC; r += NT) dstb[r * LD + kw] = dstb[r * LD + kw + 1] = 0.0;
     }
-    if (kw4 != kw)
-      for (int r = tid; r < BC; r += NT) dstb[r * LD + kw] = dstb[r * LD + kw + 1] = 0.0;
     if (kc == 0) {
       const int vb = tl % NST;
       const double* vg = p.vec + ((int64_t)blockIdx.y * p.s_pad + col0) * TW;  // BC rows of TW values, contiguous
       double* vd = Vs + vb * BC * VLD;
+#pragma unroll
       for (int x = tid; x < BC * (TW / 2); x += NT) {
-        int r = x / (TW / 2), pc = x - r * (TW / 2);
+        const int r = x / (TW / 2), pc = x % (TW / 2);  // compile-time divisor
         cp_async16(vd + r * VLD + pc * 2, vg + r * TW + pc * 2);
       }
       if (tid < BC) cp_async_small<8>(bns + vb * BC + tid, p.bn + col0 + tid);
@@ -128,8 +151,9 @@ __global__ void __launch_bounds__(NT, 1) kmv_dmma_kernel(SimtArgs<double> p) {
   for (int s = 0; s < steps; ++s) {
     cp_async_wait<1>();   // chunk s has landed (chunk s + 1 may still be in flight)
     __syncthreads();      // ... for every thread, and every warp is done with step s - 1
-    if (s + 2 < steps) issue(s + 2);
-    cp_async_commit();
+    // The copies of chunk s + 2 (into the buffer that step s - 1 read) are issued AFTER the first group of MMAs of
+    // this step: their address arithmetic then runs while the MMAs are queued in the fp64 pipe, instead of every
+    // warp doing it at the same time right behind the barrier with the pipe empty.
 
     const double* a_s = As + (nk > 1 ? (s % NST) : 0) * BR * LD + (wr * 8 * MT1 + g) * LD + q;
     const double* b_s = Bs + (s % NST) * BC * LD + (wc * 32 + g) * LD + q;
@@ -146,9 +170,14 @@ __global__ void __launch_bounds__(NT, 1) kmv_dmma_kernel(SimtArgs<double> p) {
         for (int nt = 0; nt < 4; ++nt) mma884(acc[mt][nt], a[mt], b[nt]);
     };
     if (kw4 == DK) {  // full chunk: unrolled, so the fragment loads of the next group overlap the MMAs of this one
+      k_group(0);
+      if (s + 2 < steps) issue(s + 2);
+      cp_async_commit();
 #pragma unroll
-      for (int k = 0; k < DK; k += 4) k_group(k);
+      for (int k = 4; k < DK; k += 4) k_group(k);
     } else {
+      if (s + 2 < steps) issue(s + 2);
+      cp_async_commit();
       for (int k = 0; k < kw4; k += 4) k_group(k);
     }
 
