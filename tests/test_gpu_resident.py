@@ -88,8 +88,8 @@ def test_other_sizes_kernels_and_sigmas_are_never_kept():
     assert fo.rel_l2(got, fo.dense_fdmmv_fp64(Xn, Cn, v2.cpu().numpy(), w2.cpu().numpy(), "gaussian", 3.0)) <= 1e-5
 
 
-def test_range_verdict_of_a_kept_operand_is_kept_too():
-    """A row that fp16 cannot carry sends the call to the SIMT kernels; the verdict belongs to the operand and must
+def test_range_flag_of_a_kept_operand_is_kept_too():
+    """A row that fp16 cannot carry sends the call to the SIMT kernels; that range flag belongs to the operand and must
     survive when its images are kept."""
     from falkon_b200 import _lib
     from falkon_b200.kernels import GaussianKernel
