@@ -131,8 +131,8 @@ static void choose_tt(int64_t t, bool use_wide, int* tt, int* tp) {
 
 // Is one pass over groups of 32 columns cheaper than passes over groups of 4?  Relative costs per kernel value
 // and pass, from measurements on B200 (N = 1e5, M = 2e4; d = 48 / 128 / 440: 1.6 / 2.5 / 7.6 ms per pass of 4,
-// 8.7 / 10.3 / 13.5 ms per pass of 32): tensor-core paths pay max(epilogue, exponent GEMM ~ 0.08 + 0.0033 d) for 4
-// columns and about 1.75 + 0.0023 d for 32 (the 32-column epilogue is bound by its multiply-adds and shared-memory
+// 8.3 / 8.6 / 11.1 ms per pass of 32): tensor-core paths pay max(epilogue, exponent GEMM ~ 0.08 + 0.0033 d) for 4
+// columns and about 1.6 + 0.0014 d for 32 (the 32-column epilogue is bound by its multiply-adds and shared-memory
 // reads); the SIMT / DMMA paths pay d + 4 + E against d + 32 + E multiply-adds (E = the exponential: about 4 in
 // fp32, 40 in software fp64).
 static bool wide_pays_off(bool tc, int dtype, int kernel, int64_t d, int64_t t) {
@@ -140,7 +140,7 @@ static bool wide_pays_off(bool tc, int dtype, int kernel, int64_t d, int64_t t) 
   const double passes4 = (double)ceil_div(t, 4), passes32 = (double)ceil_div(t, kWideT);
   if (tc) {
     const double epi4 = kernel == FLK_GAUSSIAN ? 0.33 : 0.6;  // the other kernel functions carry a square root
-    const double cost4 = std::max(epi4, 0.08 + 0.0033 * (double)d), cost32 = 1.75 + 0.0023 * (double)d;
+    const double cost4 = std::max(epi4, 0.08 + 0.0033 * (double)d), cost32 = 1.6 + 0.0014 * (double)d;
     return passes32 * cost32 < passes4 * cost4;
   }
   const double e = dtype == FLK_F64 ? 40.0 : 4.0;

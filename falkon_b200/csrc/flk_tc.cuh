@@ -710,7 +710,9 @@ template <int KT, int PR0, int C0 = 0>
 __device__ __forceinline__ void epilogue_wide16(const uint32_t (&r)[16], const float* vsm, uint64_t (&osum)[16]) {
   if constexpr (C0 < 16) {
     float k0, k1;
-    eval_pair<KT, poly_pair<KT>(PR0 + C0 / 2)>(r[C0], r[C0 + 1], k0, k1);
+    // every exponential on the MUFU unit: this epilogue is bound by its multiply-adds, the FMA pipe has no room
+    // for the polynomial form (and its constants would cost the registers the second register block needs)
+    eval_pair<KT, false>(r[C0], r[C0 + 1], k0, k1);
     const float kv[2] = {k0, k1};
 #pragma unroll
     for (int c = 0; c < 2; ++c) {
@@ -962,7 +964,9 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
     bool epi_ok = true;
 
     // outer loop = blocks of kFlushTiles tiles, with the fold between the blocks and outside the hot inner loop
-    for (int j0 = 0; j0 < ntiles && epi_ok; j0 += kFlushTiles) {
+    // (the many-column epilogue sums in one level: a single pass of the outer loop)
+    constexpr int kFlush = TT == kWideTT ? (1 << 30) : kFlushTiles;
+    for (int j0 = 0; j0 < ntiles && epi_ok; j0 += kFlush) {
       if constexpr (TT != kWideTT) {
         if (j0 > 0) {
           float t0, t1, t2, t3, a0, a1, b0, b1;
@@ -973,7 +977,7 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
           osum[0] = osum[1] = 0ull;
         }
       }
-      const int j1 = min(j0 + kFlushTiles, ntiles);
+      const int j1 = TT == kWideTT ? ntiles : min(j0 + kFlush, ntiles);
       for (int j = j0; j < j1; ++j) {
         if (ld_shared_i32_volatile(sm + M::ABORT)) { epi_ok = false; break; }
         bool ok = true;
@@ -1031,9 +1035,13 @@ __global__ void __launch_bounds__(kThreads, 1) kmv_tc_kernel(const SweepArgs p) 
           epilogue_32_fold<KT>(rc, sgn2, osum);
 #endif
         } else {
-          const float* vsm = reinterpret_cast<const float*>(tc_smem_raw + pad + M::V) + (j % VS) * kColsPerTile * TT;
+          // generic pointer rebuilt from the 32-bit shared address: no 64-bit base stays live across the loop
+          const float* vsm = reinterpret_cast<const float*>(
+              __cvta_shared_to_generic(sm + M::V + (uint32_t)((j % VS) * kColsPerTile * TT * 4)));
           if constexpr (TT == kWideTT) {
             // eight 16-column pieces; the accumulator goes back to its issuer once the last one is in registers
+            // (the K-loop kernel keeps two register blocks in flight here; this kernel has no registers left for
+            // the second one without spilling)
             uint32_t rw[16];
 #pragma unroll
             for (int pc = 0; pc < 8; ++pc) {

@@ -509,23 +509,25 @@ __global__ void __launch_bounds__(kThreadsL, 1) kmv_tck_kernel(const SweepArgsL 
       const float* vsm = reinterpret_cast<const float*>(
           __cvta_shared_to_generic(sm + kVecOff + vstage * kVecTileBytes + (uint32_t)(vcol * TT * 4)));
       if constexpr (TT == kWideTT) {
-        // 32 running sums per thread leave room for 16 columns at a time: four pieces; the accumulator goes back
-        // to its issuer once the last one is in registers
-        uint32_t rw[16];
-#pragma unroll
-        for (int pc = 0; pc < 4; ++pc) {
-          tmem_ld16(taddr + pc * 16, rw);
-          tmem_ld_wait_on(rw);
-          if (pc == 3) {
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(sm + kTEmpty + 8 * acc);
-          }
-          if (pc & 1)
-            epilogue_wide16<KT, 8>(rw, vsm + pc * 16 * TT, osum);
-          else
-            epilogue_wide16<KT, 0>(rw, vsm + pc * 16 * TT, osum);
-        }
+        // 32 running sums per thread leave room for 16 columns at a time: four pieces through two register blocks,
+        // the load of the next piece in flight while this one is evaluated; the accumulator goes back to its issuer
+        // once the last piece is in registers
+        uint32_t rw0[16], rw1[16];
+        tmem_ld16(taddr, rw0);
+        tmem_ld_wait_on(rw0);
+        tmem_ld16(taddr + 16, rw1);
+        epilogue_wide16<KT, 0>(rw0, vsm, osum);
+        tmem_ld_wait_on(rw1);
+        tmem_ld16(taddr + 32, rw0);
+        epilogue_wide16<KT, 8>(rw1, vsm + 16 * TT, osum);
+        tmem_ld_wait_on(rw0);
+        tmem_ld16(taddr + 48, rw1);
+        epilogue_wide16<KT, 0>(rw0, vsm + 32 * TT, osum);
+        tmem_ld_wait_on(rw1);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(sm + kTEmpty + 8 * acc);
+        epilogue_wide16<KT, 8>(rw1, vsm + 48 * TT, osum);
       } else {
         // 32 columns at a time through one register block (two blocks in flight left no room for the constants of
         // the polynomial exponential); the accumulator goes back once the second piece is in registers -- the other
