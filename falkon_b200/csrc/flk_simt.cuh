@@ -113,16 +113,23 @@ __global__ void __launch_bounds__(256, (TT == 1 ? 2 : 1)) kmv_simt_kernel(SimtAr
     for (int j = 0; j < TC; ++j) acc[i][j] = 0;
   }
 
-  auto issue = [&](int s) {
-    const int tl = s / nk, kc = s - tl * nk;
+  // 16-byte pieces per row of a chunk: DK / VEC (a power of two) for a full chunk, fewer for the last one of a row.
+  // Row and piece of copy q are q / pieces and the remainder; the division by the run-time count of the last chunk
+  // is a multiplication by its 16-bit reciprocal (exact for q < 8192), computed once.
+  constexpr int kFullPieces = DK / VEC;
+  static_assert((kFullPieces & (kFullPieces - 1)) == 0 && BR * kFullPieces < 8192, "piece arithmetic");
+  const int last_pieces = (ld - (nk - 1) * DK) / VEC;
+  const int last_recip = (65536 + last_pieces - 1) / last_pieces;
+  auto issue = [&](int s, int tl, int kc) {  // chunk kc of tile tl is step s
     const int buf = s & 1;
     const int k0 = kc * DK;
-    const int kw = min(DK, ld - k0);
-    const int pieces = kw / VEC;  // 16-byte pieces per row
+    const bool full = kc < nk - 1 || last_pieces == kFullPieces;
+    const int pieces = full ? kFullPieces : last_pieces;
+    const int recip = full ? 65536 / kFullPieces : last_recip;
     if (nk > 1 || s == 0) {
       T* dst = As + (nk > 1 ? buf : 0) * BR * LD;
       for (int q = tid; q < BR * pieces; q += 256) {
-        int r = q / pieces, pc = q - r * pieces;
+        const int r = (q * recip) >> 16, pc = q - r * pieces;
         cp_async16(dst + r * LD + pc * VEC, Ag + (int64_t)r * ld + k0 + pc * VEC);
       }
     }
@@ -130,7 +137,7 @@ __global__ void __launch_bounds__(256, (TT == 1 ? 2 : 1)) kmv_simt_kernel(SimtAr
     T* dstb = Bs + buf * BC * LD;
     const T* Bg = p.B + col0 * ld + k0;
     for (int q = tid; q < BC * pieces; q += 256) {
-      int r = q / pieces, pc = q - r * pieces;
+      const int r = (q * recip) >> 16, pc = q - r * pieces;
       cp_async16(dstb + r * LD + pc * VEC, Bg + (int64_t)r * ld + pc * VEC);
     }
     if (kc == 0 && tid < BC) {
@@ -152,20 +159,26 @@ __global__ void __launch_bounds__(256, (TT == 1 ? 2 : 1)) kmv_simt_kernel(SimtAr
     }
   };
 
-  issue(0);
+  issue(0, 0, 0);
   cp_async_commit();
 
   int tl = 0, kc = 0;
   for (int s = 0; s < steps; ++s) {
-    if (s + 1 < steps) issue(s + 1);
+    cp_async_wait<0>();  // chunk s has landed
+    __syncthreads();     // ... for every thread, and every thread is done with step s - 1, whose buffers are free now
+    // (one barrier per step: the copies of chunk s + 1 go into those buffers and have the whole step to land)
+    if (s + 1 < steps) {
+      if (kc + 1 == nk)
+        issue(s + 1, tl + 1, 0);
+      else
+        issue(s + 1, tl, kc + 1);
+    }
     cp_async_commit();
-    cp_async_wait<1>();
-    __syncthreads();
 
     const T* a_s = As + (nk > 1 ? (s & 1) : 0) * BR * LD;
     const T* b_s = Bs + (s & 1) * BC * LD;
     const int kw = min(DK, ld - kc * DK);
-    for (int k = 0; k < kw; k += VEC) {
+    auto k_iter = [&](int k) {
       Vec b[TC];
 #pragma unroll
       for (int j = 0; j < TC; ++j) b[j] = *reinterpret_cast<const Vec*>(b_s + (tx + 16 * j) * LD + k);
@@ -175,7 +188,8 @@ __global__ void __launch_bounds__(256, (TT == 1 ? 2 : 1)) kmv_simt_kernel(SimtAr
 #pragma unroll
         for (int j = 0; j < TC; ++j) acc[i][j] = dot_vec(a, b[j], acc[i][j]);
       }
-    }
+    };
+    for (int k = 0; k < kw; k += VEC) k_iter(k);
 
     if (kc == nk - 1) {
       const T* v_s = vs + (tl & 1) * BC * TT;
@@ -202,7 +216,6 @@ __global__ void __launch_bounds__(256, (TT == 1 ? 2 : 1)) kmv_simt_kernel(SimtAr
     } else {
       ++kc;
     }
-    __syncthreads();
   }
 
   // combine the 16 threads (consecutive lanes) that hold partial sums of the same rows
